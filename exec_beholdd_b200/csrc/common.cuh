@@ -1,0 +1,176 @@
+// Shared declarations of the beholdd_b200 library: context and weight handles, error
+// plumbing, and the per-element decoders of the packed GGUF block formats.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/beholdd_b200.h"
+
+#define BHD_CTX_MAGIC 0x62686443u  // "bhdC"
+#define BHD_WEIGHT_MAGIC 0x62686457u  // "bhdW"
+
+// Device status word bits (kernels OR them in; bhd_check_status reports and clears them).
+#define BHD_DEV_NAN_IN_SOFTMAX 1u
+#define BHD_DEV_BAD_EXPERT_ID 2u
+#define BHD_DEV_WAIT_TIMEOUT 4u
+#define BHD_DEV_BAD_ROUTE_PROB 8u
+
+struct bhd_ctx {
+    uint32_t magic;
+    int device;
+    int sm_count;
+    char err[512];
+    uint8_t* workspace;     // grown on demand; used by calls in stream order
+    size_t workspace_bytes;
+    uint32_t* status_dev;   // device status word (+ spare words)
+    uint32_t* status_host;  // pinned mirror
+    float* stage_x;         // device staging for the host-buffer entry points
+    float* stage_y;
+    size_t stage_x_bytes, stage_y_bytes;
+    void* pinned;           // pinned bounce buffer for host entry points
+    size_t pinned_bytes;
+    uint64_t launches;
+    void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
+};
+
+struct bhd_weight {
+    uint32_t magic;
+    bhd_ctx* ctx;
+    uint8_t* dev;
+    bool owned;
+    uint32_t kind;
+    uint64_t rows, cols, slabs;
+    uint64_t row_bytes;   // packed bytes of one row
+    uint64_t slab_bytes;  // rows * row_bytes
+    // 2-D tensor map over all rows of all slabs ([slabs*rows][row_bytes] bytes) for the
+    // TMA-staged kernels; valid only when `tmap_ok`.
+    alignas(64) unsigned char tmap[128];
+    bool tmap_ok;
+    uint32_t tmap_box_rows, tmap_box_bytes;
+};
+
+int32_t bhd_fail(bhd_ctx* ctx, int32_t status, const char* fmt, ...);
+int32_t bhd_cuda_fail(bhd_ctx* ctx, cudaError_t e, const char* what);
+int32_t bhd_ensure_workspace(bhd_ctx* ctx, size_t bytes, cudaStream_t stream);
+const char* bhd_kind_name(uint32_t kind);
+bool bhd_block_geometry(uint32_t kind, uint64_t* elems, uint64_t* bytes);
+
+#define BHD_CUDA(ctx, call, what)                                   \
+    do {                                                            \
+        cudaError_t _e = (call);                                    \
+        if (_e != cudaSuccess) return bhd_cuda_fail(ctx, _e, what); \
+    } while (0)
+
+#define BHD_LAUNCHED(ctx, what)                                     \
+    do {                                                            \
+        cudaError_t _e = cudaGetLastError();                        \
+        if (_e != cudaSuccess) return bhd_cuda_fail(ctx, _e, what); \
+        (ctx)->launches += 1;                                       \
+    } while (0)
+
+// ---- per-element decoders -------------------------------------------------------------
+// Each returns exactly the f32 the reference's CPU decoder produces for element k of a
+// packed row (crates/beholdd-kernel/src/kquant.rs:39-54, 115-162, 209-241, 268-303): the
+// same multiplications in the same order, each rounded to f32 (no FMA contraction).
+
+__device__ __forceinline__ float bhd_f16_bits_to_f32(uint16_t h) {
+    // Exact for every bit pattern including subnormals, like
+    // crates/beholdd-core/src/quant.rs:259-278.
+    return __half2float(__ushort_as_half(h));
+}
+
+// Every 16-bit field of every supported block format sits at an even offset of an even-sized
+// block, and weight bases are at least 16-byte aligned, so this load is always aligned.
+__device__ __forceinline__ uint16_t bhd_ld_u16(const uint8_t* p) {
+    return *reinterpret_cast<const uint16_t*>(p);
+}
+
+__device__ __forceinline__ void bhd_scale_min_k4(int j, const uint8_t* q, uint32_t* sc, uint32_t* m) {
+    if (j < 4) {
+        *sc = q[j] & 63u;
+        *m = q[j + 4] & 63u;
+    } else {
+        *sc = (q[j + 4] & 0xFu) | ((uint32_t(q[j - 4]) >> 6) << 4);
+        *m = (uint32_t(q[j + 4]) >> 4) | ((uint32_t(q[j]) >> 6) << 4);
+    }
+}
+
+template <uint32_t KIND>
+__device__ __forceinline__ float bhd_decode_elem(const uint8_t* row, uint64_t k);
+
+template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_F32>(const uint8_t* row, uint64_t k) {
+    return *reinterpret_cast<const float*>(row + 4 * k);
+}
+
+template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_F16>(const uint8_t* row, uint64_t k) {
+    return bhd_f16_bits_to_f32(bhd_ld_u16(row + 2 * k));
+}
+
+template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q8_0>(const uint8_t* row, uint64_t k) {
+    const uint8_t* blk = row + (k >> 5) * 34;
+    const float d = bhd_f16_bits_to_f32(bhd_ld_u16(blk));
+    return __fmul_rn(d, float(int8_t(blk[2 + (k & 31)])));
+}
+
+template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q4_K>(const uint8_t* row, uint64_t k) {
+    const uint8_t* blk = row + (k >> 8) * 144;
+    const uint32_t i = uint32_t(k & 255), pass = i >> 6, hi = (i >> 5) & 1, l = i & 31;
+    const float d = bhd_f16_bits_to_f32(bhd_ld_u16(blk));
+    const float dmin = bhd_f16_bits_to_f32(bhd_ld_u16(blk + 2));
+    uint32_t sc, m;
+    bhd_scale_min_k4(int(pass * 2 + hi), blk + 4, &sc, &m);
+    const uint32_t q = (uint32_t(blk[16 + pass * 32 + l]) >> (4 * hi)) & 15u;
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, float(sc)), float(q)), __fmul_rn(dmin, float(m)));
+}
+
+template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q5_K>(const uint8_t* row, uint64_t k) {
+    const uint8_t* blk = row + (k >> 8) * 176;
+    const uint32_t i = uint32_t(k & 255), pass = i >> 6, hi = (i >> 5) & 1, l = i & 31;
+    const float d = bhd_f16_bits_to_f32(bhd_ld_u16(blk));
+    const float dmin = bhd_f16_bits_to_f32(bhd_ld_u16(blk + 2));
+    uint32_t sc, m;
+    bhd_scale_min_k4(int(pass * 2 + hi), blk + 4, &sc, &m);
+    const uint32_t bit = (uint32_t(blk[16 + l]) >> (pass * 2 + hi)) & 1u;
+    const uint32_t q = ((uint32_t(blk[48 + pass * 32 + l]) >> (4 * hi)) & 15u) + 16u * bit;
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, float(sc)), float(q)), __fmul_rn(dmin, float(m)));
+}
+
+template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q6_K>(const uint8_t* row, uint64_t k) {
+    const uint8_t* blk = row + (k >> 8) * 210;
+    const uint32_t i = uint32_t(k & 255), half_i = i >> 7, within = i & 127, group = within >> 5, lane = within & 31;
+    const uint32_t low = (uint32_t(blk[half_i * 64 + (group & 1) * 32 + lane]) >> (4 * (group >> 1))) & 15u;
+    const uint32_t high = (uint32_t(blk[128 + half_i * 32 + lane]) >> (2 * group)) & 3u;
+    const int code = int(low | (high << 4)) - 32;
+    const float d = bhd_f16_bits_to_f32(bhd_ld_u16(blk + 208));
+    const float scale = float(int8_t(blk[192 + (i >> 4)]));
+    return __fmul_rn(__fmul_rn(d, scale), float(code));
+}
+
+// Dispatch a template on the weight kind.
+#define BHD_DISPATCH_KIND(kind, MACRO)                   \
+    switch (kind) {                                      \
+        case BHD_TYPE_F32: MACRO(BHD_TYPE_F32); break;   \
+        case BHD_TYPE_F16: MACRO(BHD_TYPE_F16); break;   \
+        case BHD_TYPE_Q8_0: MACRO(BHD_TYPE_Q8_0); break; \
+        case BHD_TYPE_Q4_K: MACRO(BHD_TYPE_Q4_K); break; \
+        case BHD_TYPE_Q5_K: MACRO(BHD_TYPE_Q5_K); break; \
+        case BHD_TYPE_Q6_K: MACRO(BHD_TYPE_Q6_K); break; \
+        default: break;                                  \
+    }
+
+// ---- kernel launchers implemented across the .cu files --------------------------------
+int32_t bhd_launch_dequantize(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, float* out, cudaStream_t s);
+int32_t bhd_launch_matvec_strict(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
+                                 uint32_t batch, float scale, int accumulate, cudaStream_t s);
+int32_t bhd_launch_matvec_general(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
+                                  uint64_t batch, float scale, int accumulate, cudaStream_t s);

@@ -1,0 +1,323 @@
+// The qwen3moe routed-expert block: router softmax + stable top-k + renormalisation,
+// per-expert route counts, and the general (any shape) expert kernels.
+//
+// Follows crates/beholdd-model/src/qwen3moe/forward.rs:1299-1407 and :1886-1924 of the
+// reference; the arithmetic that decides expert *indices* is kept in the CPU's exact
+// order so that the selection is the CPU's selection.
+#include "common.cuh"
+#include "expf_exact.h"
+
+namespace {
+
+constexpr int NEAR_MISS_WINDOW = 8;  // forward.rs NEAR_MISS_WINDOW
+
+// One CTA per position; thread e owns expert e (n_experts <= 1024).
+// Input: logits (bit-identical to the CPU's router matvec, computed by the order-exact
+// matvec kernel) in probs[t][e]; output: probabilities in place plus the selection.
+__global__ void k_route_select(float* __restrict__ probs, uint32_t n_experts, uint32_t top_k,
+                               int32_t* __restrict__ experts_out, float* __restrict__ weights_out,
+                               int32_t* __restrict__ counts, int32_t* __restrict__ near_out, uint32_t near_per,
+                               uint32_t* __restrict__ status) {
+    extern __shared__ float sh[];  // [n_experts] values, then selection scratch
+    float* val = sh;
+    float* psel = sh + n_experts;                                   // [top_k]
+    int32_t* isel = reinterpret_cast<int32_t*>(psel + top_k);       // [top_k]
+    __shared__ float s_red[32];
+    __shared__ float s_max, s_inv;
+    __shared__ double s_sum64;
+
+    const uint32_t t = blockIdx.x, e = threadIdx.x;
+    float* row = probs + uint64_t(t) * n_experts;
+    const bool live = e < n_experts;
+    float v = live ? row[e] : -INFINITY;
+    if (live && isnan(v)) atomicOr(status, BHD_DEV_NAN_IN_SOFTMAX);  // Device::softmax refuses NaN (cpu.rs:576-580)
+
+    // max (order-independent); vecops.rs:71
+    float m = v;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((e & 31) == 0) s_red[e >> 5] = m;
+    __syncthreads();
+    if (e < 32) {
+        float mm = e < (blockDim.x >> 5) ? s_red[e] : -INFINITY;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+        if (e == 0) s_max = mm;
+    }
+    __syncthreads();
+    m = s_max;
+    const bool all_masked = !isfinite(m);  // vecops.rs:72-77: every entry -inf (or +inf max) -> zeros
+    float ev = 0.0f;
+    if (live && !all_masked) ev = isfinite(v) ? bhd_expf_exact(__fsub_rn(v, m)) : 0.0f;
+    if (live) val[e] = ev;
+    __syncthreads();
+    if (e == 0) {
+        // Sequential f32 sum in index order, vecops.rs:78-83.
+        float sum = 0.0f;
+        for (uint32_t i = 0; i < n_experts; ++i) sum = __fadd_rn(sum, val[i]);
+        s_inv = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    const float p = all_masked ? 0.0f : __fmul_rn(ev, s_inv);
+    __syncthreads();
+    if (live) {
+        val[e] = p;
+        row[e] = p;
+    }
+    if (top_k == 0) return;  // softmax only
+    __syncthreads();
+    if (live) {
+        // Rank of expert e under (probability descending, index ascending): forward.rs:1902-1906.
+        if (!(isfinite(p) && p >= 0.0f)) atomicOr(status, BHD_DEV_BAD_ROUTE_PROB);  // forward.rs:1893-1898
+        uint32_t rank = 0;
+        for (uint32_t j = 0; j < n_experts; ++j) {
+            const float pj = val[j];
+            rank += (pj > p || (pj == p && j < e)) ? 1u : 0u;
+        }
+        if (rank < top_k) {
+            psel[rank] = p;
+            isel[rank] = int32_t(e);
+        } else if (near_out && rank < top_k + near_per) {
+            near_out[uint64_t(t) * near_per + (rank - top_k)] = int32_t(e);
+        }
+    }
+    __syncthreads();
+    if (e == 0) {
+        // f64 sum of the selected probabilities in selection order, forward.rs:1910-1916.
+        double sum = 0.0;
+        for (uint32_t i = 0; i < top_k; ++i) sum = __dadd_rn(sum, double(psel[i]));
+        if (!(isfinite(sum) && sum > 0.0)) atomicOr(status, BHD_DEV_BAD_ROUTE_PROB);
+        s_sum64 = sum;
+    }
+    __syncthreads();
+    if (e < top_k) {
+        const uint64_t o = uint64_t(t) * top_k + e;
+        experts_out[o] = isel[e];
+        weights_out[o] = __double2float_rn(__ddiv_rn(double(psel[e]), s_sum64));  // forward.rs:1918-1922
+        if (counts) atomicAdd(&counts[isel[e]], 1);
+    }
+}
+
+// ---- general expert kernels (any dim / expert_ff that are whole Q8_0 blocks) -----------
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// One warp per (route, ff row): gate and up dot products of the route's expert with the
+// route's position, then SiLU gating (vecops.rs:91-111 with limit 0).
+__global__ void k_moe_gate_up_warp(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ up,
+                                   uint64_t slab_bytes, uint64_t row_bytes, uint32_t dim, uint32_t ff,
+                                   const float* __restrict__ x, const int32_t* __restrict__ experts, uint32_t top_k,
+                                   uint32_t first_expert, uint32_t n_local, uint32_t n_experts_total,
+                                   float* __restrict__ act, uint32_t* __restrict__ status) {
+    const uint32_t route = blockIdx.y;
+    const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (f >= ff) return;
+    const int32_t e = experts[route];
+    if (e < 0 || uint32_t(e) >= n_experts_total) {
+        if (lane == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+        return;
+    }
+    if (uint32_t(e) < first_expert || uint32_t(e) >= first_expert + n_local) return;
+    const uint64_t off = uint64_t(uint32_t(e) - first_expert) * slab_bytes + uint64_t(f) * row_bytes;
+    const uint8_t* grow = gate + off;
+    const uint8_t* urow = up + off;
+    const float* xv = x + uint64_t(route / top_k) * dim;
+    float g = 0.0f, u = 0.0f;
+    for (uint32_t k = lane; k < dim; k += 32) {
+        const float xk = xv[k];
+        g = fmaf(bhd_decode_elem<BHD_TYPE_Q8_0>(grow, k), xk, g);
+        u = fmaf(bhd_decode_elem<BHD_TYPE_Q8_0>(urow, k), xk, u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) act[uint64_t(route) * ff + f] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+}
+
+// One warp per (position, output row): the down projections of the position's routes,
+// scaled by the route weight and added in selection order into a zero accumulator
+// (forward.rs:1385-1398; cpu.rs:280-284: out += acc * scale, product and sum rounded apart).
+__global__ void k_moe_down_warp(const uint8_t* __restrict__ down, uint64_t slab_bytes, uint64_t row_bytes,
+                                uint32_t dim, uint32_t ff, const float* __restrict__ act,
+                                const int32_t* __restrict__ experts, const float* __restrict__ weights,
+                                uint32_t top_k, uint32_t first_expert, uint32_t n_local, float* __restrict__ y,
+                                int accumulate) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (h >= dim) return;
+    float out = 0.0f;
+    for (uint32_t j = 0; j < top_k; ++j) {
+        const uint32_t route = t * top_k + j;
+        const int32_t e = experts[route];
+        if (e < 0 || uint32_t(e) < first_expert || uint32_t(e) >= first_expert + n_local) continue;
+        const uint8_t* drow = down + uint64_t(uint32_t(e) - first_expert) * slab_bytes + uint64_t(h) * row_bytes;
+        const float* a = act + uint64_t(route) * ff;
+        float d = 0.0f;
+        for (uint32_t k = lane; k < ff; k += 32) d = fmaf(bhd_decode_elem<BHD_TYPE_Q8_0>(drow, k), a[k], d);
+        d = warp_sum(d);
+        out = __fadd_rn(out, __fmul_rn(d, weights[route]));
+    }
+    if (lane == 0) {
+        float* dst = y + uint64_t(t) * dim + h;
+        *dst = accumulate ? __fadd_rn(*dst, out) : out;
+    }
+}
+
+__global__ void k_moe_combine(const float* __restrict__ per_route, float* __restrict__ y, uint64_t n, uint32_t top_k,
+                              int accumulate) {
+    const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (i >= n) return;
+    float out = 0.0f;
+    for (uint32_t j = 0; j < top_k; ++j) out = __fadd_rn(out, per_route[uint64_t(j) * n + i]);
+    y[i] = accumulate ? __fadd_rn(y[i], out) : out;
+}
+
+bool valid_ctx(const bhd_ctx* c) { return c && c->magic == BHD_CTX_MAGIC; }
+bool valid_w(const bhd_ctx* c, const bhd_weight* w) { return w && w->magic == BHD_WEIGHT_MAGIC && w->ctx == c; }
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" int32_t bhd_softmax(bhd_ctx* ctx, float* v_dev, uint64_t n_rows, uint64_t n, void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (n == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: softmax input cannot be empty");
+    if (n > 1024) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: softmax rows longer than 1024 are not supported");
+    if (n_rows == 0) return BHD_OK;
+    if (!v_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "softmax: null buffer");
+    // Reuses the router kernel with top_k = 0: softmax only.
+    const unsigned threads = unsigned((n + 31) / 32 * 32);
+    const size_t smem = n * sizeof(float) + 16;
+    k_route_select<<<unsigned(n_rows), threads, smem, cudaStream_t(stream)>>>(v_dev, uint32_t(n), 0, nullptr, nullptr,
+                                                                               nullptr, nullptr, 0, ctx->status_dev);
+    BHD_LAUNCHED(ctx, "softmax kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const float* x_dev, uint64_t n_positions,
+                                 uint32_t top_k, int32_t* experts_dev, float* weights_dev, int32_t* counts_dev,
+                                 int32_t* near_dev, float* probs_dev, void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (!valid_w(ctx, router)) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_route: router is not a weight of this context");
+    const uint64_t n_experts = router->rows;
+    if (top_k == 0 || top_k > n_experts)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: top-k must be between 1 and %llu, got %u",
+                        (unsigned long long)n_experts, top_k);
+    if (n_experts > 1024) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: more than 1024 experts are not supported");
+    if (n_positions == 0) return BHD_OK;
+    if (!x_dev || !experts_dev || !weights_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_route: null buffer");
+    cudaStream_t s = cudaStream_t(stream);
+    float* probs = probs_dev;
+    if (!probs) {
+        const int32_t st = bhd_ensure_workspace(ctx, n_positions * n_experts * sizeof(float), s);
+        if (st != BHD_OK) return st;
+        probs = reinterpret_cast<float*>(ctx->workspace);
+    }
+    if (counts_dev) BHD_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, n_experts * sizeof(int32_t), s), "clearing expert counts");
+    // Router logits in the CPU's summation order (forward.rs:1330-1336 -> cpu.rs:198-218).
+    int32_t st = bhd_launch_matvec_strict(ctx, router, 0, x_dev, probs, uint32_t(n_positions), 1.0f, 0, s);
+    if (st != BHD_OK) return st;
+    const uint32_t near_per = uint32_t(n_experts - top_k < NEAR_MISS_WINDOW ? n_experts - top_k : NEAR_MISS_WINDOW);
+    const unsigned threads = unsigned((n_experts + 31) / 32 * 32);
+    const size_t smem = (n_experts + 2 * top_k) * sizeof(float) + 16;
+    k_route_select<<<unsigned(n_positions), threads, smem, s>>>(probs, uint32_t(n_experts), top_k, experts_dev,
+                                                                 weights_dev, counts_dev, near_dev, near_per,
+                                                                 ctx->status_dev);
+    BHD_LAUNCHED(ctx, "route selection kernel");
+    return BHD_OK;
+}
+
+int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
+                             const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
+                             uint32_t first_expert, uint32_t n_local, float* y, int accumulate, cudaStream_t s,
+                             bool* handled);
+
+extern "C" int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps,
+                                   const bhd_weight* down_exps, const float* x_dev, uint64_t n_positions,
+                                   uint32_t top_k, const int32_t* experts_dev, const float* weights_dev,
+                                   uint32_t first_expert, uint32_t n_local, float* y_dev, int32_t accumulate,
+                                   void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (!valid_w(ctx, gate_exps) || !valid_w(ctx, up_exps) || !valid_w(ctx, down_exps))
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_experts: expert tensors are not weights of this context");
+    if (gate_exps->kind != BHD_TYPE_Q8_0 || up_exps->kind != BHD_TYPE_Q8_0 || down_exps->kind != BHD_TYPE_Q8_0)
+        return bhd_fail(ctx, BHD_ERR_UNSUPPORTED_FORMAT, "%s cannot decode %s routed experts (Q8_0 only)",
+                        bhd_device_name(), bhd_kind_name(gate_exps->kind));
+    const uint64_t ff = gate_exps->rows, dim = gate_exps->cols;
+    if (up_exps->rows != ff || up_exps->cols != dim || down_exps->rows != dim || down_exps->cols != ff ||
+        gate_exps->slabs != up_exps->slabs || gate_exps->slabs != down_exps->slabs)
+        return bhd_fail(ctx, BHD_ERR_SHAPE,
+                        "shape mismatch: experts gate %llux%llux%llu, up %llux%llux%llu, down %llux%llux%llu",
+                        (unsigned long long)gate_exps->rows, (unsigned long long)gate_exps->cols,
+                        (unsigned long long)gate_exps->slabs, (unsigned long long)up_exps->rows,
+                        (unsigned long long)up_exps->cols, (unsigned long long)up_exps->slabs,
+                        (unsigned long long)down_exps->rows, (unsigned long long)down_exps->cols,
+                        (unsigned long long)down_exps->slabs);
+    if (n_local != gate_exps->slabs)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: %u local experts but the tensors hold %llu slabs", n_local,
+                        (unsigned long long)gate_exps->slabs);
+    if (top_k == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: top-k must be positive");
+    if (n_positions == 0) return BHD_OK;
+    if (!x_dev || !experts_dev || !weights_dev || !y_dev)
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_experts: null buffer");
+    if (n_positions * top_k > 0x7fffffffull || dim > 0x7fffffffull || ff > 0x7fffffffull)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: routed block too large");
+    cudaStream_t s = cudaStream_t(stream);
+
+    bool handled = false;
+    int32_t st = bhd_moe_experts_fast(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev,
+                                      weights_dev, first_expert, n_local, y_dev, accumulate, s, &handled);
+    if (st != BHD_OK || handled) return st;
+
+    const uint64_t routes = n_positions * top_k;
+    st = bhd_ensure_workspace(ctx, align_up(routes * ff * sizeof(float), 256), s);
+    if (st != BHD_OK) return st;
+    float* act = reinterpret_cast<float*>(ctx->workspace);
+    const int warps = 8;
+    // An expert id beyond every rank's range is an error; ids outside this rank's range are skipped.
+    const uint32_t total = 0x7fffffffu;
+    k_moe_gate_up_warp<<<dim3(unsigned((ff + warps - 1) / warps), unsigned(routes)), warps * 32, 0, s>>>(
+        gate_exps->dev, up_exps->dev, gate_exps->slab_bytes, gate_exps->row_bytes, uint32_t(dim), uint32_t(ff), x_dev,
+        experts_dev, top_k, first_expert, n_local, total, act, ctx->status_dev);
+    BHD_LAUNCHED(ctx, "expert gate/up kernel");
+    k_moe_down_warp<<<dim3(unsigned((dim + warps - 1) / warps), unsigned(n_positions)), warps * 32, 0, s>>>(
+        down_exps->dev, down_exps->slab_bytes, down_exps->row_bytes, uint32_t(dim), uint32_t(ff), act, experts_dev,
+        weights_dev, top_k, first_expert, n_local, y_dev, accumulate);
+    BHD_LAUNCHED(ctx, "expert down kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, float* y_dev, uint64_t n_positions,
+                                   uint32_t top_k, uint64_t dim, int32_t accumulate, void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    const uint64_t n = n_positions * dim;
+    if (n == 0) return BHD_OK;
+    if (!per_route_dev || !y_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_combine: null buffer");
+    k_moe_combine<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(per_route_dev, y_dev, n, top_k, accumulate);
+    BHD_LAUNCHED(ctx, "route combine kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_moe_layer(bhd_ctx* ctx, const bhd_weight* router, const bhd_weight* gate_exps,
+                                 const bhd_weight* up_exps, const bhd_weight* down_exps, const float* x_dev,
+                                 float* y_dev, uint64_t n_positions, uint32_t top_k, int32_t* experts_dev,
+                                 float* weights_dev, int32_t* counts_dev, int32_t accumulate, void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (!valid_w(ctx, router) || !valid_w(ctx, gate_exps))
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_layer: tensors are not weights of this context");
+    if (router->cols != gate_exps->cols || router->rows != gate_exps->slabs)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: router %llux%llu against %llu experts of width %llu",
+                        (unsigned long long)router->rows, (unsigned long long)router->cols,
+                        (unsigned long long)gate_exps->slabs, (unsigned long long)gate_exps->cols);
+    if (!experts_dev || !weights_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_layer: null routing buffers");
+    int32_t st = bhd_moe_route(ctx, router, x_dev, n_positions, top_k, experts_dev, weights_dev, counts_dev, nullptr,
+                               nullptr, stream);
+    if (st != BHD_OK) return st;
+    return bhd_moe_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev, weights_dev, 0,
+                           uint32_t(gate_exps->slabs), y_dev, accumulate, stream);
+}

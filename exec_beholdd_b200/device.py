@@ -1,0 +1,332 @@
+"""Host side of the drop-in boundary: the reference's operator interface over the C ABI.
+
+`CudaDevice` mirrors `beholdd_backend::Device` (crates/beholdd-backend/src/lib.rs:164-272)
+for the operators on the quantised-matvec / routed-expert path, with the same names,
+argument meaning and refusal behaviour, and the resident half of `ExecutionDevice`
+(crates/beholdd-backend/src/execution.rs:1066-1114: upload_weight, then operators on
+device-resident tensors). Everything runs in `libbeholdd_b200.so`; there is no CPU
+fallback, and importing the library fails loudly when the shared object is missing.
+
+torch is used only to own device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libbeholdd_b200.so")
+
+OK = 0
+ERR_UNSUPPORTED_FORMAT, ERR_SHAPE, ERR_ALLOCATION, ERR_BACKEND, ERR_INVALID_ARGUMENT, ERR_DEVICE_STATUS = -1, -2, -3, -4, -5, -6
+
+#: every symbol include/beholdd_b200.h declares
+EXPORTS = [
+    "bhd_error_text", "bhd_last_error_message", "bhd_device_name", "bhd_ctx_create", "bhd_ctx_destroy", "bhd_supports",
+    "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_host",
+    "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
+    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count",
+]
+
+
+class DeviceError(Exception):
+    """crates/beholdd-backend/src/lib.rs:60-101"""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class UnsupportedFormat(DeviceError):
+    pass
+
+
+class ShapeError(DeviceError):
+    pass
+
+
+class AllocationError(DeviceError):
+    pass
+
+
+class BackendError(DeviceError):
+    pass
+
+
+_ERRORS = {ERR_UNSUPPORTED_FORMAT: UnsupportedFormat, ERR_SHAPE: ShapeError, ERR_ALLOCATION: AllocationError}
+
+
+def load_library(path: str | None = None) -> C.CDLL:
+    path = path or LIB_PATH
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python -m exec_beholdd_b200.build` "
+                          "(there is no fallback implementation)")
+    lib = C.CDLL(path)
+    vp, u64, u32, i32, f32 = C.c_void_p, C.c_uint64, C.c_uint32, C.c_int32, C.c_float
+    lib.bhd_error_text.restype = C.c_char_p
+    lib.bhd_error_text.argtypes = [i32]
+    lib.bhd_device_name.restype = C.c_char_p
+    lib.bhd_last_error_message.argtypes = [vp, C.c_char_p, i32]
+    lib.bhd_ctx_create.argtypes = [i32, C.POINTER(vp)]
+    lib.bhd_ctx_destroy.argtypes = [vp]
+    lib.bhd_supports.argtypes = [u32]
+    lib.bhd_weight_upload.argtypes = [vp, vp, u64, u32, u64, u64, u64, C.POINTER(vp)]
+    lib.bhd_weight_wrap_device.argtypes = [vp, vp, u64, u32, u64, u64, u64, C.POINTER(vp)]
+    lib.bhd_weight_free.argtypes = [vp]
+    lib.bhd_dequantize.argtypes = [vp, vp, u64, vp, u64, vp]
+    lib.bhd_matvec.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32, vp]
+    lib.bhd_matvec_host.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32]
+    lib.bhd_matmul.argtypes = [vp, vp, u64, vp, vp, u64, vp]
+    lib.bhd_softmax.argtypes = [vp, vp, u64, u64, vp]
+    lib.bhd_swiglu.argtypes = [vp, vp, vp, u64, f32, vp]
+    lib.bhd_add_in_place.argtypes = [vp, vp, vp, u64, vp]
+    lib.bhd_moe_route.argtypes = [vp, vp, vp, u64, u32, vp, vp, vp, vp, vp, vp]
+    lib.bhd_moe_experts.argtypes = [vp, vp, vp, vp, vp, u64, u32, vp, vp, u32, u32, vp, i32, vp]
+    lib.bhd_moe_combine.argtypes = [vp, vp, vp, u64, u32, u64, i32, vp]
+    lib.bhd_moe_layer.argtypes = [vp, vp, vp, vp, vp, vp, vp, u64, u32, vp, vp, vp, i32, vp]
+    lib.bhd_moe_layer_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, u64, u32, vp, vp, vp, i32]
+    lib.bhd_check_status.argtypes = [vp, vp]
+    lib.bhd_launch_count.restype = u64
+    lib.bhd_launch_count.argtypes = [vp]
+    return lib
+
+
+@dataclass(frozen=True)
+class Weight:
+    """A weight as it sits in host memory: packed bytes plus their meaning
+    (crates/beholdd-backend/src/lib.rs:47-57)."""
+    bytes: np.ndarray
+    kind: int
+    rows: int
+    cols: int
+
+
+class ResidentWeight:
+    """A packed weight in HBM (EncodedWeight/PreparedWeight, execution.rs:1066-1070).
+    `slabs` > 1 holds a 3-D expert tensor; `rows` is per slab."""
+
+    def __init__(self, device: "CudaDevice", handle: int, kind: int, rows: int, cols: int, slabs: int, n_bytes: int,
+                 keepalive=None):
+        self.device, self.handle, self.kind, self.rows, self.cols, self.slabs = device, handle, kind, rows, cols, slabs
+        self.n_bytes = n_bytes
+        self._keepalive = keepalive
+
+    def free(self) -> None:
+        if self.handle:
+            self.device.lib.bhd_weight_free(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _ptr(t):
+    """Device pointer of a torch tensor (or None)."""
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class CudaDevice:
+    """`Device` for one B200. Host-array methods follow the immediate trait; `*_resident`
+    methods take torch CUDA tensors and run asynchronously on torch's current stream."""
+
+    def __init__(self, index: int = 0, lib_path: str | None = None):
+        self.lib = load_library(lib_path)
+        self.index = index
+        h = C.c_void_p()
+        st = self.lib.bhd_ctx_create(index, C.byref(h))
+        if st != OK:
+            raise BackendError(st, f"cuda-b200 backend error: cannot create a context on device {index}: "
+                                   f"{self.lib.bhd_error_text(st).decode()}")
+        self.ctx = h
+
+    # ---- plumbing -------------------------------------------------------------------
+    def close(self) -> None:
+        if getattr(self, "ctx", None):
+            self.lib.bhd_ctx_destroy(self.ctx)
+            self.ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _message(self) -> str:
+        buf = C.create_string_buffer(600)
+        self.lib.bhd_last_error_message(self.ctx, buf, 600)
+        return buf.value.decode(errors="replace")
+
+    def _check(self, st: int) -> None:
+        if st != OK:
+            raise _ERRORS.get(st, BackendError if st == ERR_BACKEND else DeviceError)(st, self._message() or
+                                                                                        self.lib.bhd_error_text(st).decode())
+
+    @staticmethod
+    def _stream():
+        import torch
+
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def check_status(self) -> None:
+        """Synchronise the current stream and raise if a kernel flagged a problem."""
+        self._check(self.lib.bhd_check_status(self.ctx, self._stream()))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.bhd_launch_count(self.ctx))
+
+    # ---- Device ---------------------------------------------------------------------
+    def name(self) -> str:
+        return self.lib.bhd_device_name().decode()
+
+    def supports(self, kind: int) -> bool:
+        return bool(self.lib.bhd_supports(kind))
+
+    def upload_weight(self, weight: Weight, slabs: int = 1) -> ResidentWeight:
+        b = np.ascontiguousarray(weight.bytes, dtype=np.uint8)
+        h = C.c_void_p()
+        self._check(self.lib.bhd_weight_upload(self.ctx, b.ctypes.data_as(C.c_void_p), b.size, weight.kind, weight.rows,
+                                               weight.cols, slabs, C.byref(h)))
+        return ResidentWeight(self, h.value, weight.kind, weight.rows, weight.cols, slabs, b.size)
+
+    def wrap_weight(self, packed, kind: int, rows: int, cols: int, slabs: int = 1) -> ResidentWeight:
+        """Wrap packed bytes that already live in a torch uint8 CUDA tensor (no copy)."""
+        h = C.c_void_p()
+        self._check(self.lib.bhd_weight_wrap_device(self.ctx, _ptr(packed), packed.numel(), kind, rows, cols, slabs,
+                                                    C.byref(h)))
+        return ResidentWeight(self, h.value, kind, rows, cols, slabs, packed.numel(), keepalive=packed)
+
+    def dequantize(self, out: np.ndarray, weight: Weight) -> None:
+        import torch
+
+        w = self.upload_weight(weight)
+        try:
+            if out.size != weight.rows * weight.cols:
+                self._check(self.lib.bhd_dequantize(self.ctx, w.handle, 0, None, out.size, None))
+            o = torch.empty(max(out.size, 1), dtype=torch.float32, device=f"cuda:{self.index}")
+            self._check(self.lib.bhd_dequantize(self.ctx, w.handle, 0, _ptr(o), out.size, self._stream()))
+            out[...] = o[: out.size].cpu().numpy().reshape(out.shape)
+        finally:
+            w.free()
+
+    def _matvec_host(self, y: np.ndarray, x: np.ndarray, weight: Weight, scale: float, accumulate: bool) -> None:
+        assert y.dtype == np.float32 and y.flags.c_contiguous
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.size != weight.cols or y.size != weight.rows:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: weight is {weight.rows}x{weight.cols}, got x={x.size} y={y.size}")
+        w = self.upload_weight(weight)  # the immediate trait borrows host bytes on every call
+        try:
+            self._check(self.lib.bhd_matvec_host(self.ctx, w.handle, 0, x.ctypes.data_as(C.c_void_p),
+                                                 y.ctypes.data_as(C.c_void_p), 1, scale, 1 if accumulate else 0))
+        finally:
+            w.free()
+
+    def matvec(self, y: np.ndarray, x: np.ndarray, w: Weight) -> None:
+        """y[r] = sum_i W[r][i] * x[i], overwriting y (lib.rs:182-183)."""
+        self._matvec_host(y, x, w, 1.0, False)
+
+    def matvec_add(self, y: np.ndarray, x: np.ndarray, w: Weight, scale: float) -> None:
+        """y[r] += (sum_i W[r][i] * x[i]) * scale (lib.rs:189-198)."""
+        self._matvec_host(y, x, w, scale, True)
+
+    def softmax(self, v: np.ndarray) -> None:
+        import torch
+
+        if v.size == 0:
+            raise ShapeError(ERR_SHAPE, "shape mismatch: softmax input cannot be empty")
+        t = torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32)).to(f"cuda:{self.index}")
+        self._check(self.lib.bhd_softmax(self.ctx, _ptr(t), 1, v.size, self._stream()))
+        try:
+            self.check_status()
+        except DeviceError as e:
+            raise ShapeError(ERR_SHAPE, "shape mismatch: " + str(e)) from None
+        v[...] = t.cpu().numpy().reshape(v.shape)
+
+    def swiglu(self, gate: np.ndarray, up: np.ndarray, limit: float) -> None:
+        import torch
+
+        if gate.size != up.size:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: swiglu gate={gate.size} up={up.size}")
+        g = torch.from_numpy(np.ascontiguousarray(gate, dtype=np.float32)).to(f"cuda:{self.index}")
+        u = torch.from_numpy(np.ascontiguousarray(up, dtype=np.float32)).to(f"cuda:{self.index}")
+        self._check(self.lib.bhd_swiglu(self.ctx, _ptr(g), _ptr(u), gate.size, limit, self._stream()))
+        gate[...] = g.cpu().numpy().reshape(gate.shape)
+
+    def add_in_place(self, output: np.ndarray, residual: np.ndarray) -> None:
+        import torch
+
+        if output.size != residual.size:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: add_in_place output={output.size} residual={residual.size}")
+        o = torch.from_numpy(np.ascontiguousarray(output, dtype=np.float32)).to(f"cuda:{self.index}")
+        r = torch.from_numpy(np.ascontiguousarray(residual, dtype=np.float32)).to(f"cuda:{self.index}")
+        self._check(self.lib.bhd_add_in_place(self.ctx, _ptr(o), _ptr(r), output.size, self._stream()))
+        output[...] = o.cpu().numpy().reshape(output.shape)
+
+    # ---- resident operators (torch CUDA tensors, asynchronous) ------------------------
+    def dequantize_resident(self, w: ResidentWeight, out, slab: int = 0) -> None:
+        self._check(self.lib.bhd_dequantize(self.ctx, w.handle, slab, _ptr(out), out.numel(), self._stream()))
+
+    def matvec_resident(self, w: ResidentWeight, x, y, scale: float = 1.0, accumulate: bool = False, slab: int = 0) -> None:
+        """x [batch x cols] (or [cols]), y [batch x rows]: Command::Linear with
+        LinearMode::Overwrite or ScaledAdd (execution.rs:404-425)."""
+        batch = 1 if x.dim() == 1 else x.shape[0]
+        if x.numel() != batch * w.cols or y.numel() != batch * w.rows:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: weight is {w.rows}x{w.cols}, got x={tuple(x.shape)} y={tuple(y.shape)}")
+        self._check(self.lib.bhd_matvec(self.ctx, w.handle, slab, _ptr(x), _ptr(y), batch, scale, 1 if accumulate else 0,
+                                        self._stream()))
+
+    def matvec_host_resident(self, w: ResidentWeight, x: np.ndarray, y: np.ndarray, scale: float = 1.0,
+                             accumulate: bool = False, slab: int = 0) -> None:
+        """Resident weight, host activations: x in, y back, synchronous."""
+        batch = 1 if x.ndim == 1 else x.shape[0]
+        if x.size != batch * w.cols or y.size != batch * w.rows:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: weight is {w.rows}x{w.cols}, got x={x.shape} y={y.shape}")
+        self._check(self.lib.bhd_matvec_host(self.ctx, w.handle, slab, x.ctypes.data_as(C.c_void_p),
+                                             y.ctypes.data_as(C.c_void_p), batch, scale, 1 if accumulate else 0))
+
+    def matmul_resident(self, w: ResidentWeight, x, y, slab: int = 0) -> None:
+        """Prefill: y[m][n] = sum_k x[m][k] * W[n][k]."""
+        m = x.shape[0]
+        if x.numel() != m * w.cols or y.numel() != m * w.rows:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: weight is {w.rows}x{w.cols}, got x={tuple(x.shape)} y={tuple(y.shape)}")
+        self._check(self.lib.bhd_matmul(self.ctx, w.handle, slab, _ptr(x), _ptr(y), m, self._stream()))
+
+    def moe_route(self, router: ResidentWeight, x, top_k: int, experts, weights, counts=None, near=None, probs=None) -> None:
+        T = x.shape[0]
+        self._check(self.lib.bhd_moe_route(self.ctx, router.handle, _ptr(x), T, top_k, _ptr(experts), _ptr(weights),
+                                           _ptr(counts), _ptr(near), _ptr(probs), self._stream()))
+
+    def moe_experts(self, gate: ResidentWeight, up: ResidentWeight, down: ResidentWeight, x, experts, weights, y,
+                    first_expert: int = 0, n_local: int | None = None, accumulate: bool = False) -> None:
+        T, k = experts.shape
+        n_local = gate.slabs if n_local is None else n_local
+        self._check(self.lib.bhd_moe_experts(self.ctx, gate.handle, up.handle, down.handle, _ptr(x), T, k, _ptr(experts),
+                                             _ptr(weights), first_expert, n_local, _ptr(y), 1 if accumulate else 0,
+                                             self._stream()))
+
+    def moe_combine(self, per_route, y, accumulate: bool = False) -> None:
+        """per_route [k, T, dim] (rows pre-scaled by their route weights) summed in route order into y."""
+        k, T, dim = per_route.shape
+        self._check(self.lib.bhd_moe_combine(self.ctx, _ptr(per_route), _ptr(y), T, k, dim, 1 if accumulate else 0,
+                                             self._stream()))
+
+    def moe_layer(self, router: ResidentWeight, gate: ResidentWeight, up: ResidentWeight, down: ResidentWeight, x, y,
+                  top_k: int, experts, weights, counts=None, accumulate: bool = False) -> None:
+        T = x.shape[0]
+        self._check(self.lib.bhd_moe_layer(self.ctx, router.handle, gate.handle, up.handle, down.handle, _ptr(x), _ptr(y),
+                                           T, top_k, _ptr(experts), _ptr(weights), _ptr(counts), 1 if accumulate else 0,
+                                           self._stream()))
+
+    def moe_layer_host(self, router: ResidentWeight, gate: ResidentWeight, up: ResidentWeight, down: ResidentWeight,
+                       x: np.ndarray, y: np.ndarray, top_k: int, experts: np.ndarray | None = None,
+                       weights: np.ndarray | None = None, counts: np.ndarray | None = None, accumulate: bool = False) -> None:
+        T = x.shape[0]
+        p = lambda a: None if a is None else a.ctypes.data_as(C.c_void_p)
+        self._check(self.lib.bhd_moe_layer_host(self.ctx, router.handle, gate.handle, up.handle, down.handle, p(x), p(y), T,
+                                                top_k, p(experts), p(weights), p(counts), 1 if accumulate else 0))

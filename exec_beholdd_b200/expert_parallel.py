@@ -1,0 +1,136 @@
+"""Expert-parallel execution of the routed-expert layer across the GPUs of one node.
+
+The reference is single-process and has no sharding (its routed block is
+crates/beholdd-model/src/qwen3moe/forward.rs:1299-1407); this module adds the one exchange
+step each way that splitting experts across ranks needs:
+
+  * experts e in [r*E/N, (r+1)*E/N) live on rank r; the router weights are replicated;
+  * every rank owns its own positions, routes them locally (bit-exact selection), and
+    sends each route's input row to the rank that holds the selected expert
+    (all-to-all-v "dispatch"), together with the expert id and the route weight;
+  * the expert rank runs gate/up/SiLU/down for the rows it received and returns one output
+    row per route, already scaled by the route weight (all-to-all-v "combine");
+  * the owner adds the returned rows in selection order into a zeroed row, which is the
+    reference's accumulation order, so the result does not depend on N.
+
+Index bookkeeping (sorting routes by destination, split sizes) is done with torch on small
+integer tensors; all arithmetic on activations runs in the CUDA library. The class takes
+the process group and the compute callables as parameters so the exchange logic can be
+tested with gloo on CPU ranks.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def route_plan(experts, n_experts: int, world: int):
+    """For local routes experts[T, k] -> (dest rank per route, stable permutation that sorts
+    routes by destination, per-destination counts). Pure integer work."""
+    import torch
+
+    per = n_experts // world
+    flat = experts.reshape(-1).to(torch.int64)
+    dest = torch.div(flat, per, rounding_mode="floor")
+    order = torch.sort(dest, stable=True).indices
+    counts = torch.bincount(dest, minlength=world)
+    return dest, order, counts
+
+
+class ExpertParallelLayer:
+    """One routed-expert layer with experts split across `world` ranks."""
+
+    def __init__(self, dev, router, gate, up, down, n_experts, dim, ff, top_k, rank=0, world=1, group=None):
+        self.dev, self.router, self.gate, self.up, self.down = dev, router, gate, up, down
+        self.n_experts, self.dim, self.ff, self.top_k = n_experts, dim, ff, top_k
+        self.rank, self.world, self.group = rank, world, group
+        self.per = n_experts // world
+        assert n_experts % world == 0
+        self.last_counts = None
+
+    @classmethod
+    def from_synthetic(cls, dev, seed, n_experts, dim, ff, top_k, rank=0, world=1, group=None):
+        """Seeded weights of the benchmark configuration; this rank uploads only its experts."""
+        from . import synth
+        from .device import Weight
+
+        per = n_experts // world
+        router = synth.router_weights(seed, n_experts, dim)
+        gu_slab, d_slab = synth.packed_bytes(8, ff, dim), synth.packed_bytes(8, dim, ff)
+
+        def local(stream, rows, cols, slab):
+            # Expert slabs are generated per expert so that every rank sees the bytes the
+            # single-GPU run sees for the same expert.
+            parts = [synth.q8_0_matrix(seed, rows, cols, stream=stream * 1000 + e) for e in range(rank * per, (rank + 1) * per)]
+            return np.concatenate(parts)
+
+        return cls(dev, dev.upload_weight(Weight(router.view(np.uint8).reshape(-1), 0, n_experts, dim)),
+                   dev.upload_weight(Weight(local(21, ff, dim, gu_slab), 8, ff, dim), slabs=per),
+                   dev.upload_weight(Weight(local(22, ff, dim, gu_slab), 8, ff, dim), slabs=per),
+                   dev.upload_weight(Weight(local(23, dim, ff, d_slab), 8, dim, ff), slabs=per),
+                   n_experts, dim, ff, top_k, rank, world, group)
+
+    def free(self):
+        for w in (self.router, self.gate, self.up, self.down):
+            w.free()
+
+    # ---- the two device steps, replaceable in CPU tests ------------------------------------
+    def _route(self, x, experts, weights, counts):
+        self.dev.moe_route(self.router, x, self.top_k, experts, weights, counts)
+
+    def _local_experts(self, rows, expert_ids, route_weights, out):
+        """rows [R, dim] each with one (global) expert id and weight -> out[r] = w * down(silu(gate)*up)."""
+        self.dev.moe_experts(self.gate, self.up, self.down, rows, expert_ids.view(-1, 1), route_weights.view(-1, 1), out,
+                             first_expert=self.rank * self.per, n_local=self.per)
+
+    def _combine(self, per_route, y, accumulate):
+        """per_route [k, T, dim] -> y[t] (+)= ((0 + r[0][t]) + r[1][t]) + ... in route order."""
+        self.dev.moe_combine(per_route, y, accumulate)
+
+    # ---- forward ---------------------------------------------------------------------------
+    def forward(self, x, y, accumulate=False):
+        import torch
+
+        T = x.shape[0]
+        experts = torch.empty((T, self.top_k), dtype=torch.int32, device=x.device)
+        weights = torch.empty((T, self.top_k), dtype=torch.float32, device=x.device)
+        counts = torch.empty((self.n_experts,), dtype=torch.int32, device=x.device)
+        if self.world == 1:
+            self.dev.moe_layer(self.router, self.gate, self.up, self.down, x, y, self.top_k, experts, weights, counts,
+                               accumulate=accumulate)
+            self.last_counts = counts
+            return experts, weights
+
+        import torch.distributed as dist
+
+        self._route(x, experts, weights, counts)
+        self.last_counts = counts
+        _, order, send_counts = route_plan(experts, self.n_experts, self.world)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        send_list, recv_list = send_counts.tolist(), recv_counts.tolist()  # one host sync per layer
+        n_recv = int(sum(recv_list))
+
+        token_of_route = torch.div(order, self.top_k, rounding_mode="floor")
+        rows_send = x.index_select(0, token_of_route)                       # dispatch gather
+        # expert id and route weight (as raw bits) travel together, one int32 pair per route
+        meta_send = torch.stack([experts.reshape(-1)[order], weights.reshape(-1)[order].view(torch.int32)],
+                                dim=1).contiguous()
+        rows_recv = torch.empty((n_recv, self.dim), dtype=x.dtype, device=x.device)
+        meta_recv = torch.empty((n_recv, 2), dtype=torch.int32, device=x.device)
+        dist.all_to_all_single(rows_recv, rows_send, recv_list, send_list, group=self.group)
+        dist.all_to_all_single(meta_recv, meta_send, recv_list, send_list, group=self.group)
+
+        out_recv = torch.empty((n_recv, self.dim), dtype=x.dtype, device=x.device)
+        if n_recv:
+            self._local_experts(rows_recv, meta_recv[:, 0].contiguous(), meta_recv[:, 1].contiguous().view(torch.float32),
+                                out_recv)
+        out_back = torch.empty((T * self.top_k, self.dim), dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(out_back, out_recv, send_list, recv_list, group=self.group)
+
+        # Un-permute into route-major [k, T, dim], then add in selection order.
+        j_of_route = order % self.top_k
+        slot = j_of_route * T + token_of_route
+        per_route = torch.empty((self.top_k * T, self.dim), dtype=x.dtype, device=x.device)
+        per_route.index_copy_(0, slot, out_back)
+        self._combine(per_route.view(self.top_k, T, self.dim), y, accumulate)
+        return experts, weights

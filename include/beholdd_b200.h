@@ -1,0 +1,189 @@
+/*
+ * beholdd_b200 -- C ABI of the B200 (sm_100a) implementation of beholdd's quantised-matvec
+ * and qwen3moe routed-expert hot path.
+ *
+ * Conventions (the same ones beholdd's existing native transport uses,
+ * vendor/exec-hag/include/exec_hag.h:13-66): every call returns an int32_t status, 0 on
+ * success and negative on refusal or failure; handles are opaque; buffers are owned by the
+ * caller; calls on one context are serialised by the caller; nothing unwinds across this
+ * boundary. A refused call never touches its outputs and never falls back to another path
+ * (crates/beholdd-backend/src/lib.rs:62-66).
+ *
+ * Pointers named *_dev are device pointers on the context's GPU; pointers named *_host are
+ * host pointers. `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ * Device-pointer calls are asynchronous on `stream`; host-pointer calls synchronise before
+ * they return.
+ *
+ * Paths in comments are relative to the reference repository root.
+ */
+#ifndef BEHOLDD_B200_H
+#define BEHOLDD_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* Status codes. The first four mirror DeviceError (crates/beholdd-backend/src/lib.rs:60-101). */
+#define BHD_OK 0
+#define BHD_ERR_UNSUPPORTED_FORMAT (-1) /* DeviceError::UnsupportedFormat */
+#define BHD_ERR_SHAPE (-2)              /* DeviceError::Shape */
+#define BHD_ERR_ALLOCATION (-3)         /* DeviceError::Allocation */
+#define BHD_ERR_BACKEND (-4)            /* DeviceError::Backend (a CUDA call failed) */
+#define BHD_ERR_INVALID_ARGUMENT (-5)   /* null handle, foreign handle, non-finite scale */
+#define BHD_ERR_DEVICE_STATUS (-6)      /* a kernel reported a problem through its status word */
+
+/* ggml type codes of the weight formats (crates/beholdd-core/src/quant.rs:79-118). */
+#define BHD_TYPE_F32 0u
+#define BHD_TYPE_F16 1u
+#define BHD_TYPE_Q8_0 8u
+#define BHD_TYPE_Q4_K 12u
+#define BHD_TYPE_Q5_K 13u
+#define BHD_TYPE_Q6_K 14u
+
+typedef struct bhd_ctx bhd_ctx;       /* one per GPU; owns the stream-ordered workspace */
+typedef struct bhd_weight bhd_weight; /* a packed weight resident in HBM */
+
+/* Static text for a status code (like exec_hag_error_text). */
+const char* bhd_error_text(int32_t status);
+
+/* Detailed message of the last failed call on this context (DeviceError's Display text).
+ * Copies at most `capacity` bytes including the terminator; returns the full length. */
+int32_t bhd_last_error_message(const bhd_ctx* ctx, char* buffer, int32_t capacity);
+
+/* Device::name (crates/beholdd-backend/src/lib.rs:166). */
+const char* bhd_device_name(void);
+
+/* Create / destroy a context on CUDA device `device`. Replaces constructing the backend
+ * object (Cpu::new, crates/beholdd-backend/src/cpu.rs:46-49; a resident backend is created
+ * like crates/beholdd-backend/src/execution.rs:1143-1154). */
+int32_t bhd_ctx_create(int32_t device, bhd_ctx** out_ctx);
+int32_t bhd_ctx_destroy(bhd_ctx* ctx);
+
+/* Device::supports (crates/beholdd-backend/src/lib.rs:172; cpu.rs:515-517): 1 if the
+ * library decodes this ggml type, else 0. */
+int32_t bhd_supports(uint32_t ggml_type);
+
+/* ExecutionDevice::upload_weight + prepare_weight (crates/beholdd-backend/src/execution.rs:
+ * 1066-1070): validates the exact byte count like Cpu::validate_storage (cpu.rs:55-97) and
+ * copies the packed bytes to HBM unchanged. A weight may hold `n_slabs` equally shaped
+ * matrices back to back (a 3-D expert tensor, crates/beholdd-model/src/qwen3moe/forward.rs:
+ * 1668-1690); `rows` is then the row count of ONE slab. */
+int32_t bhd_weight_upload(bhd_ctx* ctx, const uint8_t* bytes_host, uint64_t n_bytes, uint32_t ggml_type,
+                          uint64_t rows, uint64_t cols, uint64_t n_slabs, bhd_weight** out_weight);
+/* Same, but the packed bytes already sit in device memory owned by the caller, which must
+ * keep them alive and unchanged while the handle exists (no copy is made). */
+int32_t bhd_weight_wrap_device(bhd_ctx* ctx, const void* bytes_dev, uint64_t n_bytes, uint32_t ggml_type,
+                               uint64_t rows, uint64_t cols, uint64_t n_slabs, bhd_weight** out_weight);
+int32_t bhd_weight_free(bhd_weight* weight);
+
+/* Device::dequantize (crates/beholdd-backend/src/lib.rs:179; cpu.rs:99-130): decode slab
+ * `slab` into rows*cols floats. */
+int32_t bhd_dequantize(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, float* out_dev, uint64_t out_len,
+                       void* stream);
+
+/* Device::matvec / Device::matvec_add (crates/beholdd-backend/src/lib.rs:182-198;
+ * cpu.rs:398-507) on resident operands, for `batch` activation vectors at once:
+ *   accumulate == 0:  y[b][r]  = (sum_i W[r][i] * x[b][i]) * scale
+ *   accumulate != 0:  y[b][r] += (sum_i W[r][i] * x[b][i]) * scale
+ * x is [batch x cols], y is [batch x rows], both row-major f32. The reference has no batched
+ * form (it loops matvec per position, forward.rs:1091-1100); batch > 1 reads the weights
+ * once. Device::matvec is scale = 1, accumulate = 0. A non-finite scale is refused
+ * (execution.rs:616-622). cols == 0 gives 0*scale (cpu.rs:439-452). */
+int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_dev, float* y_dev,
+                   uint32_t batch, float scale, int32_t accumulate, void* stream);
+
+/* The same operation through host buffers, the shape of the immediate Device trait whose
+ * slices live in host memory: copies x in, runs, copies y back, synchronises. */
+int32_t bhd_matvec_host(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_host, float* y_host,
+                        uint32_t batch, float scale, int32_t accumulate);
+
+/* Prefill: Y[m][n] = sum_k X[m][k] * W[n][k] for m < M, a loop of Device::matvec over
+ * positions in the reference (crates/beholdd-model/src/qwen3moe/forward.rs:1086-1127). */
+int32_t bhd_matmul(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_dev, float* y_dev,
+                   uint64_t m, void* stream);
+
+/* Device::softmax over `n_rows` rows of `n` floats in place (lib.rs:208; cpu.rs:572-583;
+ * vecops.rs:70-87). NaN input is reported through BHD_ERR_DEVICE_STATUS by
+ * bhd_check_status. */
+int32_t bhd_softmax(bhd_ctx* ctx, float* v_dev, uint64_t n_rows, uint64_t n, void* stream);
+
+/* Device::swiglu: gate[i] = silu(gate[i]) * up[i] with the asymmetric clamp when limit > 0
+ * (lib.rs:258; vecops.rs:101-111). */
+int32_t bhd_swiglu(bhd_ctx* ctx, float* gate_dev, const float* up_dev, uint64_t n, float limit, void* stream);
+
+/* Device::add_in_place: output[i] += residual[i] (lib.rs:255; cpu.rs:839-851). */
+int32_t bhd_add_in_place(bhd_ctx* ctx, float* output_dev, const float* residual_dev, uint64_t n, void* stream);
+
+/* Router half of the routed block (forward.rs:1327-1345 with stable_top_k :1886-1924):
+ * F32 router matvec in the CPU's summation order, softmax, stable top-k with lower-index
+ * tie-break, renormalisation in f64. Outputs (any may be NULL except experts/weights):
+ *   experts_dev  [T x top_k] int32   expert ids in selection order
+ *   weights_dev  [T x top_k] f32     renormalised route weights
+ *   counts_dev   [n_experts] int32   routes per expert
+ *   near_dev     [T x min(8, n_experts - top_k)] int32  ranks top_k.. (near misses)
+ *   probs_dev    [T x n_experts] f32 softmax probabilities
+ * `router` must be an F32 weight [n_experts x dim]. */
+int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const float* x_dev, uint64_t n_positions,
+                      uint32_t top_k, int32_t* experts_dev, float* weights_dev, int32_t* counts_dev,
+                      int32_t* near_dev, float* probs_dev, void* stream);
+
+/* Expert half (forward.rs:1360-1400): for every position and every route in selection
+ * order, gate and up matvec, SiLU gating (vecops.rs:101-111, limit 0), down matvec scaled
+ * by the route weight and added in route order into a zeroed row. gate/up weights hold
+ * n_experts slabs [expert_ff x dim], down holds n_experts slabs [dim x expert_ff], all Q8_0.
+ * Only experts e with first_expert <= e < first_expert + n_local are applied (the others
+ * contribute nothing), which is what one rank of an expert-parallel group computes; the
+ * slabs of `gate/up/down` are then the local experts only. With first_expert = 0 and
+ * n_local = n_experts this is the whole layer.
+ *   accumulate == 0: y[t] = out[t];  accumulate != 0: y[t] += out[t]  (forward.rs:1405-1407) */
+int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps,
+                        const bhd_weight* down_exps, const float* x_dev, uint64_t n_positions, uint32_t top_k,
+                        const int32_t* experts_dev, const float* weights_dev, uint32_t first_expert,
+                        uint32_t n_local, float* y_dev, int32_t accumulate, void* stream);
+
+/* Weighted combine of per-route outputs (forward.rs:1385-1398; cpu.rs:280-284): per_route is
+ * [top_k][T][dim], each row already scaled by its route weight; for every position the rows
+ * are added in selection order into a zero accumulator, ((0 + r0) + r1) + ..., then stored
+ * (accumulate == 0) or added to y (accumulate != 0). This is the owner-side half of the
+ * expert-parallel layer, where the rows come back from the ranks that hold the experts. */
+int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, float* y_dev, uint64_t n_positions, uint32_t top_k,
+                        uint64_t dim, int32_t accumulate, void* stream);
+
+/* The whole routed feed-forward of one layer (forward.rs:1299-1407): bhd_moe_route then
+ * bhd_moe_experts over all experts. The operator shape follows the reference's only
+ * resident routed-MoE entry point, VulkanDevice::routed_moe_bf16 / RoutedMoeProgram::
+ * execute_batch (crates/beholdd-backend/src/vulkan.rs:1792-1799, 2699-2706), with Q8_0
+ * experts and routing done on the device. */
+int32_t bhd_moe_layer(bhd_ctx* ctx, const bhd_weight* router, const bhd_weight* gate_exps, const bhd_weight* up_exps,
+                      const bhd_weight* down_exps, const float* x_dev, float* y_dev, uint64_t n_positions,
+                      uint32_t top_k, int32_t* experts_dev, float* weights_dev, int32_t* counts_dev,
+                      int32_t accumulate, void* stream);
+
+/* The routed layer through host buffers: x [T x dim] in, y [T x dim] (+ routing) out. */
+int32_t bhd_moe_layer_host(bhd_ctx* ctx, const bhd_weight* router, const bhd_weight* gate_exps,
+                           const bhd_weight* up_exps, const bhd_weight* down_exps, const float* x_host,
+                           float* y_host, uint64_t n_positions, uint32_t top_k, int32_t* experts_host,
+                           float* weights_host, int32_t* counts_host, int32_t accumulate);
+
+/* Synchronise `stream` and read the context's device status word: BHD_OK, or
+ * BHD_ERR_DEVICE_STATUS with the detail in bhd_last_error_message (NaN fed to softmax,
+ * an out-of-range expert id, a bounded wait that gave up). Clears the word. */
+int32_t bhd_check_status(bhd_ctx* ctx, void* stream);
+
+/* How many kernels this library has launched on the context since it was created. */
+uint64_t bhd_launch_count(const bhd_ctx* ctx);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BEHOLDD_B200_H */
