@@ -137,7 +137,9 @@ int32_t bhd_ctx_create(int32_t device, bhd_ctx** out_ctx) {
     }
     if (cudaMalloc(reinterpret_cast<void**>(&c->status_dev), 256) != cudaSuccess ||
         cudaMemset(c->status_dev, 0, 256) != cudaSuccess ||
-        cudaMallocHost(reinterpret_cast<void**>(&c->status_host), 256) != cudaSuccess) {
+        cudaMallocHost(reinterpret_cast<void**>(&c->status_host), 256) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&c->counters), 65536 * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(c->counters, 0, 65536 * sizeof(uint32_t)) != cudaSuccess) {
         cudaGetLastError();
         delete c;
         return BHD_ERR_ALLOCATION;
@@ -160,6 +162,7 @@ int32_t bhd_ctx_destroy(bhd_ctx* ctx) {
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
@@ -404,11 +407,12 @@ int32_t bhd_check_status(bhd_ctx* ctx, void* stream) {
     BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the status word");
     const uint32_t bits = ctx->status_host[0];
     if (bits == 0) return BHD_OK;
-    return bhd_fail(ctx, BHD_ERR_DEVICE_STATUS, "device status 0x%x:%s%s%s%s", bits,
+    return bhd_fail(ctx, BHD_ERR_DEVICE_STATUS, "device status 0x%x:%s%s%s%s%s", bits,
                     (bits & BHD_DEV_NAN_IN_SOFTMAX) ? " softmax input cannot contain NaN;" : "",
                     (bits & BHD_DEV_BAD_EXPERT_ID) ? " expert id out of range;" : "",
                     (bits & BHD_DEV_WAIT_TIMEOUT) ? " a bounded wait gave up;" : "",
-                    (bits & BHD_DEV_BAD_ROUTE_PROB) ? " router probabilities not finite, non-negative with a positive sum;" : "");
+                    (bits & BHD_DEV_BAD_ROUTE_PROB) ? " router probabilities not finite, non-negative with a positive sum;" : "",
+                    (bits & BHD_DEV_ACTIVATION_RANGE) ? " an activation is NaN or beyond the fp16 range (|x| > 65504);" : "");
 }
 
 uint64_t bhd_launch_count(const bhd_ctx* ctx) { return valid_ctx(ctx) ? ctx->launches : 0; }

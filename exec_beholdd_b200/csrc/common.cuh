@@ -18,6 +18,7 @@
 #define BHD_DEV_BAD_EXPERT_ID 2u
 #define BHD_DEV_WAIT_TIMEOUT 4u
 #define BHD_DEV_BAD_ROUTE_PROB 8u
+#define BHD_DEV_ACTIVATION_RANGE 16u
 
 struct bhd_ctx {
     uint32_t magic;
@@ -28,6 +29,7 @@ struct bhd_ctx {
     size_t workspace_bytes;
     uint32_t* status_dev;   // device status word (+ spare words)
     uint32_t* status_host;  // pinned mirror
+    uint32_t* counters;     // 65536 tile counters of the split-column reduction; zero between launches
     float* stage_x;         // device staging for the host-buffer entry points
     float* stage_y;
     size_t stage_x_bytes, stage_y_bytes;
