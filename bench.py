@@ -184,9 +184,17 @@ def run_reference_arm(args):
 # GPU arm
 # ------------------------------------------------------------------------------------------
 
-def time_region(torch, fn, steps, warmup, barrier=None):
+def time_region(torch, fn, steps, warmup, barrier=None, graph=True):
     """W untimed steps, then K steps bracketed by synchronise (+ barrier) on both sides, timed
-    with CUDA events on the launching stream."""
+    with CUDA events on the launching stream. The step is captured once into a CUDA graph and
+    replayed, so the host's per-call cost does not pace a launch-bound sequence of kernels."""
+    fn()  # first call sizes the workspace and sets kernel attributes (not capturable)
+    torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -228,9 +236,10 @@ def bench_matvec(dev, torch, kind, batch, steps, warmup, barrier=None, copies=No
             dev.matvec_resident(w, x, y)
 
     l0 = dev.launch_count
+    step()
+    per_step_launches = dev.launch_count - l0   # counted on an eager step; the timed steps replay the same launches
     secs = time_region(torch, step, steps, warmup, barrier)
-    launches = dev.launch_count - l0 - 0
-    per_step_launches = (dev.launch_count - l0) // (steps + 0) if steps else 0
+    launches = per_step_launches * steps
     bytes_per_step = copies * algorithmic_bytes(kind, ROWS, COLS, batch)
     res = {"gbs": bytes_per_step * steps / secs / 1e9, "ms_per_step": secs / steps * 1e3, "copies": copies,
            "us_per_matvec": secs / steps / copies * 1e6, "bytes_per_matvec": algorithmic_bytes(kind, ROWS, COLS, batch),
@@ -282,7 +291,7 @@ def bench_moe(dev, torch, T, steps, warmup, rank=0, world=1, barrier=None):
     def step():
         layer.forward(x, y)
 
-    secs = time_region(torch, step, steps, warmup, barrier)
+    secs = time_region(torch, step, steps, warmup, barrier, graph=(world == 1))
     dev.check_status()
     counts = layer.last_counts.cpu().numpy()
     touched = int((counts > 0).sum())
