@@ -15,6 +15,9 @@
 int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                uint64_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
 void bhd_weight_build_tensor_map(bhd_ctx* ctx, bhd_weight* w);
+void bhd_weight_build_tensor_map16(bhd_ctx* ctx, bhd_weight* w);
+int32_t bhd_launch_matvec_decode(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
+                                 uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
 
 int32_t bhd_fail(bhd_ctx* ctx, int32_t status, const char* fmt, ...) {
     if (ctx) {
@@ -252,6 +255,7 @@ static int32_t make_weight(bhd_ctx* ctx, const void* src, bool src_is_device, ui
         }
     }
     bhd_weight_build_tensor_map(ctx, w);
+    bhd_weight_build_tensor_map16(ctx, w);
     *out = w;
     return BHD_OK;
 }
@@ -311,6 +315,10 @@ int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float
     if (batch == 0 || w->rows == 0) return BHD_OK;
     cudaStream_t s = cudaStream_t(stream);
     bool handled = false;
+    if (batch <= 4) {
+        const int32_t ds = bhd_launch_matvec_decode(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s, &handled);
+        if (ds != BHD_OK || handled) return ds;
+    }
     const int32_t fs = bhd_launch_matvec_fast(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s, &handled);
     if (fs != BHD_OK || handled) return fs;
     return bhd_launch_matvec_general(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s);

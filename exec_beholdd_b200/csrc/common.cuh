@@ -53,6 +53,8 @@ struct bhd_weight {
     alignas(64) unsigned char tmap[128];
     bool tmap_ok;
     uint32_t tmap_box_rows, tmap_box_bytes;
+    alignas(64) unsigned char tmap16[128];  // same view with a 16-row box (decode kernel)
+    bool tmap16_ok;
 };
 
 int32_t bhd_fail(bhd_ctx* ctx, int32_t status, const char* fmt, ...);
