@@ -104,8 +104,32 @@ __device__ __forceinline__ void mma_new(float (&c)[4], uint32_t a0, uint32_t a1,
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "f"(0.0f));
 }
-__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
-__device__ __forceinline__ uint2 lds64(const uint8_t* p) { return *reinterpret_cast<const uint2*>(p); }
+// Shared-memory loads by 32-bit shared address: keeps all address arithmetic in 32 bits.
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ float h2f(uint32_t h) { return __half2float(__ushort_as_half(uint16_t(h))); }
 // Small unsigned integer (< 2^23) in the low bits of v -> float, without the conversion pipe.
 __device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.0f; }
@@ -192,9 +216,11 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     __shared__ uint64_t bars[WARPS][RING];
     __shared__ float red[WARPS][ROWS][NB];
+    __shared__ __align__(16) uint8_t zero_area[STEPS * NB * 64 + 64];  // what inactive lanes feed the MMA
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t tile = blockIdx.x;
+    for (int i = threadIdx.x; i < int(sizeof(zero_area) / 4); i += blockDim.x) reinterpret_cast<uint32_t*>(zero_area)[i] = 0u;
     if (lane == 0) {
         for (int i = 0; i < RING; ++i) mbar_init(&bars[warp][i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -202,6 +228,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
     __syncthreads();
 
     uint8_t* ring = smem + warp * (RING * STAGE);
+    const uint32_t ring32 = smem_u32(ring);
+    const uint32_t zeros32 = smem_u32(zero_area);
     const uint32_t my_chunks = p.chunks > uint32_t(warp) ? (p.chunks - warp + WARPS - 1) / WARPS : 0;
     auto issue = [&](uint32_t i) {  // lane 0 only: stage the warp's i-th chunk
         const uint32_t chunk = warp + i * WARPS, slot = i % RING;
@@ -226,19 +254,16 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
             if (lane == 0) atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT);
             break;
         }
-        const uint8_t* st = ring + slot * STAGE;
-        const uint8_t* w0 = st + r0 * BOX;
-        const uint8_t* w1 = st + r1 * BOX;
-        const uint8_t* xb = st + W_BYTES;
-        const uint8_t* zero = xb + FRAG + GROUPS * NB * 4;  // 64 zero bytes
-        const float* sums = reinterpret_cast<const float*>(xb + FRAG);
-        // B fragment of step s: real data for the lanes whose column belongs to the step's
-        // group, zeros for the others.
-        auto bfrag = [&](int s) -> uint2 {
-            const int grp = step_group(KIND, s);
-            const uint8_t* src = (grp % GPT == bgl) ? xb + s * (64 * NB) + boff : zero + t * 8;
-            return lds64(src);
-        };
+        const uint32_t st = ring32 + slot * STAGE;
+        const uint32_t w0 = st + r0 * BOX, w1 = st + r1 * BOX;
+        const uint32_t xb = st + W_BYTES;
+        const uint32_t sums = xb + FRAG + 4 * v;  // + 4 * NB * group
+        // Where this lane reads its B fragments: the staged activations when the step's group
+        // is the one its column stands for, an all-zero area otherwise. Steps add a constant.
+        uint32_t bsrc[GPT];
+#pragma unroll
+        for (int c = 0; c < GPT; ++c) bsrc[c] = (c == bgl) ? xb + boff : zeros32;
+        auto bfrag = [&](int s) -> uint2 { return lds64(bsrc[step_group(KIND, s) % GPT] + s * (64 * NB)); };
         float acc[TILES][4];
 
         if constexpr (KIND == BHD_TYPE_Q8_0) {
@@ -267,9 +292,9 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
 #pragma unroll
             for (int tl = 0; tl < TILES; ++tl) {
                 const int blk = tl * GPT + gl;  // the block whose sums sit in this lane's columns
-                const float d0 = h2f(*reinterpret_cast<const uint16_t*>(w0 + 34 * blk));
-                const float d1 = h2f(*reinterpret_cast<const uint16_t*>(w1 + 34 * blk));
-                const float sx = sums[blk * NB + v];
+                const float d0 = h2f(lds16(w0 + 34 * blk));
+                const float d1 = h2f(lds16(w1 + 34 * blk));
+                const float sx = ldsf(sums + 4 * NB * blk);
                 tot0 = fmaf(d0, fmaf(-1152.f, sx, acc[tl][0] + acc[tl][1]), tot0);
                 tot1 = fmaf(d1, fmaf(-1152.f, sx, acc[tl][2] + acc[tl][3]), tot1);
             }
@@ -299,8 +324,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
                 }
             }
             // Scales and mins of the sub-blocks this lane owns: j = tl * GPT + gl.
-            const uint4 h0 = *reinterpret_cast<const uint4*>(w0);
-            const uint4 h1 = *reinterpret_cast<const uint4*>(w1);
+            const uint4 h0 = lds128(w0);
+            const uint4 h1 = lds128(w1);
             const float d0 = h2f(h0.x & 0xffffu), m0 = h2f(h0.x >> 16), d1 = h2f(h1.x & 0xffffu), m1 = h2f(h1.x >> 16);
             // Packed 6-bit fields (crates/beholdd-kernel/src/kquant.rs:176-185), four per word:
             // scales 0-3, mins 0-3, scales 4-7, mins 4-7.
@@ -322,16 +347,16 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
                 const float sc1 = u2f((f1[2 * hi4] >> sh) & 0xffu), mn1 = u2f((f1[2 * hi4 + 1] >> sh) & 0xffu);
                 const float off = (j & 1) ? 64.f : 1024.f;
                 const float ds0 = d0 * sc0, ds1 = d1 * sc1;
-                const float sx = sums[j * NB + v];
+                const float sx = ldsf(sums + 4 * NB * j);
                 tot0 += fmaf(ds0, acc[tl][0] + acc[tl][1], -fmaf(ds0, off, m0 * mn0) * sx);
                 tot1 += fmaf(ds1, acc[tl][2] + acc[tl][3], -fmaf(ds1, off, m1 * mn1) * sx);
             }
         } else {  // Q6_K
             const uint32_t q6_off = (210u * chunk) & 15u;  // where the superblock starts in the staged window
             const uint32_t shb = 8u * (q6_off & 3u);
-            const uint8_t* b0 = w0 + (q6_off & ~3u);
-            const uint8_t* b1 = w1 + (q6_off & ~3u);
-            auto word = [&](const uint8_t* base, int byte_off) -> uint32_t {
+            const uint32_t b0 = w0 + (q6_off & ~3u);
+            const uint32_t b1 = w1 + (q6_off & ~3u);
+            auto word = [&](uint32_t base, int byte_off) -> uint32_t {
                 return __funnelshift_r(lds32(base + byte_off), lds32(base + byte_off + 4), shb);
             };
             // The loop below follows the packed planes, not the tile order, so tiles start at zero.
@@ -364,7 +389,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
                 const uint32_t sw0 = word(b0, 192 + (s & ~3)), sw1 = word(b1, 192 + (s & ~3));
                 const float s0 = d0 * float(int8_t((sw0 >> (8 * (s & 3))) & 0xffu));
                 const float s1 = d1 * float(int8_t((sw1 >> (8 * (s & 3))) & 0xffu));
-                const float sx = sums[s * NB + v];
+                const float sx = ldsf(sums + 4 * NB * s);
                 tot0 = fmaf(s0, fmaf(-1056.f, sx, acc[tl][0] + acc[tl][1]), tot0);  // codes carry 1024 + c; value is c - 32
                 tot1 = fmaf(s1, fmaf(-1056.f, sx, acc[tl][2] + acc[tl][3]), tot1);
             }

@@ -109,21 +109,26 @@ __device__ __forceinline__ uint2 lds64(const uint8_t* p) { return *reinterpret_c
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2float(__ushort_as_half(uint16_t(h))); }
 
 // ---- activation packer ------------------------------------------------------------------
-// x [batch x K] f32 (row b at x + rowidx[b]*ldx when rowidx is given) -> per chunk a blob of
-// MMA B-fragments: column n of n-tile j is activation vector b = 4j + n/2, its fp16 high part
-// (n even) or the fp16 remainder (n odd). Columns past `batch` and k past K are zero.
-__global__ void k_pack_x(uint32_t kind, const float* __restrict__ x, const int32_t* __restrict__ rowidx, uint64_t ldx,
-                         uint32_t batch, uint32_t K, int nt, uint8_t* __restrict__ blob, uint32_t* __restrict__ status) {
-    __shared__ float stepsum[STEPS][8];
-    const int chunk = blockIdx.x, j = blockIdx.y;
+// Builds, for one 256-column chunk and one n-tile j, the MMA B-fragments of up to 8 columns.
+// Split mode: column n is activation vector 4j + n/2, its fp16 high part (n even) or the fp16
+// remainder (n odd), so x = hi + lo to 2^-22. Plain mode: column n is vector 8j + n rounded to
+// fp16. `row` is this lane's source row (nullptr: the column is padding and packs as zero);
+// with `row2` the value packed is silu(row[i]) * row2[i] (crates/beholdd-kernel/src/vecops.rs:
+// 91-111, limit 0). Must be called by all 512 threads of the CTA (16 steps x 32 lanes).
+__device__ __forceinline__ void pack_tile(uint32_t kind, const float* row, const float* row2, bool lo_part, uint32_t chunk,
+                                          uint32_t K, int nt, int j, uint8_t* cb, float (*stepsum)[8], uint32_t* status) {
     const int s = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t b = 4 * j + (g >> 1);
-    const bool lo_part = g & 1;
-    const uint32_t k4 = uint32_t(chunk) * CHUNK_K + chunk_k4(kind, s, t);
+    const uint32_t k4 = chunk * CHUNK_K + chunk_k4(kind, s, t);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (b < batch && k4 < K) {
-        const uint64_t row = rowidx ? uint64_t(rowidx[b]) : uint64_t(b);
-        v = *reinterpret_cast<const float4*>(x + row * ldx + k4);
+    if (row && k4 < K) {
+        v = *reinterpret_cast<const float4*>(row + k4);
+        if (row2) {
+            const float4 u = *reinterpret_cast<const float4*>(row2 + k4);
+            v.x = __fmul_rn(__fdiv_rn(v.x, __fadd_rn(1.0f, expf(-v.x))), u.x);
+            v.y = __fmul_rn(__fdiv_rn(v.y, __fadd_rn(1.0f, expf(-v.y))), u.y);
+            v.z = __fmul_rn(__fdiv_rn(v.z, __fadd_rn(1.0f, expf(-v.z))), u.z);
+            v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.0f, expf(-v.w))), u.w);
+        }
     }
     float e[4] = {v.x, v.y, v.z, v.w};
     uint32_t hbits[4];
@@ -143,20 +148,30 @@ __global__ void k_pack_x(uint32_t kind, const float* __restrict__ x, const int32
     uint2 frag;
     if (kind == BHD_TYPE_Q4_K) frag = make_uint2(hbits[0] | (hbits[2] << 16), hbits[1] | (hbits[3] << 16));
     else frag = make_uint2(hbits[0] | (hbits[1] << 16), hbits[2] | (hbits[3] << 16));
-    uint8_t* cb = blob + uint64_t(chunk) * xblob_bytes(kind, nt);
     *reinterpret_cast<uint2*>(cb + (s * nt + j) * 256 + lane * 8) = frag;
     float sum = (part[0] + part[1]) + (part[2] + part[3]);
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    __syncthreads();  // stepsum may still be read for the previous n-tile
     if (t == 0) stepsum[s][g] = sum;
     __syncthreads();
     const int groups = groups_of(kind), per = STEPS / groups;
-    if (threadIdx.x < groups * 8) {
+    if (int(threadIdx.x) < groups * 8) {
         const int grp = threadIdx.x >> 3, n = threadIdx.x & 7;
         float acc = 0.f;
         for (int i = 0; i < per; ++i) acc += stepsum[grp * per + i][n];
         reinterpret_cast<float*>(cb + STEPS * nt * 256)[(grp * nt + j) * 8 + n] = acc;
     }
+}
+
+// x [batch x K] f32 -> one blob per chunk, split mode. grid (chunks, nt), 512 threads.
+__global__ void k_pack_x(uint32_t kind, const float* __restrict__ x, uint64_t ldx, uint32_t batch, uint32_t K, int nt,
+                         uint8_t* __restrict__ blob, uint32_t* __restrict__ status) {
+    __shared__ float stepsum[STEPS][8];
+    const int j = blockIdx.y, g = (threadIdx.x & 31) >> 2;
+    const uint32_t b = 4 * j + (g >> 1);
+    pack_tile(kind, b < batch ? x + uint64_t(b) * ldx : nullptr, nullptr, g & 1, blockIdx.x, K, nt, j,
+              blob + uint64_t(blockIdx.x) * xblob_bytes(kind, nt), stepsum, status);
 }
 
 // ---- main kernel ------------------------------------------------------------------------------
@@ -175,6 +190,7 @@ struct MatvecParams {
     uint32_t per_cta;       // stages per CTA
     float scale;
     int accumulate;
+    const float* vec_scale; // optional per-vector factor (replaces `scale`)
 };
 
 template <uint32_t KIND, int NT>
@@ -343,9 +359,12 @@ __device__ __forceinline__ void consume_stage(const uint8_t* __restrict__ wrow0,
     }
 }
 
-template <uint32_t KIND, int NT>
-__global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ CUtensorMap tmap, const MatvecParams p,
-                                                        int n_stages_ring) {
+// The body shared by the plain and the grouped kernel: CTA `cta_index` streams stages
+// [cta_index * per_cta, +per_cta) of the (row tile, chunk) sequence described by p.
+// SPLIT says what the 8 columns of an n-tile are (see pack_tile).
+template <uint32_t KIND, int NT, bool SPLIT>
+__device__ __forceinline__ void run_stage_range(const CUtensorMap* tmap_ptr, const MatvecParams& p, uint32_t cta_index,
+                                                int n_stages_ring) {
     using S = Smem<KIND, NT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // TMA destinations need 128-byte alignment
@@ -353,7 +372,7 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t s_begin = blockIdx.x * p.per_cta;
+    const uint32_t s_begin = cta_index * p.per_cta;
     const uint32_t s_end = min(s_begin + p.per_cta, p.total_stages);
     if (s_begin >= s_end) return;
 
@@ -382,7 +401,7 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
                 mbar_arrive_expect_tx(&full_bar[slot], S::W_BYTES + S::X_BYTES);
                 // Inner coordinate in 2-byte elements; its byte offset is a multiple of 16.
                 const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : Fmt<KIND>::CHUNK_BYTES * chunk;
-                tma_load_2d(dst, &tmap, int(byte0 >> 1), int(p.row_base + tile * TILE_ROWS), &full_bar[slot]);
+                tma_load_2d(dst, tmap_ptr, int(byte0 >> 1), int(p.row_base + tile * TILE_ROWS), &full_bar[slot]);
                 bulk_load_1d(dst + S::X_OFF, p.xblob + uint64_t(chunk) * S::X_BYTES, S::X_BYTES, &full_bar[slot]);
             }
         }
@@ -423,7 +442,7 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
             const uint32_t first_cta = (tile * p.chunks) / p.per_cta;
             const uint32_t last_cta = (tile * p.chunks + p.chunks - 1) / p.per_cta;
             const uint32_t nseg = last_cta - first_cta + 1;
-            float* mine = p.partial + (uint64_t(tile + blockIdx.x) * CONSUMER_WARPS + warp) * (NT * 4 * 32);
+            float* mine = p.partial + (uint64_t(tile + cta_index) * CONSUMER_WARPS + warp) * (NT * 4 * 32);
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -449,19 +468,27 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
             }
         }
         if (write_out) {
+            auto store = [&](uint32_t b, float va, float vb) {
+                if (b >= p.batch) return;
+                const float sc = p.vec_scale ? p.vec_scale[b] : p.scale;
+                va = __fmul_rn(va, sc);
+                vb = __fmul_rn(vb, sc);
+                if (row_a < p.rows) {
+                    float* o = p.y + uint64_t(b) * p.rows + row_a;
+                    *o = p.accumulate ? __fadd_rn(*o, va) : va;
+                }
+                if (row_b < p.rows) {
+                    float* o = p.y + uint64_t(b) * p.rows + row_b;
+                    *o = p.accumulate ? __fadd_rn(*o, vb) : vb;
+                }
+            };
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const uint32_t b = 4 * j + t;  // this lane's activation vector; columns 2t (hi) and 2t+1 (lo)
-                if (b < p.batch) {
-                    const float va = __fmul_rn(tot[j][0] + tot[j][1], p.scale), vb = __fmul_rn(tot[j][2] + tot[j][3], p.scale);
-                    if (row_a < p.rows) {
-                        float* o = p.y + uint64_t(b) * p.rows + row_a;
-                        *o = p.accumulate ? __fadd_rn(*o, va) : va;
-                    }
-                    if (row_b < p.rows) {
-                        float* o = p.y + uint64_t(b) * p.rows + row_b;
-                        *o = p.accumulate ? __fadd_rn(*o, vb) : vb;
-                    }
+                if (SPLIT) {  // columns 2t (hi) and 2t+1 (lo) of vector 4j + t
+                    store(4 * j + t, tot[j][0] + tot[j][1], tot[j][2] + tot[j][3]);
+                } else {      // columns 2t and 2t+1 are vectors 8j + 2t and 8j + 2t + 1
+                    store(8 * j + 2 * t, tot[j][0], tot[j][2]);
+                    store(8 * j + 2 * t + 1, tot[j][1], tot[j][3]);
                 }
             }
         }
@@ -469,6 +496,178 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
         for (int j = 0; j < NT; ++j) tot[j][0] = tot[j][1] = tot[j][2] = tot[j][3] = 0.f;
         seg_first_chunk = 0;
     }
+}
+
+template <uint32_t KIND, int NT>
+__global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ CUtensorMap tmap, const MatvecParams p,
+                                                        int n_stages_ring) {
+    run_stage_range<KIND, NT, true>(&tmap, p, blockIdx.x, n_stages_ring);
+}
+
+// ---- grouped experts (qwen3moe routed block) ---------------------------------------------------
+// Routes are sorted by expert; every expert's routes are cut into groups of up to 32 vectors and
+// each (group, 64-row tile) of an expert matrix is one CTA streaming all columns. Group sizes
+// pick the column layout: up to 8 vectors use split (hi + lo) activations, larger groups use
+// plain fp16 activations with 8 vectors per n-tile.
+
+struct MoeGroup {
+    int32_t expert_local, slot0, nb, cls;
+    uint32_t blob_x, blob_a;  // offsets of the packed inputs of gate/up and of down, in 256-byte units
+    uint32_t pad0, pad1;
+};
+struct MoeHeader {
+    uint32_t gcount[4];
+    uint32_t total_groups, local_routes, pad0, pad1;
+};
+__host__ __device__ constexpr int moe_nt(int cls) { return cls == 0 ? 1 : (cls == 3 ? 4 : 2); }
+__host__ __device__ constexpr bool moe_split(int cls) { return cls < 2; }
+__host__ __device__ constexpr int moe_cls(int nb) { return nb <= 4 ? 0 : (nb <= 8 ? 1 : (nb <= 16 ? 2 : 3)); }
+
+// One CTA. Sorts the local routes by (expert, route index) -- a stable counting sort through a
+// route bitmap per expert, so the order is deterministic -- and lists the groups.
+__global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ experts, const float* __restrict__ weights,
+                                                   uint32_t n_routes, uint32_t first_expert, uint32_t n_local,
+                                                   uint32_t chunks_x, uint32_t chunks_a, MoeHeader* hdr,
+                                                   uint32_t* counts, uint32_t* offsets, int32_t* route_slot,
+                                                   int32_t* slot_route, float* slot_weight, MoeGroup* groups,
+                                                   int32_t* glist, uint32_t gmax, uint32_t* bitmap, uint32_t* prefix,
+                                                   uint32_t* status) {
+    const uint32_t words = (n_routes + 31) / 32;
+    for (uint32_t i = threadIdx.x; i < n_local * words; i += blockDim.x) bitmap[i] = 0u;
+    __syncthreads();
+    for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
+        const int32_t e = experts[r];
+        if (e < 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+        if (e >= int32_t(first_expert) && uint32_t(e) < first_expert + n_local)
+            atomicOr(&bitmap[(uint32_t(e) - first_expert) * words + (r >> 5)], 1u << (r & 31));
+        else
+            route_slot[r] = -1;
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < n_local; e += blockDim.x) {
+        uint32_t run = 0;
+        for (uint32_t w = 0; w < words; ++w) {
+            prefix[e * words + w] = run;
+            run += __popc(bitmap[e * words + w]);
+        }
+        counts[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t off = 0, ng = 0, bx = 0, ba = 0, gc[4] = {0, 0, 0, 0};
+        for (uint32_t e = 0; e < n_local; ++e) {
+            offsets[e] = off;
+            uint32_t n = counts[e], s0 = off;
+            off += n;
+            while (n > 0 && ng < gmax) {
+                const uint32_t nb = n < 32 ? n : 32;
+                const int cls = moe_cls(int(nb));
+                MoeGroup g;
+                g.expert_local = int32_t(e); g.slot0 = int32_t(s0); g.nb = int32_t(nb); g.cls = cls;
+                g.blob_x = bx; g.blob_a = ba; g.pad0 = g.pad1 = 0;
+                bx += chunks_x * uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls)) / 256);
+                ba += chunks_a * uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls)) / 256);
+                glist[cls * gmax + gc[cls]++] = int32_t(ng);
+                groups[ng++] = g;
+                s0 += nb;
+                n -= nb;
+            }
+        }
+        offsets[n_local] = off;
+        for (int c = 0; c < 4; ++c) hdr->gcount[c] = gc[c];
+        hdr->total_groups = ng;
+        hdr->local_routes = off;
+    }
+    __syncthreads();
+    for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
+        const int32_t e = experts[r];
+        if (e >= int32_t(first_expert) && uint32_t(e) < first_expert + n_local) {
+            const uint32_t el = uint32_t(e) - first_expert, w = r >> 5;
+            const uint32_t rank = prefix[el * words + w] + __popc(bitmap[el * words + w] & ((1u << (r & 31)) - 1u));
+            const uint32_t slot = offsets[el] + rank;
+            route_slot[r] = int32_t(slot);
+            slot_route[slot] = int32_t(r);
+            slot_weight[slot] = weights[r];
+        }
+    }
+}
+
+// Packs the inputs of every group. mode 0: rows of x gathered by position (the token-to-expert
+// gather); mode 1: silu(gate) * up of the group's slots. grid (chunks, max groups), 512 threads.
+__global__ void k_moe_pack(int mode, const MoeHeader* __restrict__ hdr, const MoeGroup* __restrict__ groups,
+                           const int32_t* __restrict__ slot_route, uint32_t top_k, const float* __restrict__ src,
+                           const float* __restrict__ src2, uint32_t K, uint8_t* __restrict__ blob,
+                           uint32_t* __restrict__ status) {
+    __shared__ float stepsum[STEPS][8];
+    if (blockIdx.y >= hdr->total_groups) return;
+    const MoeGroup g = groups[blockIdx.y];
+    const int nt = moe_nt(g.cls);
+    const bool split = moe_split(g.cls);
+    const int col = (threadIdx.x & 31) >> 2;
+    uint8_t* cb = blob + uint64_t(mode ? g.blob_a : g.blob_x) * 256 + uint64_t(blockIdx.x) * xblob_bytes(BHD_TYPE_Q8_0, nt);
+    for (int j = 0; j < nt; ++j) {
+        const int b = split ? 4 * j + (col >> 1) : 8 * j + col;
+        const float* row = nullptr;
+        const float* row2 = nullptr;
+        if (b < g.nb) {
+            const uint32_t slot = uint32_t(g.slot0 + b);
+            if (mode == 0) row = src + uint64_t(uint32_t(slot_route[slot]) / top_k) * K;
+            else { row = src + uint64_t(slot) * K; row2 = src2 + uint64_t(slot) * K; }
+        }
+        pack_tile(BHD_TYPE_Q8_0, row, row2, split && (col & 1), blockIdx.x, K, nt, j, cb, stepsum, status);
+    }
+}
+
+struct MoeRun {
+    const MoeHeader* hdr;
+    const MoeGroup* groups;
+    const int32_t* glist;      // the class's group indices
+    const uint8_t* blob;
+    float* out0;               // [slot][rows] of matrix 0 (gate, or down)
+    float* out1;               // [slot][rows] of matrix 1 (up)
+    const float* slot_weight;  // down only: route weight per slot
+    uint32_t* status;
+    uint32_t rows, chunks;
+    int use_blob_a;
+};
+
+template <int CLS>
+__global__ void __launch_bounds__(THREADS) k_moe_grouped(const __grid_constant__ CUtensorMap tmap0,
+                                                         const __grid_constant__ CUtensorMap tmap1, const MoeRun r,
+                                                         int n_stages_ring) {
+    if (blockIdx.y >= r.hdr->gcount[CLS]) return;
+    const MoeGroup g = r.groups[r.glist[blockIdx.y]];
+    MatvecParams p;
+    p.xblob = r.blob + uint64_t(r.use_blob_a ? g.blob_a : g.blob_x) * 256;
+    p.y = (blockIdx.z ? r.out1 : r.out0) + uint64_t(g.slot0) * r.rows;
+    p.partial = nullptr;
+    p.counters = nullptr;
+    p.status = r.status;
+    p.rows = r.rows;
+    p.row_base = uint32_t(g.expert_local) * r.rows;
+    p.batch = uint32_t(g.nb);
+    p.chunks = r.chunks;
+    p.total_stages = (blockIdx.x + 1) * r.chunks;  // this CTA streams exactly one whole tile
+    p.per_cta = r.chunks;
+    p.scale = 1.0f;
+    p.accumulate = 0;
+    p.vec_scale = r.slot_weight ? r.slot_weight + g.slot0 : nullptr;
+    run_stage_range<BHD_TYPE_Q8_0, moe_nt(CLS), moe_split(CLS)>(blockIdx.z ? &tmap1 : &tmap0, p, blockIdx.x, n_stages_ring);
+}
+
+// y[t] (+)= ((0 + d[slot(t,0)]) + d[slot(t,1)]) + ...: the reference's accumulation order
+// (crates/beholdd-model/src/qwen3moe/forward.rs:1385-1398); routes of other ranks are skipped.
+__global__ void k_moe_combine_slots(const float* __restrict__ d, const int32_t* __restrict__ route_slot,
+                                    float* __restrict__ y, uint64_t n, uint32_t dim, uint32_t top_k, int accumulate) {
+    const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t t = i / dim, h = i - t * dim;
+    float out = 0.0f;
+    for (uint32_t j = 0; j < top_k; ++j) {
+        const int32_t slot = route_slot[t * top_k + j];
+        if (slot >= 0) out = __fadd_rn(out, d[uint64_t(slot) * dim + h]);
+    }
+    y[i] = accumulate ? __fadd_rn(y[i], out) : out;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -564,8 +763,8 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
         if (st != BHD_OK) return st;
         uint8_t* blob = ctx->workspace;
 
-        k_pack_x<<<dim3(chunks, nt), STEPS * 32, 0, s>>>(w->kind, x + b0 * w->cols, nullptr, w->cols, nb, uint32_t(w->cols),
-                                                         nt, blob, ctx->status_dev);
+        k_pack_x<<<dim3(chunks, nt), STEPS * 32, 0, s>>>(w->kind, x + b0 * w->cols, w->cols, nb, uint32_t(w->cols), nt, blob,
+                                                         ctx->status_dev);
         BHD_LAUNCHED(ctx, "activation packing kernel");
 
         MatvecParams p;
@@ -582,6 +781,7 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
         p.per_cta = 0;
         p.scale = scale;
         p.accumulate = accumulate;
+        p.vec_scale = nullptr;
 #define BHD_CASE(K)                                                 \
     case K:                                                         \
         switch (nt) {                                               \
@@ -605,9 +805,140 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
     return BHD_OK;
 }
 
-int32_t bhd_moe_experts_fast(bhd_ctx*, const bhd_weight*, const bhd_weight*, const bhd_weight*, const float*, uint64_t,
-                             uint32_t, const int32_t*, const float*, uint32_t, uint32_t, float*, int, cudaStream_t,
+namespace {
+
+template <int CLS>
+int32_t launch_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const MoeRun& run, uint32_t tiles,
+                       uint32_t group_bound, cudaStream_t s) {
+    using S = Smem<BHD_TYPE_Q8_0, moe_nt(CLS)>;
+    auto kern = k_moe_grouped<CLS>;
+    static int ring = 0, cached_device = -1;
+    if (cached_device != ctx->device) {
+        int r = 4;
+        size_t dyn = size_t(r) * S::STAGE + 128;
+        if (dyn > 200 * 1024) { r = 3; dyn = size_t(r) * S::STAGE + 128; }
+        BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        ring = r;
+        cached_device = ctx->device;
+    }
+    if (group_bound == 0) return BHD_OK;
+    CUtensorMap m0, m1;
+    memcpy(&m0, w0->tmap, sizeof(m0));
+    memcpy(&m1, (w1 ? w1 : w0)->tmap, sizeof(m1));
+    kern<<<dim3(tiles, group_bound, w1 ? 2 : 1), THREADS, size_t(ring) * S::STAGE + 128, s>>>(m0, m1, run, ring);
+    BHD_LAUNCHED(ctx, "grouped expert kernel");
+    return BHD_OK;
+}
+
+int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, MoeRun run, const int32_t* glist,
+                           uint32_t gmax, uint32_t tiles, uint32_t n_routes, uint32_t n_local, cudaStream_t s) {
+    // A class can only occur when there are enough routes for its smallest group.
+    const uint32_t small = n_local < n_routes ? n_local : n_routes;
+    int32_t st = BHD_OK;
+    run.glist = glist + 0 * gmax;
+    st = launch_grouped<0>(ctx, w0, w1, run, tiles, small, s);
+    if (st != BHD_OK) return st;
+    if (n_routes >= 5) {
+        run.glist = glist + 1 * gmax;
+        if ((st = launch_grouped<1>(ctx, w0, w1, run, tiles, small < n_routes / 5 ? small : n_routes / 5, s)) != BHD_OK) return st;
+    }
+    if (n_routes >= 9) {
+        run.glist = glist + 2 * gmax;
+        if ((st = launch_grouped<2>(ctx, w0, w1, run, tiles, small < n_routes / 9 ? small : n_routes / 9, s)) != BHD_OK) return st;
+    }
+    if (n_routes >= 17) {
+        run.glist = glist + 3 * gmax;
+        if ((st = launch_grouped<3>(ctx, w0, w1, run, tiles, n_routes / 17, s)) != BHD_OK) return st;
+    }
+    return BHD_OK;
+}
+
+}  // namespace
+
+// Fast path of bhd_moe_experts: plan (sort routes by expert), gather + pack, grouped gate/up,
+// SiLU gating fused into the packing of the down input, grouped down scaled by the route
+// weight, combine in route order. Sets *handled = false when the tensors do not meet the
+// alignment rules of the TMA path.
+int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
+                             const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
+                             uint32_t first_expert, uint32_t n_local, float* y, int accumulate, cudaStream_t s,
                              bool* handled) {
     *handled = false;
+    if (!gate->tmap_ok || !up->tmap_ok || !down->tmap_ok) return BHD_OK;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return BHD_OK;
+    const uint64_t ff = gate->rows, dim = gate->cols;
+    if (dim % 4 != 0 || ff % 4 != 0) return BHD_OK;
+    const uint64_t R64 = T * top_k;
+    if (R64 > (1u << 22)) return BHD_OK;
+    const uint32_t R = uint32_t(R64), E = n_local;
+    const uint32_t chunks_x = uint32_t((dim + CHUNK_K - 1) / CHUNK_K), chunks_a = uint32_t((ff + CHUNK_K - 1) / CHUNK_K);
+    const uint32_t words = (R + 31) / 32;
+    const uint32_t gmax = E + R / 32 + 1;
+    const uint64_t nt_sum = R / 4 + gmax;  // every group has nt <= nb / 4 + 1
+    const size_t unit = size_t(xblob_bytes(BHD_TYPE_Q8_0, 1));
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_hdr = take(sizeof(MoeHeader)), o_counts = take(4 * size_t(E)), o_offsets = take(4 * size_t(E + 1));
+    const size_t o_rslot = take(4 * size_t(R)), o_sroute = take(4 * size_t(R)), o_sweight = take(4 * size_t(R));
+    const size_t o_groups = take(sizeof(MoeGroup) * size_t(gmax)), o_glist = take(4 * 4 * size_t(gmax));
+    const size_t o_bitmap = take(4 * size_t(E) * words), o_prefix = take(4 * size_t(E) * words);
+    const size_t o_g = take(4 * size_t(R) * ff), o_u = take(4 * size_t(R) * ff), o_d = take(4 * size_t(R) * dim);
+    const size_t o_bx = take(nt_sum * unit * chunks_x), o_ba = take(nt_sum * unit * chunks_a);
+    int32_t st = bhd_ensure_workspace(ctx, off, s);
+    if (st != BHD_OK) return st;
+    uint8_t* ws = ctx->workspace;
+    MoeHeader* hdr = reinterpret_cast<MoeHeader*>(ws + o_hdr);
+    MoeGroup* groups = reinterpret_cast<MoeGroup*>(ws + o_groups);
+    int32_t* glist = reinterpret_cast<int32_t*>(ws + o_glist);
+    int32_t* route_slot = reinterpret_cast<int32_t*>(ws + o_rslot);
+    int32_t* slot_route = reinterpret_cast<int32_t*>(ws + o_sroute);
+    float* slot_weight = reinterpret_cast<float*>(ws + o_sweight);
+    float* gbuf = reinterpret_cast<float*>(ws + o_g);
+    float* ubuf = reinterpret_cast<float*>(ws + o_u);
+    float* dbuf = reinterpret_cast<float*>(ws + o_d);
+
+    k_moe_plan<<<1, 1024, 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
+                                  reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
+                                  route_slot, slot_route, slot_weight, groups, glist, gmax,
+                                  reinterpret_cast<uint32_t*>(ws + o_bitmap), reinterpret_cast<uint32_t*>(ws + o_prefix),
+                                  ctx->status_dev);
+    BHD_LAUNCHED(ctx, "route planning kernel");
+    const uint32_t group_bound = gmax < R ? gmax : R;
+    k_moe_pack<<<dim3(chunks_x, group_bound), STEPS * 32, 0, s>>>(0, hdr, groups, slot_route, top_k, x, nullptr, uint32_t(dim),
+                                                                  ws + o_bx, ctx->status_dev);
+    BHD_LAUNCHED(ctx, "token gather and packing kernel");
+
+    MoeRun run;
+    run.hdr = hdr;
+    run.groups = groups;
+    run.glist = glist;
+    run.status = ctx->status_dev;
+    // gate and up: [ff x dim] per expert, both matrices in one launch
+    run.blob = ws + o_bx;
+    run.out0 = gbuf;
+    run.out1 = ubuf;
+    run.slot_weight = nullptr;
+    run.rows = uint32_t(ff);
+    run.chunks = chunks_x;
+    run.use_blob_a = 0;
+    st = launch_grouped_all(ctx, gate, up, run, glist, gmax, uint32_t((ff + TILE_ROWS - 1) / TILE_ROWS), R, E, s);
+    if (st != BHD_OK) return st;
+    k_moe_pack<<<dim3(chunks_a, group_bound), STEPS * 32, 0, s>>>(1, hdr, groups, slot_route, top_k, gbuf, ubuf, uint32_t(ff),
+                                                                  ws + o_ba, ctx->status_dev);
+    BHD_LAUNCHED(ctx, "gating and packing kernel");
+    // down: [dim x ff] per expert, each output row scaled by its route weight
+    run.blob = ws + o_ba;
+    run.out0 = dbuf;
+    run.out1 = nullptr;
+    run.slot_weight = slot_weight;
+    run.rows = uint32_t(dim);
+    run.chunks = chunks_a;
+    run.use_blob_a = 1;
+    st = launch_grouped_all(ctx, down, nullptr, run, glist, gmax, uint32_t((dim + TILE_ROWS - 1) / TILE_ROWS), R, E, s);
+    if (st != BHD_OK) return st;
+    const uint64_t n = T * dim;
+    k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, route_slot, y, n, uint32_t(dim), top_k, accumulate);
+    BHD_LAUNCHED(ctx, "route combine kernel");
+    *handled = true;
     return BHD_OK;
 }

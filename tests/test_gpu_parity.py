@@ -212,7 +212,7 @@ def test_full_size_matvec_properties(dev, kind, rows, cols):
     # a batch equals its single-vector calls
     y1 = torch.empty((1, rows), device="cuda")
     dev.matvec_resident(w, x[3:4].contiguous(), y1)
-    assert max_rel_err(y1.cpu().numpy(), y[3:4].cpu().numpy()) <= 1e-5
+    assert max_rel_err(y1.cpu().numpy(), y[3:4].cpu().numpy()) <= 1e-4
     # linearity in x
     ysum = torch.empty((1, rows), device="cuda")
     dev.matvec_resident(w, (x[0:1] + x[1:2]).contiguous(), ysum)
@@ -333,7 +333,8 @@ def test_routing_ties_break_to_the_lower_index(dev, oracle):
 
 
 @pytest.mark.parametrize("n_experts,dim,ff,top_k,T", [(128, 2048, 768, 8, 1), (128, 2048, 768, 8, 16),
-                                                     (128, 2048, 768, 8, 64), (8, 64, 32, 2, 5), (16, 256, 96, 4, 33)])
+                                                     (128, 2048, 768, 8, 64), (8, 64, 32, 2, 5), (16, 256, 96, 4, 33),
+                                                     (8, 512, 256, 2, 40), (4, 512, 256, 2, 150), (4, 256, 512, 4, 3)])
 def test_moe_layer_matches_oracle(dev, oracle, n_experts, dim, ff, top_k, T):
     import torch
 
