@@ -342,7 +342,7 @@ def run_gpu_arm(args):
     value = world * bytes_per_step * steps / secs / 1e9
 
     detail = {}
-    if not args.quick:
+    if not args.quick and not args.skip_matvec_detail:
         for kind in (8, 12, 14):
             for batch in (1, 2, 4, 8):
                 if kind == HEAD_KIND and batch == 1:
@@ -352,7 +352,7 @@ def run_gpu_arm(args):
                                                         "frac_of_peak": round(r["gbs"] / peak, 4)}
     moe = {}
     try:
-        for T in (() if args.quick else (1, 16, 64, 512)):
+        for T in (() if args.quick else tuple(int(v) for v in args.moe_tokens.split(",") if v)):
             moe[f"T{T}"] = bench_moe(dev, torch, T, max(2, steps // 4), 3, rank, world, barrier)
     except Exception as e:  # the headline number must still be reported
         moe["error"] = repr(e)
@@ -401,6 +401,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="headline workload only")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--moe-tokens", default="1,16,64,512", help="token counts of the routed-layer detail runs")
+    ap.add_argument("--skip-matvec-detail", action="store_true", help="skip the other formats / batch sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

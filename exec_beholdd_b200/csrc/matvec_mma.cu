@@ -532,7 +532,9 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
                                                    int32_t* slot_route, float* slot_weight, MoeGroup* groups,
                                                    int32_t* glist, uint32_t gmax, uint32_t* bitmap, uint32_t* prefix,
                                                    uint32_t* status) {
+    __shared__ uint32_t s_counts[1024], s_offsets[1025];
     const uint32_t words = (n_routes + 31) / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     for (uint32_t i = threadIdx.x; i < n_local * words; i += blockDim.x) bitmap[i] = 0u;
     __syncthreads();
     for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
@@ -544,20 +546,29 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
             route_slot[r] = -1;
     }
     __syncthreads();
-    for (uint32_t e = threadIdx.x; e < n_local; e += blockDim.x) {
+    // One warp per expert: exclusive prefix of the set bits over the expert's bitmap words.
+    for (uint32_t e = warp; e < n_local; e += n_warps) {
         uint32_t run = 0;
-        for (uint32_t w = 0; w < words; ++w) {
-            prefix[e * words + w] = run;
-            run += __popc(bitmap[e * words + w]);
+        for (uint32_t w0 = 0; w0 < words; w0 += 32) {
+            const uint32_t w = w0 + lane;
+            const uint32_t c = w < words ? __popc(bitmap[e * words + w]) : 0u;
+            uint32_t incl = c;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
+            }
+            if (w < words) prefix[e * words + w] = run + incl - c;
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        counts[e] = run;
+        if (lane == 0) s_counts[e] = run;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         uint32_t off = 0, ng = 0, bx = 0, ba = 0, gc[4] = {0, 0, 0, 0};
         for (uint32_t e = 0; e < n_local; ++e) {
-            offsets[e] = off;
-            uint32_t n = counts[e], s0 = off;
+            s_offsets[e] = off;
+            uint32_t n = s_counts[e], s0 = off;
             off += n;
             while (n > 0 && ng < gmax) {
                 const uint32_t nb = n < 32 ? n : 32;
@@ -573,18 +584,22 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
                 n -= nb;
             }
         }
-        offsets[n_local] = off;
+        s_offsets[n_local] = off;
         for (int c = 0; c < 4; ++c) hdr->gcount[c] = gc[c];
         hdr->total_groups = ng;
         hdr->local_routes = off;
     }
     __syncthreads();
+    for (uint32_t e = threadIdx.x; e <= n_local; e += blockDim.x) {
+        offsets[e] = s_offsets[e];
+        if (e < n_local) counts[e] = s_counts[e];
+    }
     for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
         const int32_t e = experts[r];
         if (e >= int32_t(first_expert) && uint32_t(e) < first_expert + n_local) {
             const uint32_t el = uint32_t(e) - first_expert, w = r >> 5;
             const uint32_t rank = prefix[el * words + w] + __popc(bitmap[el * words + w] & ((1u << (r & 31)) - 1u));
-            const uint32_t slot = offsets[el] + rank;
+            const uint32_t slot = s_offsets[el] + rank;
             route_slot[r] = int32_t(slot);
             slot_route[slot] = int32_t(r);
             slot_weight[slot] = weights[r];
@@ -869,7 +884,7 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const uint64_t ff = gate->rows, dim = gate->cols;
     if (dim % 4 != 0 || ff % 4 != 0) return BHD_OK;
     const uint64_t R64 = T * top_k;
-    if (R64 > (1u << 22)) return BHD_OK;
+    if (R64 > (1u << 22) || n_local > 1024) return BHD_OK;
     const uint32_t R = uint32_t(R64), E = n_local;
     const uint32_t chunks_x = uint32_t((dim + CHUNK_K - 1) / CHUNK_K), chunks_a = uint32_t((ff + CHUNK_K - 1) / CHUNK_K);
     const uint32_t words = (R + 31) / 32;

@@ -98,6 +98,49 @@ __global__ void k_route_select(float* __restrict__ probs, uint32_t n_experts, ui
     }
 }
 
+// Router logits for an F32 router in the CPU's summation order, fast: logits[t][e] is one f32
+// accumulator walked over the columns left to right with separately rounded product and sum
+// (crates/beholdd-backend/src/cpu.rs:198-218), so only the additions are sequential. Four
+// loader warps form the products w[e][c] * x[c] of a 32-expert x 128-column tile in shared
+// memory (coalesced, double buffered) while each lane of warp 0 adds the products of its own
+// expert in column order. Bit-identical to the order-exact matvec kernel.
+__global__ void __launch_bounds__(160) k_router_logits_f32(const float* __restrict__ w, uint32_t n_experts, uint32_t dim,
+                                                           const float* __restrict__ x, float* __restrict__ out) {
+    __shared__ float prod[2][32][129];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t e0 = blockIdx.x * 32, t = blockIdx.y;
+    const float* xv = x + uint64_t(t) * dim;
+    const uint32_t tiles = (dim + 127) / 128;
+    auto load = [&](uint32_t tile, int buf) {  // loader warps 1..4: eight experts each
+        const uint32_t c0 = tile * 128;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const uint32_t row = (warp - 1) * 8 + r, e = e0 + row;
+#pragma unroll
+            for (int seg = 0; seg < 4; ++seg) {
+                const uint32_t c = c0 + seg * 32 + lane;
+                float v = 0.0f;
+                if (e < n_experts && c < dim) v = __fmul_rn(w[uint64_t(e) * dim + c], xv[c]);
+                prod[buf][row][seg * 32 + lane] = v;
+            }
+        }
+    };
+    if (warp > 0) load(0, 0);
+    __syncthreads();
+    float acc = 0.0f;
+    for (uint32_t tile = 0; tile < tiles; ++tile) {
+        const int buf = tile & 1;
+        if (warp > 0) {
+            if (tile + 1 < tiles) load(tile + 1, buf ^ 1);
+        } else {
+            const uint32_t n = min(128u, dim - tile * 128);
+            for (uint32_t c = 0; c < n; ++c) acc = __fadd_rn(acc, prod[buf][lane][c]);
+        }
+        __syncthreads();
+    }
+    if (warp == 0 && e0 + lane < n_experts) out[uint64_t(t) * n_experts + e0 + lane] = acc;
+}
+
 // ---- general expert kernels (any dim / expert_ff that are whole Q8_0 blocks) -----------
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -220,8 +263,14 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     }
     if (counts_dev) BHD_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, n_experts * sizeof(int32_t), s), "clearing expert counts");
     // Router logits in the CPU's summation order (forward.rs:1330-1336 -> cpu.rs:198-218).
-    int32_t st = bhd_launch_matvec_strict(ctx, router, 0, x_dev, probs, uint32_t(n_positions), 1.0f, 0, s);
-    if (st != BHD_OK) return st;
+    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535) {
+        k_router_logits_f32<<<dim3(unsigned((n_experts + 31) / 32), unsigned(n_positions)), 160, 0, s>>>(
+            reinterpret_cast<const float*>(router->dev), uint32_t(n_experts), uint32_t(router->cols), x_dev, probs);
+        BHD_LAUNCHED(ctx, "router logits kernel");
+    } else {
+        const int32_t st = bhd_launch_matvec_strict(ctx, router, 0, x_dev, probs, uint32_t(n_positions), 1.0f, 0, s);
+        if (st != BHD_OK) return st;
+    }
     const uint32_t near_per = uint32_t(n_experts - top_k < NEAR_MISS_WINDOW ? n_experts - top_k : NEAR_MISS_WINDOW);
     const unsigned threads = unsigned((n_experts + 31) / 32 * 32);
     const size_t smem = (n_experts + 2 * top_k) * sizeof(float) + 16;
