@@ -531,9 +531,14 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
                                                    uint32_t* counts, uint32_t* offsets, int32_t* route_slot,
                                                    int32_t* slot_route, float* slot_weight, MoeGroup* groups,
                                                    int32_t* glist, uint32_t gmax, uint32_t* bitmap, uint32_t* prefix,
-                                                   uint32_t* status) {
+                                                   uint32_t* status, int use_smem) {
     __shared__ uint32_t s_counts[1024], s_offsets[1025];
+    extern __shared__ uint32_t s_dyn[];
     const uint32_t words = (n_routes + 31) / 32;
+    if (use_smem) {  // small problems keep the bitmap and its prefix on chip
+        bitmap = s_dyn;
+        prefix = s_dyn + n_local * words;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     for (uint32_t i = threadIdx.x; i < n_local * words; i += blockDim.x) bitmap[i] = 0u;
     __syncthreads();
@@ -912,11 +917,13 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     float* ubuf = reinterpret_cast<float*>(ws + o_u);
     float* dbuf = reinterpret_cast<float*>(ws + o_d);
 
-    k_moe_plan<<<1, 1024, 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
+    const size_t plan_smem = size_t(E) * words * 8;
+    const int plan_on_chip = plan_smem <= 40 * 1024;
+    k_moe_plan<<<1, R <= 256 ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
                                   reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
                                   route_slot, slot_route, slot_weight, groups, glist, gmax,
                                   reinterpret_cast<uint32_t*>(ws + o_bitmap), reinterpret_cast<uint32_t*>(ws + o_prefix),
-                                  ctx->status_dev);
+                                  ctx->status_dev, plan_on_chip);
     BHD_LAUNCHED(ctx, "route planning kernel");
     const uint32_t group_bound = gmax < R ? gmax : R;
     k_moe_pack<<<dim3(chunks_x, group_bound), STEPS * 32, 0, s>>>(0, hdr, groups, slot_route, top_k, x, nullptr, uint32_t(dim),

@@ -134,7 +134,16 @@ __global__ void __launch_bounds__(160) k_router_logits_f32(const float* __restri
             if (tile + 1 < tiles) load(tile + 1, buf ^ 1);
         } else {
             const uint32_t n = min(128u, dim - tile * 128);
-            for (uint32_t c = 0; c < n; ++c) acc = __fadd_rn(acc, prod[buf][lane][c]);
+            const float* mine = prod[buf][lane];
+            uint32_t c = 0;
+            for (; c + 16 <= n; c += 16) {  // loads first, then the ordered additions
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = mine[c + i];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc = __fadd_rn(acc, v[i]);
+            }
+            for (; c < n; ++c) acc = __fadd_rn(acc, mine[c]);
         }
         __syncthreads();
     }
