@@ -519,3 +519,94 @@ int32_t bhd_launch_matvec_decode(bhd_ctx* ctx, const bhd_weight* w, uint64_t sla
     *handled = true;
     return BHD_OK;
 }
+
+// ---- decode matvec for callers that must not allocate ------------------------------------------
+// Some embedders of this library run where device allocation is off the table once serving has
+// started: a real-time decode loop that may not take the allocator's locks or its implicit
+// synchronisation, a process whose whole HBM budget was handed to a weight/KV-cache arena at
+// start-up, or a host that calls in from inside a stream capture. For them this entry point
+// keeps the one piece of scratch the decode matvec needs -- the packed fp16 activations -- in
+// a fixed array that is part of the library image instead of the context's growable workspace.
+//
+// The array costs BHD_NOALLOC_SCRATCH_BYTES of HBM on every GPU that loads the library, for the
+// life of the process. It always suffices for cols <= 16384 with up to 4 activation vectors;
+// requests whose packed activations do not fit are refused with BHD_ERR_SHAPE rather than
+// served some other way.
+constexpr size_t BHD_NOALLOC_SCRATCH_BYTES = 288 * 1024;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[BHD_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+// Device address of g_noalloc_scratch per CUDA device. In host code the symbol's name is only a
+// handle for the runtime, not a device pointer, so the address is looked up once per device.
+uint8_t* g_noalloc_ptr[MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int32_t bhd_matvec_noalloc(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
+                                                                             const float* x_dev, float* y_dev, uint32_t batch,
+                                                                             float scale, int32_t accumulate, void* stream) {
+    if (!ctx || ctx->magic != BHD_CTX_MAGIC) return BHD_ERR_INVALID_ARGUMENT;
+    if (!w || w->magic != BHD_WEIGHT_MAGIC || w->ctx != ctx)
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "matvec_noalloc: not a weight of this context");
+    if (slab >= w->slabs)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: slab %llu of %llu", (unsigned long long)slab,
+                        (unsigned long long)w->slabs);
+    if (!isfinite(scale)) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "matvec_noalloc: scale must be finite");
+    if (batch == 0 || w->rows == 0) return BHD_OK;
+    if (!x_dev || !y_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "matvec_noalloc: null buffer");
+    if (batch > 4)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: matvec_noalloc serves at most 4 activation vectors, got %u", batch);
+    cudaStream_t s = cudaStream_t(stream);
+    const bool tma_path = w->tmap16_ok && w->cols != 0 && w->cols % 4 == 0 && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 &&
+                          w->rows <= 0x7fffffffull;
+    if (!tma_path)  // the general kernels need no scratch at all
+        return bhd_launch_matvec_general(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s);
+    const uint32_t chunks = uint32_t((w->cols + CHUNK_K - 1) / CHUNK_K);
+    const uint32_t tiles = uint32_t((w->rows + ROWS - 1) / ROWS);
+    const int nb = batch == 3 ? 4 : int(batch);
+    const size_t need = size_t(chunks) * dblob_bytes(w->kind, nb);
+    if (need > BHD_NOALLOC_SCRATCH_BYTES)
+        return bhd_fail(ctx, BHD_ERR_SHAPE,
+                        "shape mismatch: matvec_noalloc needs %zu bytes of scratch for %llu columns x %u vectors, the fixed "
+                        "array holds %zu (cols <= 16384)",
+                        need, (unsigned long long)w->cols, batch, BHD_NOALLOC_SCRATCH_BYTES);
+    if (ctx->device < 0 || ctx->device >= MAX_DEVICES)
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "matvec_noalloc: device index %d out of range", ctx->device);
+    if (!g_noalloc_ptr[ctx->device]) {
+        // First call on this device: resolve the array's device address (with the device current).
+        BHD_CUDA(ctx, cudaSetDevice(ctx->device), "selecting the device");
+        void* p = nullptr;
+        BHD_CUDA(ctx, cudaGetSymbolAddress(&p, g_noalloc_scratch), "resolving the fixed scratch array");
+        g_noalloc_ptr[ctx->device] = static_cast<uint8_t*>(p);
+    }
+    uint8_t* blob = g_noalloc_ptr[ctx->device];
+    // The packer rewrites every byte the matvec reads (fragments, sums and zero padding), so the
+    // previous call's contents never leak into this one.
+    k_pack_x_decode<<<chunks, STEPS * 32, 0, s>>>(w->kind, x_dev, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev);
+    BHD_LAUNCHED(ctx, "activation packing kernel");
+    DecodeParams p;
+    p.blob = blob;
+    p.y = y_dev;
+    p.status = ctx->status_dev;
+    p.rows = uint32_t(w->rows);
+    p.row_base = uint32_t(slab * w->rows);
+    p.chunks = chunks;
+    p.batch = batch;
+    p.scale = scale;
+    p.accumulate = accumulate;
+    int32_t st = BHD_OK;
+#define BHD_CASE(K)                                                      \
+    case K:                                                              \
+        if (nb == 1) st = launch_decode<K, 1>(ctx, w, p, tiles, s);      \
+        else if (nb == 2) st = launch_decode<K, 2>(ctx, w, p, tiles, s); \
+        else st = launch_decode<K, 4>(ctx, w, p, tiles, s);              \
+        break;
+    switch (w->kind) {
+        BHD_CASE(BHD_TYPE_Q8_0)
+        BHD_CASE(BHD_TYPE_Q4_K)
+        BHD_CASE(BHD_TYPE_Q6_K)
+        default: return bhd_launch_matvec_general(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s);
+    }
+#undef BHD_CASE
+    return st;
+}

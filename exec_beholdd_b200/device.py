@@ -26,7 +26,7 @@ ERR_UNSUPPORTED_FORMAT, ERR_SHAPE, ERR_ALLOCATION, ERR_BACKEND, ERR_INVALID_ARGU
 #: every symbol include/beholdd_b200.h declares
 EXPORTS = [
     "bhd_error_text", "bhd_last_error_message", "bhd_device_name", "bhd_ctx_create", "bhd_ctx_destroy", "bhd_supports",
-    "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_host",
+    "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_noalloc", "bhd_matvec_host",
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
     "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count",
 ]
@@ -78,6 +78,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_weight_free.argtypes = [vp]
     lib.bhd_dequantize.argtypes = [vp, vp, u64, vp, u64, vp]
     lib.bhd_matvec.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32, vp]
+    lib.bhd_matvec_noalloc.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32, vp]
     lib.bhd_matvec_host.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32]
     lib.bhd_matmul.argtypes = [vp, vp, u64, vp, vp, u64, vp]
     lib.bhd_softmax.argtypes = [vp, vp, u64, u64, vp]

@@ -103,6 +103,22 @@ int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const 
 int32_t bhd_matvec_host(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_host, float* y_host,
                         uint32_t batch, float scale, int32_t accumulate);
 
+/* No counterpart in the reference. A decode matvec (same operation and results as bhd_matvec,
+ * batch <= 4) for hosts that may not allocate device memory once they are serving: real-time
+ * decode loops that cannot take the allocator's locks or implicit synchronisation, processes
+ * that gave all of HBM to their own arena at start-up. Its scratch (the packed fp16
+ * activations) is a fixed 288 KiB array inside the library image, held by every GPU that loads
+ * the library until the process exits, instead of the context workspace; the call performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - Limit: batch <= 4, and the packed activations must fit the array (always true for
+ *     cols <= 16384); anything larger is refused with BHD_ERR_SHAPE, outputs untouched.
+ *   - The first call on a device also looks up the array's device address; make that call
+ *     before starting any stream capture.
+ *   - All calls on a GPU share the one array (from any context or stream): calls whose kernels
+ *     can overlap on the GPU race on it. Issue them on one stream, or order them yourself. */
+int32_t bhd_matvec_noalloc(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_dev, float* y_dev,
+                           uint32_t batch, float scale, int32_t accumulate, void* stream);
+
 /* Prefill: Y[m][n] = sum_k X[m][k] * W[n][k] for m < M, a loop of Device::matvec over
  * positions in the reference (crates/beholdd-model/src/qwen3moe/forward.rs:1086-1127). */
 int32_t bhd_matmul(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_dev, float* y_dev,
