@@ -295,14 +295,21 @@ def bench_moe(dev, torch, T, steps, warmup, rank=0, world=1, barrier=None):
         layer.forward(x, y)
 
     secs = time_region(torch, step, steps, warmup, barrier, graph=(world == 1))
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([secs], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
     dev.check_status()
     counts = layer.last_counts.cpu().numpy()
     touched = int((counts > 0).sum())
     slab = 3 * synth.packed_bytes(8, m["ff"], m["dim"])
     bytes_touched = m["n_experts"] * m["dim"] * 4 + touched * slab + 8 * T * m["dim"]
-    out = {"T": T, "tokens_per_s": T * steps / secs, "ms_per_layer": secs / steps * 1e3, "experts_touched": touched,
+    out = {"T_per_gpu": T, "tokens_per_s": world * T * steps / secs, "ms_per_layer": secs / steps * 1e3,
+           "exchange": layer.exchange if world > 1 else "none", "experts_touched": touched,
            "gbs_of_touched_bytes": bytes_touched * steps / secs / 1e9,
-           "tflops": T * m["top_k"] * 3 * 2 * m["ff"] * m["dim"] * steps / secs / 1e12}
+           "tflops": world * T * m["top_k"] * 3 * 2 * m["ff"] * m["dim"] * steps / secs / 1e12}
     layer.free()
     return out
 

@@ -39,12 +39,15 @@ def route_plan(experts, n_experts: int, world: int):
 class ExpertParallelLayer:
     """One routed-expert layer with experts split across `world` ranks."""
 
-    def __init__(self, dev, router, gate, up, down, n_experts, dim, ff, top_k, rank=0, world=1, group=None):
+    def __init__(self, dev, router, gate, up, down, n_experts, dim, ff, top_k, rank=0, world=1, group=None,
+                 exchange="gather"):
         self.dev, self.router, self.gate, self.up, self.down = dev, router, gate, up, down
         self.n_experts, self.dim, self.ff, self.top_k = n_experts, dim, ff, top_k
         self.rank, self.world, self.group = rank, world, group
         self.per = n_experts // world
         assert n_experts % world == 0
+        assert exchange in ("gather", "alltoall")
+        self.exchange = exchange
         self.last_counts = None
 
     @classmethod
@@ -82,6 +85,12 @@ class ExpertParallelLayer:
         self.dev.moe_experts(self.gate, self.up, self.down, rows, expert_ids.view(-1, 1), route_weights.view(-1, 1), out,
                              first_expert=self.rank * self.per, n_local=self.per)
 
+    def _local_partial(self, x_all, experts_all, weights_all, out):
+        """All positions of all ranks, only this rank's experts: out[t] = sum over the local
+        routes of t, in selection order (routes of other ranks contribute nothing)."""
+        self.dev.moe_experts(self.gate, self.up, self.down, x_all, experts_all, weights_all, out,
+                             first_expert=self.rank * self.per, n_local=self.per)
+
     def _combine(self, per_route, y, accumulate):
         """per_route [k, T, dim] -> y[t] (+)= ((0 + r[0][t]) + r[1][t]) + ... in route order."""
         self.dev.moe_combine(per_route, y, accumulate)
@@ -104,6 +113,8 @@ class ExpertParallelLayer:
 
         self._route(x, experts, weights, counts)
         self.last_counts = counts
+        if self.exchange == "gather":
+            return self._forward_gather(x, y, experts, weights, accumulate)
         _, order, send_counts = route_plan(experts, self.n_experts, self.world)
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
@@ -133,4 +144,34 @@ class ExpertParallelLayer:
         per_route = torch.empty((self.top_k * T, self.dim), dtype=x.dtype, device=x.device)
         per_route.index_copy_(0, slot, out_back)
         self._combine(per_route.view(self.top_k, T, self.dim), y, accumulate)
+        return experts, weights
+
+    def _forward_gather(self, x, y, experts, weights, accumulate):
+        """Exchange without a host round trip: all-gather the positions and their routes,
+        every rank applies its own experts to all positions, reduce-scatter the partial
+        outputs. Dispatch volume is the same order as the all-to-all (a position's 8 routes
+        reach most ranks anyway) and nothing depends on counts known only on the device, so
+        the whole layer stays asynchronous. The cross-rank sum is NCCL's reduction order, not
+        the selection order: identical to the single-GPU result within f32 rounding."""
+        import torch
+        import torch.distributed as dist
+
+        T, W = x.shape[0], self.world
+        x_all = torch.empty((W * T, self.dim), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+        meta = torch.cat([experts, weights.view(torch.int32)], dim=1).contiguous()
+        meta_all = torch.empty((W * T, 2 * self.top_k), dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(meta_all, meta, group=self.group)
+        experts_all = meta_all[:, : self.top_k].contiguous()
+        weights_all = meta_all[:, self.top_k:].contiguous().view(torch.float32)
+        partial = torch.empty((W * T, self.dim), dtype=x.dtype, device=x.device)
+        self._local_partial(x_all, experts_all, weights_all, partial)
+        mine = torch.empty((T, self.dim), dtype=x.dtype, device=x.device) if accumulate else y
+        if dist.get_backend(self.group) == "gloo":  # gloo has no reduce-scatter
+            dist.all_reduce(partial, group=self.group)
+            mine.copy_(partial[self.rank * T:(self.rank + 1) * T])
+        else:
+            dist.reduce_scatter_tensor(mine, partial, group=self.group)
+        if accumulate:
+            y.add_(mine)
         return experts, weights
