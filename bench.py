@@ -281,6 +281,21 @@ def bench_matvec_e2e(dev, torch, kind, steps, warmup, copies):
             "d2h_bytes_per_step": copies * 4 * ROWS, "us_per_matvec": secs / steps / copies * 1e6}
 
 
+def bench_prefill(dev, torch, M, N, K, steps, warmup, peak_tflops):
+    """Q8_0 prefill matmul Y[M x N] = X[M x K] W^T (tensor-core bound for M >= 512)."""
+    from exec_beholdd_b200 import synth
+
+    packed = torch.from_numpy(synth.q8_0_matrix(SEED + 5, N, K)).cuda()
+    w = dev.wrap_weight(packed, 8, N, K)
+    x = torch.from_numpy(synth.activations(SEED + 6, (M, K), outliers=True)).cuda()
+    y = torch.empty((M, N), device="cuda")
+    secs = time_region(torch, lambda: dev.matmul_resident(w, x, y), steps, warmup)
+    dev.check_status()
+    w.free()
+    tf = 2.0 * M * N * K * steps / secs / 1e12
+    return {"us": round(secs / steps * 1e6, 1), "tflops": round(tf, 1), "frac_of_tensor_peak": round(tf / peak_tflops, 4)}
+
+
 def bench_moe(dev, torch, T, steps, warmup, rank=0, world=1, barrier=None):
     """One routed-expert layer at the Qwen3-30B-A3B shapes; experts split `world` ways."""
     from exec_beholdd_b200 import Weight, synth
@@ -360,6 +375,19 @@ def run_gpu_arm(args):
                 r, _, _ = bench_matvec(dev, torch, kind, batch, max(2, steps // 4), 3, barrier)
                 detail[f"{KIND_NAME[kind]}_b{batch}"] = {"gbs": round(r["gbs"], 1), "us": round(r["us_per_matvec"], 2),
                                                         "frac_of_peak": round(r["gbs"] / peak, 4)}
+    prefill = {}
+    if not args.quick and not args.skip_matvec_detail and world == 1:
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+                tpeak = float(json.load(fh)["bf16_tflops_sustained"])
+        except Exception:
+            tpeak = 1400.0
+        for M in (128, 512, 2048):
+            for N in (12288, 4096):
+                try:
+                    prefill[f"M{M}_N{N}"] = bench_prefill(dev, torch, M, N, 4096, max(2, steps // 4), 3, tpeak)
+                except Exception as e:
+                    prefill[f"M{M}_N{N}"] = {"error": repr(e)}
     moe = {}
     try:
         for T in (() if args.quick else tuple(int(v) for v in args.moe_tokens.split(",") if v)):
@@ -395,7 +423,7 @@ def run_gpu_arm(args):
                          "traffic": HEAD_TRAFFIC_BYTES, "peak_source": peak_kind, "kernel": "matvec (dominant kernel of the step)",
                          "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
-            "clocks": clocks.summary(), "matvec_detail": detail, "moe_layer": moe,
+            "clocks": clocks.summary(), "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "moe_layer": moe,
         }
         print(json.dumps(line), flush=True)
     dev.close()

@@ -16,6 +16,8 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
                                uint64_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
 void bhd_weight_build_tensor_map(bhd_ctx* ctx, bhd_weight* w);
 void bhd_weight_build_tensor_map16(bhd_ctx* ctx, bhd_weight* w);
+int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y, uint64_t m,
+                                   cudaStream_t s, bool* handled);
 int32_t bhd_launch_matvec_decode(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                  uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
 
@@ -331,6 +333,8 @@ int32_t bhd_matmul(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float
     if (m == 0 || w->rows == 0) return BHD_OK;
     cudaStream_t s = cudaStream_t(stream);
     bool handled = false;
+    const int32_t gs = bhd_launch_gemm_q8_tcgen05(ctx, w, slab, x_dev, y_dev, m, s, &handled);
+    if (gs != BHD_OK || handled) return gs;
     const int32_t fs = bhd_launch_matvec_fast(ctx, w, slab, x_dev, y_dev, m, 1.0f, 0, s, &handled);
     if (fs != BHD_OK || handled) return fs;
     return bhd_launch_matvec_general(ctx, w, slab, x_dev, y_dev, m, 1.0f, 0, s);
