@@ -344,7 +344,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     }
     static int cached_device = -1;
     if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024),
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
                  "raising the shared memory limit");
         cached_device = ctx->device;
     }
