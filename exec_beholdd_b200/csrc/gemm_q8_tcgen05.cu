@@ -35,7 +35,8 @@ constexpr int SLICE_K = 64;            // columns per fp16 stage (one 128-byte s
 constexpr int PACK_ROW = 272;          // packed bytes per row per chunk
 constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
-constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 convert + epilogue
+constexpr int CONVERTERS = 128;        // groups of 128 converter threads (one per weight row) take alternating slices
+constexpr int THREADS = 64 + CONVERTERS;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2.. convert, warps 2-5 also epilogue
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -147,32 +148,61 @@ struct GemmParams {
     uint32_t k;          // columns
     uint32_t tn;         // tokens per tile: 64, 128 or 256
     uint32_t stages;     // fp16 stages in the ring
+    // Grouped (routed experts) mode, when `groups` is set: blockIdx.y walks the class list
+    // `glist`; the tile's tokens are the group's slots, its weights the group's expert slab.
+    const MoeHeader* hdr;
+    const MoeGroup* groups;
+    const int32_t* glist;
+    uint32_t cls;
+    float* y1;                 // output of the second weight tensor (blockIdx.z == 1)
+    const float* slot_weight;  // optional per-slot factor (down projection)
+    // Split activations: x = hi + lo in fp16 (22 bits). The B tile then holds tn rows of hi followed by
+    // tn rows of lo (lo rows live `lo_row_offset` rows further down the activation matrix) and the
+    // epilogue adds the two column halves.
+    uint32_t split, lo_row_offset;
 };
 
-__global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_constant__ CUtensorMap tmap_w,
+// GROUPED = false: plain prefill matmul. GROUPED = true: routed experts (group list, two weight tensors, split
+// operands); compile-time so that the prefill instance carries none of the grouped code.
+template <bool GROUPED>
+__global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_constant__ CUtensorMap tmap_w0,
+                                                                const __grid_constant__ CUtensorMap tmap_w1,
                                                                 const __grid_constant__ CUtensorMap tmap_x,
                                                                 const GemmParams p) {
+    constexpr bool SPLIT = GROUPED;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[4], b_full[4], st_empty[4], tmem_full;
+    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[8], b_full[8], st_empty[8], tmem_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-    const uint32_t stage_bytes = A_BYTES + p.tn * 128u;
+    const uint32_t bn = SPLIT ? 2 * p.tn : p.tn;  // MMA N = rows of the B tile
+    const uint32_t a_bytes = SPLIT ? 2 * A_BYTES : A_BYTES;  // split mode keeps a second tile: the rounding remainder of d*q
+    const uint32_t stage_bytes = a_bytes + bn * 128u;
     const uint32_t pack_addr = smem0, stage_addr = smem0 + 2 * PACK_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t n0 = blockIdx.x * TILE_N, m0 = blockIdx.y * p.tn;
+    uint32_t m0 = blockIdx.y * p.tn, m_end = p.m, row_base = p.row_base;
+    if (GROUPED) {
+        if (blockIdx.y >= p.hdr->gcount[p.cls]) return;  // whole CTA, before anything is set up
+        const MoeGroup g = p.groups[p.glist[blockIdx.y]];
+        m0 = uint32_t(g.slot0);
+        m_end = m0 + uint32_t(g.nb);
+        row_base = uint32_t(g.expert_local) * p.n_rows;
+    }
+    const CUtensorMap* tmap_w = (GROUPED && blockIdx.z) ? &tmap_w1 : &tmap_w0;
+    float* const yout = (GROUPED && blockIdx.z) ? p.y1 : p.y;
+    const uint32_t n0 = blockIdx.x * TILE_N;
     const uint32_t slices = (p.k + SLICE_K - 1) / SLICE_K, chunks = (p.k + CHUNK_K - 1) / CHUNK_K;
     const uint32_t S = p.stages;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 128); }
-        for (uint32_t i = 0; i < S; ++i) { mbar_init(&a_full[i], 128); mbar_init(&b_full[i], 1); mbar_init(&st_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], CONVERTERS / 32); }
+        for (uint32_t i = 0; i < S; ++i) { mbar_init(&a_full[i], 4); mbar_init(&b_full[i], 1); mbar_init(&st_empty[i], 1); }
         mbar_init(&tmem_full, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(&tmem_base_slot, p.tn);  // TN is a power of two >= 64
+    if (warp == 1) tmem_alloc(&tmem_base_slot, bn);  // a power of two >= 32
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -187,44 +217,52 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_con
                 const uint32_t pb = c & 1;
                 if (!mbar_wait(&pk_empty[pb], ((c >> 1) & 1) ^ 1)) { give_up(); break; }
                 mbar_arrive_expect_tx(&pk_full[pb], PACK_BYTES);
-                tma_load_2d(pack_addr + pb * PACK_BYTES, &tmap_w, int(c * (PACK_ROW / 2)), int(p.row_base + n0), &pk_full[pb]);
+                tma_load_2d(pack_addr + pb * PACK_BYTES, tmap_w, int(c * (PACK_ROW / 2)), int(row_base + n0), &pk_full[pb]);
                 for (uint32_t kb = 0; kb < 4; ++kb) {
                     const uint32_t it = c * 4 + kb;
                     if (it >= slices) break;
                     const uint32_t s = it % S;
                     if (!mbar_wait(&st_empty[s], ((it / S) & 1) ^ 1)) { give_up(); break; }
-                    mbar_arrive_expect_tx(&b_full[s], p.tn * 128u);
-                    tma_load_2d(stage_addr + s * stage_bytes + A_BYTES, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
+                    mbar_arrive_expect_tx(&b_full[s], bn * 128u);
+                    tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
+                    if (SPLIT)
+                        tma_load_2d(stage_addr + s * stage_bytes + a_bytes + p.tn * 128u, &tmap_x, int(it * SLICE_K),
+                                    int(p.lo_row_offset + m0), &b_full[s]);
                 }
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer --------------------------------------------------------------------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(TILE_N, p.tn);
+            const uint32_t idesc = umma_idesc(TILE_N, bn);
             bool ok = true;
             for (uint32_t it = 0; it < slices && ok; ++it) {
                 const uint32_t s = it % S, par = (it / S) & 1;
                 if (aborted() || !mbar_wait(&b_full[s], par) || !mbar_wait(&a_full[s], par)) { give_up(); ok = false; break; }
                 tc_fence_after();
-                const uint64_t da = umma_desc(stage_addr + s * stage_bytes), db = umma_desc(stage_addr + s * stage_bytes + A_BYTES);
+                const uint64_t da = umma_desc(stage_addr + s * stage_bytes), db = umma_desc(stage_addr + s * stage_bytes + a_bytes);
+                const uint64_t dl = umma_desc(stage_addr + s * stage_bytes + A_BYTES);
 #pragma unroll
-                for (uint32_t k16 = 0; k16 < 4; ++k16)  // 32 bytes (16 fp16) further along the swizzled row per step
+                for (uint32_t k16 = 0; k16 < 4; ++k16) {  // 32 bytes (16 fp16) further along the swizzled row per step
                     tc_mma_f16(tmem_base, da + 2 * k16, db + 2 * k16, idesc, (it | k16) ? 1u : 0u);
+                    if (SPLIT) tc_mma_f16(tmem_base, dl + 2 * k16, db + 2 * k16, idesc, 1u);
+                }
                 tc_commit(&st_empty[s]);  // arrives when these MMAs have finished reading the stage
             }
             tc_commit(&tmem_full);        // arrives when every MMA issued so far is complete
         }
     } else {
-        // ---- converters: thread = one weight row; then the epilogue ----------------------------------
-        const uint32_t row = threadIdx.x - 64;  // 0..127
+        // ---- converters: two groups of four warps take alternating 64-column slices, so the latency of one
+        // group's convert -> fence -> arrive chain hides behind the other's; thread = one weight row ----
+        const uint32_t ct = threadIdx.x - 64;   // 0..255
+        const uint32_t row = ct & 127, grp = ct >> 7;  // grp is uniform per warp
         const uint32_t sw = row & 7, a_row_off = (row >> 3) * 1024 + sw * 128;
         bool ok = true;
         for (uint32_t c = 0; c < chunks && ok; ++c) {
             const uint32_t pb = c & 1;
             if (aborted() || !mbar_wait(&pk_full[pb], (c >> 1) & 1)) { give_up(); ok = false; break; }
             const uint32_t src_row = pack_addr + pb * PACK_BYTES + row * PACK_ROW;
-            for (uint32_t kb = 0; kb < 4; ++kb) {
+            for (uint32_t kb = grp; kb < 4; kb += CONVERTERS / 128) {
                 const uint32_t it = c * 4 + kb;
                 if (it >= slices) break;
                 const uint32_t s = it % S;
@@ -234,11 +272,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_con
 #pragma unroll
                 for (int i = 0; i < 17; ++i) w[i] = lds32(src_row + kb * 68 + 4 * i);
                 const uint32_t a_dst = stage_addr + s * stage_bytes + a_row_off;
+                const __half2 off = __half2half2(__ushort_as_half(uint16_t(0x6480)));  // 1152
 #pragma unroll
                 for (int blk = 0; blk < 2; ++blk) {
                     const uint32_t dbits = blk == 0 ? (w[0] & 0xffffu) : (w[8] >> 16);
                     const __half2 d2 = __half2half2(__ushort_as_half(uint16_t(dbits)));
-                    const __half2 off = __half2half2(__ushort_as_half(uint16_t(0x6480)));  // 1152
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {  // 8 quants -> one 16-byte chunk of the swizzled row
                         uint32_t q[2];
@@ -247,39 +285,60 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_con
                             const int i = 2 * ch + j;
                             q[j] = blk == 0 ? __funnelshift_r(w[i], w[i + 1], 16) : w[9 + i];
                         }
-                        uint32_t h[4];
+                        uint32_t h[4], l[4];
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const uint32_t u = q[j] ^ 0x80808080u;  // 0x6400 | (q + 128) is the fp16 q + 1152
                             const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140), hi = __byte_perm(u, 0x64646464u, 0x4342);
-                            const __half2 a = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&lo), off), d2);
-                            const __half2 b = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&hi), off), d2);
+                            const __half2 qa = __hsub2(*reinterpret_cast<const __half2*>(&lo), off);
+                            const __half2 qb = __hsub2(*reinterpret_cast<const __half2*>(&hi), off);
+                            const __half2 a = __hmul2(qa, d2), b = __hmul2(qb, d2);
                             h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
                             h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
+                            if (SPLIT) {  // q*d - fp16(q*d), exact in one fused operation
+                                const __half2 ra = __hfma2(qa, d2, __hneg2(a)), rb = __hfma2(qb, d2, __hneg2(b));
+                                l[2 * j] = *reinterpret_cast<const uint32_t*>(&ra);
+                                l[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&rb);
+                            }
                         }
                         const uint32_t chunk16 = uint32_t(blk * 4 + ch) ^ sw;  // 128B swizzle: chunk index XOR row mod 8
                         sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
+                        if (SPLIT) sts128(a_dst + A_BYTES + chunk16 * 16, make_uint4(l[0], l[1], l[2], l[3]));
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
-                mbar_arrive(&a_full[s]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[s]);  // one arrival per converter warp
             }
-            mbar_arrive(&pk_empty[pb]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pk_empty[pb]);
         }
         // ---- epilogue: TMEM lane = weight row, column = token ------------------------------------
-        if (ok && !aborted() && mbar_wait(&tmem_full, 0)) {
+        if (warp >= 6) {
+            // warps 6-9 only convert
+        } else if (ok && !aborted() && mbar_wait(&tmem_full, 0)) {
             tc_fence_after();
             const uint32_t q = warp & 3;                 // the TMEM lane quarter this warp may read
             const uint32_t n = n0 + q * 32 + lane;
             for (uint32_t col = 0; col < p.tn; col += 32) {
-                if (m0 + col >= p.m) break;              // uniform across the warp
+                if (m0 + col >= m_end) break;            // uniform across the warp
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((q * 32u) << 16) + col, r);
+                if (SPLIT) {  // add the lo half of the columns
+                    uint32_t r2[32];
+                    tc_ld32(tmem_base + ((q * 32u) << 16) + p.tn + col, r2);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
                 if (n < p.n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t m = m0 + col + j;
-                        if (m < p.m) p.y[uint64_t(m) * p.n_rows + n] = __uint_as_float(r[j]);
+                        if (m < m_end) {
+                            float v = __uint_as_float(r[j]);
+                            if (GROUPED && p.slot_weight) v = __fmul_rn(v, p.slot_weight[m]);
+                            yout[uint64_t(m) * p.n_rows + n] = v;
+                        }
                     }
                 }
             }
@@ -289,7 +348,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, p.tn);
+    if (warp == 1) tmem_dealloc(tmem_base, bn);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -344,7 +403,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     }
     static int cached_device = -1;
     if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
                  "raising the shared memory limit");
         cached_device = ctx->device;
     }
@@ -357,8 +416,131 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     p.k = K;
     p.tn = tn;
     p.stages = stages;
-    k_gemm_q8_tcgen05<<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), THREADS, dyn, s>>>(map_w, map_x, p);
+    p.hdr = nullptr;
+    p.groups = nullptr;
+    p.glist = nullptr;
+    p.cls = 0;
+    p.y1 = nullptr;
+    p.slot_weight = nullptr;
+    p.split = 0;
+    p.lo_row_offset = 0;
+    k_gemm_q8_tcgen05<false><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), THREADS, dyn, s>>>(map_w, map_w, map_x, p);
     BHD_LAUNCHED(ctx, "tcgen05 matmul kernel");
     *handled = true;
+    return BHD_OK;
+}
+
+namespace {
+
+// fp16 activations of the routed experts in slot order (routes sorted by expert):
+// mode 0: row of slot = x[position of the slot's route] (the token-to-expert gather);
+// mode 1: row of slot = silu(g[slot]) * u[slot] (crates/beholdd-kernel/src/vecops.rs:91-111, limit 0).
+__global__ void k_moe_slots_f16(int mode, const MoeHeader* __restrict__ hdr, const int32_t* __restrict__ slot_route,
+                                uint32_t top_k, const float* __restrict__ src, const float* __restrict__ src2, uint32_t K,
+                                __half* __restrict__ out, uint32_t lo_row_offset, uint32_t* __restrict__ status) {
+    const uint32_t slot = blockIdx.y;
+    if (slot >= hdr->local_routes) return;
+    const uint32_t k = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (k >= K) return;
+    float4 v;
+    if (mode == 0) {
+        v = *reinterpret_cast<const float4*>(src + uint64_t(uint32_t(slot_route[slot]) / top_k) * K + k);
+    } else {
+        v = *reinterpret_cast<const float4*>(src + uint64_t(slot) * K + k);
+        const float4 u = *reinterpret_cast<const float4*>(src2 + uint64_t(slot) * K + k);
+        v.x = __fmul_rn(__fdiv_rn(v.x, __fadd_rn(1.0f, expf(-v.x))), u.x);
+        v.y = __fmul_rn(__fdiv_rn(v.y, __fadd_rn(1.0f, expf(-v.y))), u.y);
+        v.z = __fmul_rn(__fdiv_rn(v.z, __fadd_rn(1.0f, expf(-v.z))), u.z);
+        v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.0f, expf(-v.w))), u.w);
+    }
+    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    if (!(fabsf(fa.x) <= 65504.f && fabsf(fa.y) <= 65504.f && fabsf(fb.x) <= 65504.f && fabsf(fb.y) <= 65504.f))
+        atomicOr(status, BHD_DEV_ACTIVATION_RANGE);
+    __half* dst = out + uint64_t(slot) * K + k;
+    *reinterpret_cast<__half2*>(dst) = a;
+    *reinterpret_cast<__half2*>(dst + 2) = b;
+    // remainder x - hi, so that hi + lo carries 22 bits
+    __half* dlo = out + uint64_t(lo_row_offset + slot) * K + k;
+    *reinterpret_cast<__half2*>(dlo) = __floats2half2_rn(v.x - fa.x, v.y - fa.y);
+    *reinterpret_cast<__half2*>(dlo + 2) = __floats2half2_rn(v.z - fb.x, v.w - fb.y);
+}
+
+bool encode_weight_map(bhd_ctx* ctx, const bhd_weight* w, CUtensorMap* map) {
+    const cuuint64_t dims[2] = {w->row_bytes / 2, w->rows * w->slabs};
+    const cuuint64_t strides[1] = {w->row_bytes};
+    const cuuint32_t box[2] = {PACK_ROW / 2, TILE_N};
+    const cuuint32_t estr[2] = {1, 1};
+    return reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->dev, dims, strides, box, estr,
+                                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool bhd_moe_tcgen05_usable(const bhd_ctx* ctx, const bhd_weight* w) {
+    return ctx->tmap_encode && w->kind == BHD_TYPE_Q8_0 && w->row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(w->dev) & 15) == 0 &&
+           w->cols % 32 == 0 && w->cols > 0 && w->rows * w->slabs <= 0x7fffffffull;
+}
+
+int32_t bhd_launch_moe_slots_f16(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
+                                 const float* src, const float* src2, uint32_t K, uint32_t max_slots, void* out16,
+                                 cudaStream_t s) {
+    if (max_slots == 0) return BHD_OK;
+    // out16 holds 2 * max_slots rows: the hi halves, then the lo halves
+    k_moe_slots_f16<<<dim3((K / 4 + 127) / 128, max_slots), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, top_k,
+                                                                         src, src2, K, static_cast<__half*>(out16), max_slots,
+                                                                         ctx->status_dev);
+    BHD_LAUNCHED(ctx, mode ? "expert gating kernel" : "token gather kernel");
+    return BHD_OK;
+}
+
+// Grouped expert matmul on the tensor cores for the groups of one size class (9..32 routes):
+// one CTA per (group, 128-row tile of the expert matrix[, gate|up]).
+int32_t bhd_launch_moe_grouped_tcgen05(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr,
+                                       const void* groups, const int32_t* glist, uint32_t cls, uint32_t group_bound,
+                                       const void* x16, uint32_t x_rows, float* out0, float* out1, const float* slot_weight,
+                                       cudaStream_t s) {
+    if (group_bound == 0) return BHD_OK;
+    const uint32_t K = uint32_t(w0->cols), N = uint32_t(w0->rows), tn = 32, stages = 3;
+    const size_t dyn = 1024 + 2 * size_t(PACK_BYTES) + size_t(stages) * (2 * A_BYTES + 2 * tn * 128u);
+    CUtensorMap m0, m1, mx;
+    if (!encode_weight_map(ctx, w0, &m0) || !encode_weight_map(ctx, w1 ? w1 : w0, &m1))
+        return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the expert tensor map", bhd_device_name());
+    const cuuint64_t dims[2] = {K, 2 * uint64_t(x_rows)};  // hi rows, then lo rows
+    const cuuint64_t strides[1] = {uint64_t(K) * 2};
+    const cuuint32_t box[2] = {SLICE_K, tn};
+    const cuuint32_t estr[2] = {1, 1};
+    if (reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode)(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x16), dims, strides, box,
+                                                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the activation tensor map", bhd_device_name());
+    static int cached_device = -1;
+    if (cached_device != ctx->device) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
+                 "raising the shared memory limit");
+        cached_device = ctx->device;
+    }
+    GemmParams p;
+    p.y = out0;
+    p.status = ctx->status_dev;
+    p.n_rows = N;
+    p.row_base = 0;
+    p.m = 0;
+    p.k = K;
+    p.tn = tn;
+    p.stages = stages;
+    p.hdr = static_cast<const MoeHeader*>(hdr);
+    p.groups = static_cast<const MoeGroup*>(groups);
+    p.glist = glist;
+    p.cls = cls;
+    p.y1 = out1;
+    p.slot_weight = slot_weight;
+    p.split = 1;
+    p.lo_row_offset = x_rows;
+    k_gemm_q8_tcgen05<true><<<dim3((N + TILE_N - 1) / TILE_N, group_bound, w1 ? 2 : 1), THREADS, dyn, s>>>(m0, m1, mx, p);
+    BHD_LAUNCHED(ctx, "tcgen05 grouped expert kernel");
     return BHD_OK;
 }

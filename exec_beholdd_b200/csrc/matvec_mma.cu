@@ -510,15 +510,6 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
 // pick the column layout: up to 8 vectors use split (hi + lo) activations, larger groups use
 // plain fp16 activations with 8 vectors per n-tile.
 
-struct MoeGroup {
-    int32_t expert_local, slot0, nb, cls;
-    uint32_t blob_x, blob_a;  // offsets of the packed inputs of gate/up and of down, in 256-byte units
-    uint32_t pad0, pad1;
-};
-struct MoeHeader {
-    uint32_t gcount[4];
-    uint32_t total_groups, local_routes, pad0, pad1;
-};
 __host__ __device__ constexpr int moe_nt(int cls) { return cls == 0 ? 1 : (cls == 3 ? 4 : 2); }
 __host__ __device__ constexpr bool moe_split(int cls) { return cls < 2; }
 __host__ __device__ constexpr int moe_cls(int nb) { return nb <= 4 ? 0 : (nb <= 8 ? 1 : (nb <= 16 ? 2 : 3)); }
@@ -617,10 +608,11 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
 __global__ void k_moe_pack(int mode, const MoeHeader* __restrict__ hdr, const MoeGroup* __restrict__ groups,
                            const int32_t* __restrict__ slot_route, uint32_t top_k, const float* __restrict__ src,
                            const float* __restrict__ src2, uint32_t K, uint8_t* __restrict__ blob,
-                           uint32_t* __restrict__ status) {
+                           uint32_t* __restrict__ status, int skip_from_cls) {
     __shared__ float stepsum[STEPS][8];
     if (blockIdx.y >= hdr->total_groups) return;
     const MoeGroup g = groups[blockIdx.y];
+    if (g.cls >= skip_from_cls) return;  // those groups take the tcgen05 path, which reads plain fp16 rows
     const int nt = moe_nt(g.cls);
     const bool split = moe_split(g.cls);
     const int col = (threadIdx.x & 31) >> 2;
@@ -850,8 +842,10 @@ int32_t launch_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1,
     return BHD_OK;
 }
 
+// x16: fp16 rows in slot order for the tensor-core path (nullptr: every class uses the mma.sync kernel).
 int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, MoeRun run, const int32_t* glist,
-                           uint32_t gmax, uint32_t tiles, uint32_t n_routes, uint32_t n_local, cudaStream_t s) {
+                           uint32_t gmax, uint32_t tiles, uint32_t n_routes, uint32_t n_local, cudaStream_t s,
+                           const void* x16 = nullptr) {
     // A class can only occur when there are enough routes for its smallest group.
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
     int32_t st = BHD_OK;
@@ -863,12 +857,17 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
         if ((st = launch_grouped<1>(ctx, w0, w1, run, tiles, small < n_routes / 5 ? small : n_routes / 5, s)) != BHD_OK) return st;
     }
     if (n_routes >= 9) {
+        const uint32_t bound = small < n_routes / 9 ? small : n_routes / 9;
         run.glist = glist + 2 * gmax;
-        if ((st = launch_grouped<2>(ctx, w0, w1, run, tiles, small < n_routes / 9 ? small : n_routes / 9, s)) != BHD_OK) return st;
+        if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 2, bound, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
+        else st = launch_grouped<2>(ctx, w0, w1, run, tiles, bound, s);
+        if (st != BHD_OK) return st;
     }
     if (n_routes >= 17) {
         run.glist = glist + 3 * gmax;
-        if ((st = launch_grouped<3>(ctx, w0, w1, run, tiles, n_routes / 17, s)) != BHD_OK) return st;
+        if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 3, n_routes / 17, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
+        else st = launch_grouped<3>(ctx, w0, w1, run, tiles, n_routes / 17, s);
+        if (st != BHD_OK) return st;
     }
     return BHD_OK;
 }
@@ -904,6 +903,8 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const size_t o_bitmap = take(4 * size_t(E) * words), o_prefix = take(4 * size_t(E) * words);
     const size_t o_g = take(4 * size_t(R) * ff), o_u = take(4 * size_t(R) * ff), o_d = take(4 * size_t(R) * dim);
     const size_t o_bx = take(nt_sum * unit * chunks_x), o_ba = take(nt_sum * unit * chunks_a);
+    const bool tc = R >= 9 && R <= 65535 && bhd_moe_tcgen05_usable(ctx, gate) && bhd_moe_tcgen05_usable(ctx, up) && bhd_moe_tcgen05_usable(ctx, down);
+    const size_t o_x16 = take(tc ? 4 * size_t(R) * dim : 0), o_a16 = take(tc ? 4 * size_t(R) * ff : 0);  // hi + lo fp16 rows
     int32_t st = bhd_ensure_workspace(ctx, off, s);
     if (st != BHD_OK) return st;
     uint8_t* ws = ctx->workspace;
@@ -918,7 +919,12 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     float* dbuf = reinterpret_cast<float*>(ws + o_d);
 
     const size_t plan_smem = size_t(E) * words * 8;
-    const int plan_on_chip = plan_smem <= 40 * 1024;
+    const int plan_on_chip = plan_smem <= 160 * 1024;
+    static int plan_device = -1;
+    if (plan_device != ctx->device) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_moe_plan, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), "raising the shared memory limit");
+        plan_device = ctx->device;
+    }
     k_moe_plan<<<1, R <= 256 ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
                                   reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
                                   route_slot, slot_route, slot_weight, groups, glist, gmax,
@@ -926,9 +932,11 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
                                   ctx->status_dev, plan_on_chip);
     BHD_LAUNCHED(ctx, "route planning kernel");
     const uint32_t group_bound = gmax < R ? gmax : R;
+    const int skip_cls = tc ? 2 : 4;  // groups of 9+ routes go to the tensor-core kernel
     k_moe_pack<<<dim3(chunks_x, group_bound), STEPS * 32, 0, s>>>(0, hdr, groups, slot_route, top_k, x, nullptr, uint32_t(dim),
-                                                                  ws + o_bx, ctx->status_dev);
+                                                                  ws + o_bx, ctx->status_dev, skip_cls);
     BHD_LAUNCHED(ctx, "token gather and packing kernel");
+    if (tc && (st = bhd_launch_moe_slots_f16(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_x16, s)) != BHD_OK) return st;
 
     MoeRun run;
     run.hdr = hdr;
@@ -943,11 +951,12 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     run.rows = uint32_t(ff);
     run.chunks = chunks_x;
     run.use_blob_a = 0;
-    st = launch_grouped_all(ctx, gate, up, run, glist, gmax, uint32_t((ff + TILE_ROWS - 1) / TILE_ROWS), R, E, s);
+    st = launch_grouped_all(ctx, gate, up, run, glist, gmax, uint32_t((ff + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_x16 : nullptr);
     if (st != BHD_OK) return st;
     k_moe_pack<<<dim3(chunks_a, group_bound), STEPS * 32, 0, s>>>(1, hdr, groups, slot_route, top_k, gbuf, ubuf, uint32_t(ff),
-                                                                  ws + o_ba, ctx->status_dev);
+                                                                  ws + o_ba, ctx->status_dev, skip_cls);
     BHD_LAUNCHED(ctx, "gating and packing kernel");
+    if (tc && (st = bhd_launch_moe_slots_f16(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_a16, s)) != BHD_OK) return st;
     // down: [dim x ff] per expert, each output row scaled by its route weight
     run.blob = ws + o_ba;
     run.out0 = dbuf;
@@ -956,7 +965,7 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     run.rows = uint32_t(dim);
     run.chunks = chunks_a;
     run.use_blob_a = 1;
-    st = launch_grouped_all(ctx, down, nullptr, run, glist, gmax, uint32_t((dim + TILE_ROWS - 1) / TILE_ROWS), R, E, s);
+    st = launch_grouped_all(ctx, down, nullptr, run, glist, gmax, uint32_t((dim + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_a16 : nullptr);
     if (st != BHD_OK) return st;
     const uint64_t n = T * dim;
     k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, route_slot, y, n, uint32_t(dim), top_k, accumulate);

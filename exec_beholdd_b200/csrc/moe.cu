@@ -100,54 +100,74 @@ __global__ void k_route_select(float* __restrict__ probs, uint32_t n_experts, ui
 
 // Router logits for an F32 router in the CPU's summation order, fast: logits[t][e] is one f32
 // accumulator walked over the columns left to right with separately rounded product and sum
-// (crates/beholdd-backend/src/cpu.rs:198-218), so only the additions are sequential. Four
-// loader warps form the products w[e][c] * x[c] of a 32-expert x 128-column tile in shared
-// memory (coalesced, double buffered) while each lane of warp 0 adds the products of its own
-// expert in column order. Bit-identical to the order-exact matvec kernel.
-__global__ void __launch_bounds__(160) k_router_logits_f32(const float* __restrict__ w, uint32_t n_experts, uint32_t dim,
-                                                           const float* __restrict__ x, float* __restrict__ out) {
-    __shared__ float prod[2][32][129];
+// (crates/beholdd-backend/src/cpu.rs:198-218), so only the additions are sequential. A CTA owns
+// 32 experts x up to 8 positions; all threads stream 128-column tiles of the router weights and
+// of the activations into shared memory with cp.async (4 tiles in flight), and warp t walks the
+// tile for position t, lane e adding the products of expert e in column order. Bit-identical to
+// the order-exact matvec kernel.
+constexpr int RT_TOK = 8, RT_COLS = 128, RT_BUF = 4;
+constexpr int RT_W_FLOATS = RT_COLS * 33, RT_X_FLOATS = RT_TOK * RT_COLS;
+constexpr size_t RT_SMEM = size_t(RT_BUF) * (RT_W_FLOATS + RT_X_FLOATS) * sizeof(float);
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(256) k_router_logits_f32(const float* __restrict__ w, uint32_t n_experts, uint32_t dim,
+                                                           const float* __restrict__ x, uint32_t n_positions,
+                                                           float* __restrict__ out) {
+    extern __shared__ float rt_smem[];
+    float* ws = rt_smem;                          // [buf][col][33]: expert-minor, so lane e reads bank e + col
+    float* xs = rt_smem + RT_BUF * RT_W_FLOATS;   // [buf][position][col]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t e0 = blockIdx.x * 32, t = blockIdx.y;
-    const float* xv = x + uint64_t(t) * dim;
-    const uint32_t tiles = (dim + 127) / 128;
-    auto load = [&](uint32_t tile, int buf) {  // loader warps 1..4: eight experts each
-        const uint32_t c0 = tile * 128;
+    const uint32_t e0 = blockIdx.x * 32, t0 = blockIdx.y * RT_TOK;
+    const uint32_t tiles = (dim + RT_COLS - 1) / RT_COLS;
+    auto load = [&](uint32_t tile, int buf) {
+        const uint32_t c0 = tile * RT_COLS;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const uint32_t row = (warp - 1) * 8 + r, e = e0 + row;
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t idx = threadIdx.x + 256 * i, e = idx >> 7, c = idx & 127;
+            float* dst = ws + buf * RT_W_FLOATS + c * 33 + e;
+            if (e0 + e < n_experts && c0 + c < dim) cp_async4(dst, w + uint64_t(e0 + e) * dim + c0 + c);
+            else *dst = 0.0f;
+        }
 #pragma unroll
-            for (int seg = 0; seg < 4; ++seg) {
-                const uint32_t c = c0 + seg * 32 + lane;
-                float v = 0.0f;
-                if (e < n_experts && c < dim) v = __fmul_rn(w[uint64_t(e) * dim + c], xv[c]);
-                prod[buf][row][seg * 32 + lane] = v;
-            }
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t idx = threadIdx.x + 256 * i, t = idx >> 7, c = idx & 127;
+            float* dst = xs + buf * RT_X_FLOATS + t * RT_COLS + c;
+            if (t0 + t < n_positions && c0 + c < dim) cp_async4(dst, x + uint64_t(t0 + t) * dim + c0 + c);
+            else *dst = 0.0f;
         }
     };
-    if (warp > 0) load(0, 0);
-    __syncthreads();
+    for (uint32_t i = 0; i < RT_BUF - 1; ++i) {
+        if (i < tiles) load(i, i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     float acc = 0.0f;
+    const bool chain = t0 + warp < n_positions;  // warp t walks position t0 + t
     for (uint32_t tile = 0; tile < tiles; ++tile) {
-        const int buf = tile & 1;
-        if (warp > 0) {
-            if (tile + 1 < tiles) load(tile + 1, buf ^ 1);
-        } else {
-            const uint32_t n = min(128u, dim - tile * 128);
-            const float* mine = prod[buf][lane];
+        const int buf = tile % RT_BUF;
+        if (tile + RT_BUF - 1 < tiles) load(tile + RT_BUF - 1, (tile + RT_BUF - 1) % RT_BUF);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(RT_BUF - 1) : "memory");
+        __syncthreads();
+        if (chain) {
+            const uint32_t n = min(uint32_t(RT_COLS), dim - tile * RT_COLS);
+            const float* wt = ws + buf * RT_W_FLOATS + lane;
+            const float* xt = xs + buf * RT_X_FLOATS + warp * RT_COLS;
             uint32_t c = 0;
-            for (; c + 16 <= n; c += 16) {  // loads first, then the ordered additions
+            for (; c + 16 <= n; c += 16) {  // products first, then the ordered additions
                 float v[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = mine[c + i];
+                for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(wt[(c + i) * 33], xt[c + i]);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc = __fadd_rn(acc, v[i]);
             }
-            for (; c < n; ++c) acc = __fadd_rn(acc, mine[c]);
+            for (; c < n; ++c) acc = __fadd_rn(acc, __fmul_rn(wt[c * 33], xt[c]));
         }
         __syncthreads();
     }
-    if (warp == 0 && e0 + lane < n_experts) out[uint64_t(t) * n_experts + e0 + lane] = acc;
+    if (chain && e0 + lane < n_experts) out[uint64_t(t0 + warp) * n_experts + e0 + lane] = acc;
 }
 
 // ---- general expert kernels (any dim / expert_ff that are whole Q8_0 blocks) -----------
@@ -272,9 +292,16 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     }
     if (counts_dev) BHD_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, n_experts * sizeof(int32_t), s), "clearing expert counts");
     // Router logits in the CPU's summation order (forward.rs:1330-1336 -> cpu.rs:198-218).
-    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535) {
-        k_router_logits_f32<<<dim3(unsigned((n_experts + 31) / 32), unsigned(n_positions)), 160, 0, s>>>(
-            reinterpret_cast<const float*>(router->dev), uint32_t(n_experts), uint32_t(router->cols), x_dev, probs);
+    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535 * RT_TOK) {
+        static int cached_device = -1;
+        if (cached_device != ctx->device) {
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RT_SMEM)),
+                     "raising the shared memory limit");
+            cached_device = ctx->device;
+        }
+        k_router_logits_f32<<<dim3(unsigned((n_experts + 31) / 32), unsigned((n_positions + RT_TOK - 1) / RT_TOK)), 256, RT_SMEM, s>>>(
+            reinterpret_cast<const float*>(router->dev), uint32_t(n_experts), uint32_t(router->cols), x_dev,
+            uint32_t(n_positions), probs);
         BHD_LAUNCHED(ctx, "router logits kernel");
     } else {
         const int32_t st = bhd_launch_matvec_strict(ctx, router, 0, x_dev, probs, uint32_t(n_positions), 1.0f, 0, s);
