@@ -20,6 +20,8 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
                                    cudaStream_t s, bool* handled);
 int32_t bhd_launch_matvec_decode(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                  uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
+int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
+                                    uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
 
 int32_t bhd_fail(bhd_ctx* ctx, int32_t status, const char* fmt, ...) {
     if (ctx) {
@@ -317,6 +319,10 @@ int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float
     if (batch == 0 || w->rows == 0) return BHD_OK;
     cudaStream_t s = cudaStream_t(stream);
     bool handled = false;
+    if (batch <= 2) {
+        const int32_t is = bhd_launch_matvec_decode_i8(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s, &handled);
+        if (is != BHD_OK || handled) return is;
+    }
     if (batch <= 4) {
         const int32_t ds = bhd_launch_matvec_decode(ctx, w, slab, x_dev, y_dev, batch, scale, accumulate, s, &handled);
         if (ds != BHD_OK || handled) return ds;

@@ -35,8 +35,9 @@ constexpr int SLICE_K = 64;            // columns per fp16 stage (one 128-byte s
 constexpr int PACK_ROW = 272;          // packed bytes per row per chunk
 constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
-constexpr int CONVERTERS = 128;        // groups of 128 converter threads (one per weight row) take alternating slices
-constexpr int THREADS = 64 + CONVERTERS;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2.. convert, warps 2-5 also epilogue
+// warp 0 TMA, warp 1 MMA + TMEM, then NG groups of four converter warps (one thread per weight row) that take
+// alternating slices; the first group is also the epilogue.
+__host__ __device__ constexpr int gemm_threads(int ng) { return 64 + 128 * ng; }
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -139,6 +140,8 @@ __global__ void k_f32_to_f16(const float* __restrict__ x, __half* __restrict__ o
     *reinterpret_cast<__half2*>(out + i + 2) = b;
 }
 
+constexpr int PLAIN_NG = 1, GROUPED_NG = 2;  // converter groups per instance (measured)
+
 struct GemmParams {
     float* y;            // [M x N]
     uint32_t* status;
@@ -164,8 +167,8 @@ struct GemmParams {
 
 // GROUPED = false: plain prefill matmul. GROUPED = true: routed experts (group list, two weight tensors, split
 // operands); compile-time so that the prefill instance carries none of the grouped code.
-template <bool GROUPED>
-__global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_constant__ CUtensorMap tmap_w0,
+template <bool GROUPED, int NG>
+__global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const __grid_constant__ CUtensorMap tmap_w0,
                                                                 const __grid_constant__ CUtensorMap tmap_w1,
                                                                 const __grid_constant__ CUtensorMap tmap_x,
                                                                 const GemmParams p) {
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_con
     const uint32_t S = p.stages;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], CONVERTERS / 32); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 4 * NG); }
         for (uint32_t i = 0; i < S; ++i) { mbar_init(&a_full[i], 4); mbar_init(&b_full[i], 1); mbar_init(&st_empty[i], 1); }
         mbar_init(&tmem_full, 1);
         abort_flag = 0;
@@ -262,7 +265,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_tcgen05(const __grid_con
             const uint32_t pb = c & 1;
             if (aborted() || !mbar_wait(&pk_full[pb], (c >> 1) & 1)) { give_up(); ok = false; break; }
             const uint32_t src_row = pack_addr + pb * PACK_BYTES + row * PACK_ROW;
-            for (uint32_t kb = grp; kb < 4; kb += CONVERTERS / 128) {
+            for (uint32_t kb = grp; kb < 4; kb += NG) {
                 const uint32_t it = c * 4 + kb;
                 if (it >= slices) break;
                 const uint32_t s = it % S;
@@ -403,7 +406,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     }
     static int cached_device = -1;
     if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<false, PLAIN_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
                  "raising the shared memory limit");
         cached_device = ctx->device;
     }
@@ -424,7 +427,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     p.slot_weight = nullptr;
     p.split = 0;
     p.lo_row_offset = 0;
-    k_gemm_q8_tcgen05<false><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), THREADS, dyn, s>>>(map_w, map_w, map_x, p);
+    k_gemm_q8_tcgen05<false, PLAIN_NG><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), gemm_threads(PLAIN_NG), dyn, s>>>(map_w, map_w, map_x, p);
     BHD_LAUNCHED(ctx, "tcgen05 matmul kernel");
     *handled = true;
     return BHD_OK;
@@ -519,7 +522,7 @@ int32_t bhd_launch_moe_grouped_tcgen05(bhd_ctx* ctx, const bhd_weight* w0, const
         return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the activation tensor map", bhd_device_name());
     static int cached_device = -1;
     if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<true, GROUPED_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
                  "raising the shared memory limit");
         cached_device = ctx->device;
     }
@@ -540,7 +543,7 @@ int32_t bhd_launch_moe_grouped_tcgen05(bhd_ctx* ctx, const bhd_weight* w0, const
     p.slot_weight = slot_weight;
     p.split = 1;
     p.lo_row_offset = x_rows;
-    k_gemm_q8_tcgen05<true><<<dim3((N + TILE_N - 1) / TILE_N, group_bound, w1 ? 2 : 1), THREADS, dyn, s>>>(m0, m1, mx, p);
+    k_gemm_q8_tcgen05<true, GROUPED_NG><<<dim3((N + TILE_N - 1) / TILE_N, group_bound, w1 ? 2 : 1), gemm_threads(GROUPED_NG), dyn, s>>>(m0, m1, mx, p);
     BHD_LAUNCHED(ctx, "tcgen05 grouped expert kernel");
     return BHD_OK;
 }
