@@ -22,13 +22,16 @@
 
 namespace {
 
-constexpr int ROWS = 16, WARPS = 4, CHUNK_K = 256, RING = 2;
+constexpr int ROWS = 16, WARPS = 4, CHUNK_K = 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 template <uint32_t KIND> struct Geo;
-template <> struct Geo<BHD_TYPE_Q8_0> { static constexpr int BOX = 272, GROUPS = 8; };
-template <> struct Geo<BHD_TYPE_Q4_K> { static constexpr int BOX = 144, GROUPS = 8; };
-template <> struct Geo<BHD_TYPE_Q6_K> { static constexpr int BOX = 240, GROUPS = 16; };
+// RING: stages per warp. Four stages of Q4_K hold all 4096 columns of a projection, so a CTA
+// that starts early (programmatic dependent launch) has requested all its weights before the
+// activations exist; the wider formats keep two stages to leave room for six CTAs per SM.
+template <> struct Geo<BHD_TYPE_Q8_0> { static constexpr int BOX = 272, GROUPS = 8, RING = 2; };
+template <> struct Geo<BHD_TYPE_Q4_K> { static constexpr int BOX = 144, GROUPS = 8, RING = 4; };
+template <> struct Geo<BHD_TYPE_Q6_K> { static constexpr int BOX = 240, GROUPS = 16, RING = 2; };
 __host__ __device__ constexpr int igroups(uint32_t kind) { return kind == BHD_TYPE_Q6_K ? 16 : 8; }
 
 // Packed activations of one chunk: [group][vector][digit][t] 8-byte B fragments (b0, b1), then
@@ -115,11 +118,21 @@ __device__ __forceinline__ uint2 lds64(uint32_t a) {
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
+// Packed activations are rewritten by every launch while CTAs of the next one may already be
+// resident, so they are read past L1.
+__device__ __forceinline__ uint2 ldg64_cg(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
+// Programmatic dependent launch (a no-op when the kernel was launched without the attribute).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ float h2f(uint32_t h) { return __half2float(__ushort_as_half(uint16_t(h))); }
 __device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.0f; }
 
@@ -130,6 +143,11 @@ __global__ void k_pack_x_i8(uint32_t kind, const float* __restrict__ x, uint32_t
                             uint8_t* __restrict__ blob, uint32_t* __restrict__ status) {
     const int chunk = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int groups = igroups(kind), per = 256 / groups;  // columns per group: 32 or 16
+    // Programmatic dependent launch: let the matvec kernel that follows start its weight
+    // prefetch now; wait for whatever preceded this launch (it may have produced x, and the
+    // previous matvec may still be reading the blob) before touching memory.
+    pdl_launch_dependents();
+    pdl_wait();
     uint8_t* cb = blob + uint64_t(chunk) * iblob_bytes(kind, nb);
     float2* meta = reinterpret_cast<float2*>(cb + iblob_frag_bytes(kind, nb));
     for (int item = warp; item < groups * int(nb); item += blockDim.x >> 5) {
@@ -185,20 +203,18 @@ __device__ __forceinline__ int tile_row(int m) {
 
 // NB vectors; GPT = 4 / NB scale groups share one accumulator tile; lane-in-quad t owns tile
 // columns (2t, 2t+1) = (group gl = t / NB, vector v = t % NB) x (digit 0, digit 1).
-template <uint32_t KIND, int NB>
+template <uint32_t KIND, int NB, int RING>
 __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_constant__ CUtensorMap tmap, const DecodeI8Params p) {
     constexpr int BOX = Geo<KIND>::BOX, GROUPS = Geo<KIND>::GROUPS, GPT = 4 / NB, TILES = GROUPS / GPT;
     constexpr int W_BYTES = ROWS * BOX, X_BYTES = iblob_bytes(KIND, NB), FRAG = iblob_frag_bytes(KIND, NB);
-    constexpr int STAGE = (W_BYTES + X_BYTES + 127) / 128 * 128;
+    constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     __shared__ uint64_t bars[WARPS][RING];
     __shared__ float red[WARPS][ROWS][NB];
-    __shared__ __align__(16) uint8_t zero_area[GROUPS * NB * 64 + 64];  // what inactive lanes feed the MMA
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t tile = blockIdx.x;
-    for (int i = threadIdx.x; i < int(sizeof(zero_area) / 4); i += blockDim.x) reinterpret_cast<uint32_t*>(zero_area)[i] = 0u;
     if (lane == 0) {
         for (int i = 0; i < RING; ++i) mbar_init(&bars[warp][i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -206,18 +222,22 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     __syncthreads();
 
     uint8_t* ring = smem + warp * (RING * STAGE);
-    const uint32_t ring32 = smem_u32(ring), zeros32 = smem_u32(zero_area);
+    const uint32_t ring32 = smem_u32(ring);
     const uint32_t my_chunks = p.chunks > uint32_t(warp) ? (p.chunks - warp + WARPS - 1) / WARPS : 0;
-    auto issue = [&](uint32_t i) {  // lane 0 only: stage the warp's i-th chunk
+    // lane 0 only: stage the weights of the warp's i-th chunk.
+    auto issue_w = [&](uint32_t i) {
         const uint32_t chunk = warp + i * WARPS, slot = i % RING;
-        uint8_t* dst = ring + slot * STAGE;
-        mbar_arrive_expect_tx(&bars[warp][slot], W_BYTES + X_BYTES);
+        mbar_arrive_expect_tx(&bars[warp][slot], W_BYTES);
         const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : uint32_t(BOX) * chunk;
-        tma_load_2d(dst, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
-        bulk_load_1d(dst + W_BYTES, p.blob + uint64_t(chunk) * X_BYTES, X_BYTES, &bars[warp][slot]);
+        tma_load_2d(ring + slot * STAGE, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
     };
+    // Weights are never written by a preceding kernel, so their first stages are requested
+    // before waiting for the grids this launch depends on (the packer, and before it whatever
+    // produced x and y); everything else happens after the wait.
     if (lane == 0)
-        for (uint32_t i = 0; i < my_chunks && i < RING; ++i) issue(i);
+        for (uint32_t i = 0; i < my_chunks && i < RING; ++i) issue_w(i);
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int r0 = tile_row<KIND>(g), r1 = tile_row<KIND>(g + 8);
     const int gl = t / NB, v = t % NB;                  // what this lane's accumulator columns mean
@@ -225,19 +245,41 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     const int boff = bv * 64 + (g & 1) * 32 + t * 8;    // fragment offset within a group
     float tot0 = 0.f, tot1 = 0.f;
 
+    // The lane's share of a chunk's packed activations, straight from global memory (L2): the
+    // B fragments of the TILES groups its MMA column stands for, and (2^(e-14), sum) of the
+    // TILES groups its accumulator columns stand for. Loaded one chunk ahead.
+    uint2 bq[TILES], bq_next[TILES];
+    float2 mq[TILES], mq_next[TILES];
+    auto load_x = [&](uint32_t chunk, uint2 (&q)[TILES], float2 (&m)[TILES]) {
+        const uint8_t* cb = p.blob + uint64_t(chunk) * X_BYTES;
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl) {
+            q[tl] = ldg64_cg(cb + (tl * GPT + bgl) * (64 * NB) + boff);
+            const uint2 mm = ldg64_cg(cb + FRAG + 8 * ((tl * GPT + gl) * NB + v));
+            m[tl] = make_float2(__uint_as_float(mm.x), __uint_as_float(mm.y));
+        }
+    };
+    if (my_chunks > 0) load_x(warp, bq_next, mq_next);
+
     for (uint32_t i = 0; i < my_chunks; ++i) {
         const uint32_t slot = i % RING, chunk = warp + i * WARPS;
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl) {
+            bq[tl] = bq_next[tl];
+            mq[tl] = mq_next[tl];
+        }
+        if (i + 1 < my_chunks) load_x(chunk + WARPS, bq_next, mq_next);
         if (!mbar_wait(&bars[warp][slot], (i / RING) & 1)) {
             if (lane == 0) atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT);
             break;
         }
         const uint32_t st = ring32 + slot * STAGE;
-        const uint32_t w0 = st + r0 * BOX, w1 = st + r1 * BOX, xb = st + W_BYTES;
-        const uint32_t meta = xb + FRAG + 8 * v;  // + 8 * NB * group: (2^(e-14), sum of the group's activations)
-        uint32_t bsrc[GPT];  // real fragments when the group is the one this lane's column stands for, zeros otherwise
-#pragma unroll
-        for (int c = 0; c < GPT; ++c) bsrc[c] = (c == bgl) ? xb + boff : zeros32;
-        auto bfrag = [&](int grp) -> uint2 { return lds64(bsrc[grp % GPT] + grp * (64 * NB)); };
+        const uint32_t w0 = st + r0 * BOX, w1 = st + r1 * BOX;
+        // real fragment when the group is one this lane's MMA column stands for, zeros otherwise
+        auto bfrag = [&](int grp) -> uint2 {
+            const bool on = (grp % GPT) == bgl;
+            return make_uint2(on ? bq[grp / GPT].x : 0u, on ? bq[grp / GPT].y : 0u);
+        };
         int acc[TILES][4];
 
         if constexpr (KIND == BHD_TYPE_Q8_0) {
@@ -261,7 +303,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
 #pragma unroll
             for (int tl = 0; tl < TILES; ++tl) {
                 const int blk = tl * GPT + gl;
-                const float2 m = ldsf2(meta + 8 * NB * blk);
+                const float2 m = mq[tl];
                 const float d0 = h2f(lds16(w0 + 34 * blk)) * m.x, d1 = h2f(lds16(w1 + 34 * blk)) * m.x;
                 tot0 = fmaf(d0, float(acc[tl][0] * 256 + acc[tl][1]), tot0);
                 tot1 = fmaf(d1, float(acc[tl][2] * 256 + acc[tl][3]), tot1);
@@ -305,7 +347,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 const uint32_t sh = 8u * uint32_t(j & 3);
                 const float sc0 = u2f((f0[2 * hi4] >> sh) & 0xffu), mn0 = u2f((f0[2 * hi4 + 1] >> sh) & 0xffu);
                 const float sc1 = u2f((f1[2 * hi4] >> sh) & 0xffu), mn1 = u2f((f1[2 * hi4 + 1] >> sh) & 0xffu);
-                const float2 m = ldsf2(meta + 8 * NB * j);
+                const float2 m = mq[tl];
                 tot0 += fmaf(d0 * sc0 * m.x, float(acc[tl][0] * 256 + acc[tl][1]), -(m0 * mn0) * m.y);
                 tot1 += fmaf(d1 * sc1 * m.x, float(acc[tl][2] * 256 + acc[tl][3]), -(m1 * mn1) * m.y);
             }
@@ -348,14 +390,14 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 const uint32_t sw0 = word(b0, 192 + (s & ~3)), sw1 = word(b1, 192 + (s & ~3));
                 const float s0 = d0 * float(int8_t((sw0 >> (8 * (s & 3))) & 0xffu));
                 const float s1 = d1 * float(int8_t((sw1 >> (8 * (s & 3))) & 0xffu));
-                const float2 m = ldsf2(meta + 8 * NB * s);
+                const float2 m = mq[tl];
                 // codes are unsigned 0..63; the value is code - 32
                 tot0 = fmaf(s0, fmaf(m.x, float(acc[tl][0] * 256 + acc[tl][1]), -32.f * m.y), tot0);
                 tot1 = fmaf(s1, fmaf(m.x, float(acc[tl][2] * 256 + acc[tl][3]), -32.f * m.y), tot1);
             }
         }
         __syncwarp();
-        if (lane == 0 && i + RING < my_chunks) issue(i + RING);
+        if (lane == 0 && i + RING < my_chunks) issue_w(i + RING);
     }
 
     // Sum over the groups handled by different lanes of the quad (same vector v), then over warps.
@@ -383,12 +425,12 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     }
 }
 
-template <uint32_t KIND, int NB>
+template <uint32_t KIND, int NB, int RING = Geo<KIND>::RING>
 int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, uint32_t tiles, cudaStream_t s) {
-    constexpr int W_BYTES = ROWS * Geo<KIND>::BOX, X_BYTES = iblob_bytes(KIND, NB);
-    constexpr int STAGE = (W_BYTES + X_BYTES + 127) / 128 * 128;
+    constexpr int W_BYTES = ROWS * Geo<KIND>::BOX;
+    constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     constexpr size_t DYN = size_t(WARPS) * RING * STAGE + 128;
-    auto kern = k_matvec_decode_i8<KIND, NB>;
+    auto kern = k_matvec_decode_i8<KIND, NB, RING>;
     static int cached_device = -1;
     if (cached_device != ctx->device) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(DYN)), "raising the shared memory limit");
@@ -396,8 +438,18 @@ int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, ui
     }
     CUtensorMap map;
     memcpy(&map, w->tmap16, sizeof(map));
-    kern<<<tiles, WARPS * 32, DYN, s>>>(map, p);
-    BHD_LAUNCHED(ctx, "integer decode matvec kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = DYN;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, map, p), "launching the integer decode matvec kernel");
+    ctx->launches += 1;
     return BHD_OK;
 }
 
@@ -415,8 +467,20 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     int32_t st = bhd_ensure_workspace(ctx, size_t(chunks) * iblob_bytes(w->kind, nb), s);
     if (st != BHD_OK) return st;
     uint8_t* blob = ctx->workspace;
-    k_pack_x_i8<<<chunks, 256, 0, s>>>(w->kind, x, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev);
-    BHD_LAUNCHED(ctx, "activation packing kernel");
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(chunks);
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_pack_x_i8, w->kind, x, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev),
+                 "launching the activation packing kernel");
+        ctx->launches += 1;
+    }
     DecodeI8Params p;
     p.blob = blob;
     p.y = y;
