@@ -23,6 +23,8 @@
 namespace {
 
 constexpr int ROWS = 16, WARPS = 4, CHUNK_K = 256;
+constexpr int CLUSTER = 4;            // CTAs that share one packing of the activations
+constexpr int MAX_X_SMEM = 16 * 1024; // packed activations a CTA may hold
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 template <uint32_t KIND> struct Geo;
@@ -30,7 +32,7 @@ template <uint32_t KIND> struct Geo;
 // that starts early (programmatic dependent launch) has requested all its weights before the
 // activations exist; the wider formats keep two stages to leave room for six CTAs per SM.
 template <> struct Geo<BHD_TYPE_Q8_0> { static constexpr int BOX = 272, GROUPS = 8, RING = 2; };
-template <> struct Geo<BHD_TYPE_Q4_K> { static constexpr int BOX = 144, GROUPS = 8, RING = 4; };
+template <> struct Geo<BHD_TYPE_Q4_K> { static constexpr int BOX = 144, GROUPS = 8, RING = 3; };
 template <> struct Geo<BHD_TYPE_Q6_K> { static constexpr int BOX = 240, GROUPS = 16, RING = 2; };
 __host__ __device__ constexpr int igroups(uint32_t kind) { return kind == BHD_TYPE_Q6_K ? 16 : 8; }
 
@@ -42,17 +44,14 @@ __host__ __device__ constexpr int iblob_bytes(uint32_t kind, int nb) {
 }
 
 // Column (within the chunk) behind k-slot `slot` (0..31) of the MMA that covers scale group
-// `grp`. Q8_0: the block's bytes in order. Q4_K: a lane's eight bytes are split over the two
-// halves of the k range. Q6_K: a k32 MMA spans two 16-column groups, the even one in slots
-// 0..15 and the odd one in slots 16..31 (slot is then relative to the pair).
-__host__ __device__ __forceinline__ int slot_column(uint32_t kind, int grp, int slot) {
-    if (kind == BHD_TYPE_Q8_0) return 32 * grp + slot;
-    if (kind == BHD_TYPE_Q4_K) {
-        const int t = (slot & 15) >> 2, i = slot & 3, hi = slot >> 4;
-        return 64 * (grp >> 1) + 32 * (grp & 1) + 8 * t + 4 * hi + i;
-    }
-    return 16 * grp + (slot & 15);  // caller passes slots 0..15 for even groups, 16..31 for odd ones
-}
+// `grp`:
+//   Q8_0: 32 * grp + slot (the block's bytes in order);
+//   Q4_K: 64 * (grp / 2) + 32 * (grp % 2) + 8 * t + 4 * hi + i with t = (slot % 16) / 4,
+//         i = slot % 4, hi = slot / 16 (a lane's eight bytes are split over the two halves of k);
+//   Q6_K: a k32 MMA spans two 16-column groups, the even one in slots 0..15 and the odd one in
+//         slots 16..31: 16 * grp + slot % 16.
+// In every format the bytes behind B-fragment registers b0 (slots 4t..4t+3) and b1 (slots
+// 16+4t..16+4t+3) of lane-in-quad t are runs of four consecutive columns.
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -82,11 +81,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
-__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
 // A unsigned (nibbles, 6-bit codes) or signed (Q8_0 quants); B always signed digits.
 template <bool A_SIGNED, bool FIRST>
 __device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
@@ -108,22 +102,30 @@ __device__ __forceinline__ uint32_t lds16(uint32_t a) {
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
     return v;
 }
-__device__ __forceinline__ float2 ldsf2(uint32_t a) {
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
-    return v;
-}
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
-// Packed activations are rewritten by every launch while CTAs of the next one may already be
-// resident, so they are read past L1.
-__device__ __forceinline__ uint2 ldg64_cg(const void* p) {
+// Distributed shared memory: the address of `local` (a shared-memory address of this CTA) in
+// the CTA of rank `rank` of the cluster, and an 8-byte load from such an address.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ uint2 ld_cluster64(uint32_t a) {
     uint2 v;
-    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    asm volatile("ld.shared::cluster.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory");
     return v;
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
@@ -136,61 +138,97 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ float h2f(uint32_t h) { return __half2float(__ushort_as_half(uint16_t(h))); }
 __device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.0f; }
 
-// ---- activation packer ----------------------------------------------------------------------
-// One CTA per chunk, one warp per scale group (looping when there are more groups than warps).
-// Lane l holds column slot l of its group (Q6_K: lanes 0..15). x [nvec x K] f32.
-__global__ void k_pack_x_i8(uint32_t kind, const float* __restrict__ x, uint32_t nvec, uint32_t nb, uint32_t K,
-                            uint8_t* __restrict__ blob, uint32_t* __restrict__ status) {
-    const int chunk = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int groups = igroups(kind), per = 256 / groups;  // columns per group: 32 or 16
-    // Programmatic dependent launch: let the matvec kernel that follows start its weight
-    // prefetch now; wait for whatever preceded this launch (it may have produced x, and the
-    // previous matvec may still be reading the blob) before touching memory.
-    pdl_launch_dependents();
-    pdl_wait();
-    uint8_t* cb = blob + uint64_t(chunk) * iblob_bytes(kind, nb);
-    float2* meta = reinterpret_cast<float2*>(cb + iblob_frag_bytes(kind, nb));
-    for (int item = warp; item < groups * int(nb); item += blockDim.x >> 5) {
-        const int grp = item / int(nb), v = item % int(nb);
-        // the slot this lane fills: Q6_K odd groups live in slots 16..31 of their MMA
-        const bool live = lane < per;
-        const int slot = (kind == BHD_TYPE_Q6_K && (grp & 1)) ? 16 + lane : lane;
-        const uint32_t k = uint32_t(chunk) * CHUNK_K + uint32_t(slot_column(kind, grp, slot));
-        float val = 0.f;
-        if (live && uint32_t(v) < nvec && k < K) val = x[uint64_t(v) * K + k];
-        if (!(fabsf(val) <= 3.0e38f)) { atomicOr(status, BHD_DEV_ACTIVATION_RANGE); val = 0.f; }  // NaN or infinity
-        float mx = fabsf(val);
+// ---- activation packer (runs inside the matvec kernel, once per cluster) --------------------
+// The CTAs of a cluster split the chunks between them; each packs its share into its own shared
+// memory and every CTA of the cluster reads the fragments it needs through distributed shared
+// memory. One quad of lanes packs one (group, vector) item: lane t of the quad holds exactly
+// the columns behind its own B-fragment registers (see slot_column), so no bytes cross lanes.
+// x [nvec x K] f32; dst = this CTA's packed chunks [n_local][iblob_bytes].
+template <uint32_t KIND, int NB>
+__device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_t nvec, uint32_t K, uint32_t chunk0,
+                                            uint32_t chunk_stride, uint32_t n_local, uint32_t chunks, uint8_t* dst,
+                                            uint32_t* status) {
+    constexpr int GROUPS = igroups(KIND), X_BYTES = iblob_bytes(KIND, NB), FRAG = iblob_frag_bytes(KIND, NB);
+    constexpr int ITEMS = GROUPS * NB;  // per chunk
+    static_assert(ITEMS % 8 == 0, "whole warps must run the same number of passes (full-mask shuffles below)");
+    const int quad = threadIdx.x >> 2, t = threadIdx.x & 3, nquads = blockDim.x >> 2;
+    const bool vec_ok = (K & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    for (uint32_t it = quad; it < n_local * ITEMS; it += nquads) {
+        const uint32_t lc = it / ITEMS, item = it % ITEMS, chunk = chunk0 + lc * chunk_stride;
+        const int grp = int(item) / NB, v = int(item) % NB;
+        // columns (within the chunk) behind b0 and b1 of this lane
+        int c0, c1;
+        if (KIND == BHD_TYPE_Q8_0) { c0 = 32 * grp + 4 * t; c1 = c0 + 16; }
+        else if (KIND == BHD_TYPE_Q4_K) { c0 = 64 * (grp >> 1) + 32 * (grp & 1) + 8 * t; c1 = c0 + 4; }
+        else { c0 = 16 * grp + 4 * t; c1 = -1; }  // Q6_K: the other half of the k range is the neighbouring group
+        float val[8];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        int ex = 0;
-        if (mx > 0.f) frexpf(mx, &ex);              // mx = m * 2^ex, m in [0.5, 1)
-        // Groups whose largest magnitude is below 2^-100 pack as zero (their power of two would overflow).
-        const float up = ex < -100 ? 0.f : ldexpf(1.0f, 14 - ex), down = ex < -100 ? 0.f : ldexpf(1.0f, ex - 14);
-        const int X = __float2int_rn(val * up);      // |X| <= 2^14
-        const int d0 = (X + 128) >> 8, d1 = X - d0 * 256;  // X = 256 * d0 + d1, both in [-128, 127]
-        float sum = float(X) * down;
+        for (int i = 0; i < 8; ++i) val[i] = 0.f;
+        const uint32_t k0 = chunk * CHUNK_K + uint32_t(c0), k1 = chunk * CHUNK_K + uint32_t(c1);
+        const bool live = chunk < chunks && uint32_t(v) < nvec;
+        const float* xr = x + uint64_t(v) * K;
+        if (live && k0 + 3 < K && vec_ok) {
+            const float4 f = *reinterpret_cast<const float4*>(xr + k0);
+            val[0] = f.x; val[1] = f.y; val[2] = f.z; val[3] = f.w;
+        } else if (live) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        // fragment [grp][v][digit][t]: bytes 0..3 = slots 4t..4t+3 (b0), bytes 4..7 = slots 16+4t.. (b1)
-        uint8_t* frag = cb + (grp * nb + v) * 64;
-        const int t = (slot & 15) >> 2, i = slot & 3, half_ = slot >> 4;
-        if (live) {
-            frag[t * 8 + half_ * 4 + i] = uint8_t(int8_t(d0));
-            frag[32 + t * 8 + half_ * 4 + i] = uint8_t(int8_t(d1));
-            if (kind == BHD_TYPE_Q6_K) {  // the other half of the k range belongs to the neighbouring group: zero here
-                frag[t * 8 + (half_ ^ 1) * 4 + i] = 0;
-                frag[32 + t * 8 + (half_ ^ 1) * 4 + i] = 0;
+            for (int i = 0; i < 4; ++i) if (k0 + i < K) val[i] = xr[k0 + i];
+        }
+        if (c1 >= 0) {
+            if (live && k1 + 3 < K && vec_ok) {
+                const float4 f = *reinterpret_cast<const float4*>(xr + k1);
+                val[4] = f.x; val[5] = f.y; val[6] = f.z; val[7] = f.w;
+            } else if (live) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k1 + i < K) val[4 + i] = xr[k1 + i];
             }
         }
-        if (lane == 0) meta[grp * nb + v] = make_float2(down, sum);
+        float mx = 0.f;
+        bool bad = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (!(fabsf(val[i]) <= 3.0e38f)) { bad = true; val[i] = 0.f; }  // NaN or infinity
+            mx = fmaxf(mx, fabsf(val[i]));
+        }
+        if (bad) atomicOr(status, BHD_DEV_ACTIVATION_RANGE);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        // mx = m * 2^ex with m in [0.5, 1): ex = biased exponent - 126. Groups whose largest
+        // magnitude is below 2^-100 (denormals included) pack as zero.
+        const int eb = int(__float_as_uint(mx) >> 23);
+        const bool tiny = eb < 27;
+        const float up = tiny ? 0.f : __uint_as_float(uint32_t(267 - eb) << 23);    // 2^(14 - ex)
+        const float down = tiny ? 0.f : __uint_as_float(uint32_t(eb - 13) << 23);   // 2^(ex - 14)
+        uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};  // digit 0 / digit 1 words for b0, b1
+        int sumX = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int X = __float2int_rn(val[i] * up);          // |X| <= 2^14
+            const int d0 = (X + 128) >> 8, d1 = X - d0 * 256;   // X = 256 * d0 + d1, both in [-128, 127]
+            w0[i >> 2] |= (uint32_t(d0) & 0xffu) << (8 * (i & 3));
+            w1[i >> 2] |= (uint32_t(d1) & 0xffu) << (8 * (i & 3));
+            sumX += X;
+        }
+        sumX += __shfl_xor_sync(0xffffffffu, sumX, 1);
+        sumX += __shfl_xor_sync(0xffffffffu, sumX, 2);
+        uint8_t* cb = dst + size_t(lc) * X_BYTES;
+        uint2* frag = reinterpret_cast<uint2*>(cb + (grp * NB + v) * 64);
+        if (KIND == BHD_TYPE_Q6_K && (grp & 1)) {  // odd groups sit in slots 16..31 of their MMA: b1
+            frag[t] = make_uint2(0u, w0[0]);
+            frag[4 + t] = make_uint2(0u, w1[0]);
+        } else {
+            frag[t] = make_uint2(w0[0], w0[1]);
+            frag[4 + t] = make_uint2(w1[0], w1[1]);
+        }
+        if (t == 0) reinterpret_cast<float2*>(cb + FRAG)[grp * NB + v] = make_float2(down, float(sumX) * down);
     }
 }
 
 struct DecodeI8Params {
-    const uint8_t* blob;
+    const float* x;
     float* y;
     uint32_t* status;
-    uint32_t rows, row_base, chunks, batch;
+    uint32_t rows, row_base, chunks, batch, cols, tiles, chunks_per_cta;
     float scale;
     int accumulate;
 };
@@ -214,7 +252,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     __shared__ float red[WARPS][ROWS][NB];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t tile = blockIdx.x;
+    const uint32_t tile = blockIdx.x;  // the grid is padded to whole clusters: tiles beyond the matrix only pack
     if (lane == 0) {
         for (int i = 0; i < RING; ++i) mbar_init(&bars[warp][i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -223,7 +261,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
 
     uint8_t* ring = smem + warp * (RING * STAGE);
     const uint32_t ring32 = smem_u32(ring);
-    const uint32_t my_chunks = p.chunks > uint32_t(warp) ? (p.chunks - warp + WARPS - 1) / WARPS : 0;
+    const uint32_t my_chunks = (tile < p.tiles && p.chunks > uint32_t(warp)) ? (p.chunks - warp + WARPS - 1) / WARPS : 0;
     // lane 0 only: stage the weights of the warp's i-th chunk.
     auto issue_w = [&](uint32_t i) {
         const uint32_t chunk = warp + i * WARPS, slot = i % RING;
@@ -232,12 +270,18 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
         tma_load_2d(ring + slot * STAGE, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
     };
     // Weights are never written by a preceding kernel, so their first stages are requested
-    // before waiting for the grids this launch depends on (the packer, and before it whatever
-    // produced x and y); everything else happens after the wait.
+    // before waiting for the grids this launch depends on (whatever produced x and y);
+    // everything else happens after the wait.
     if (lane == 0)
         for (uint32_t i = 0; i < my_chunks && i < RING; ++i) issue_w(i);
     pdl_launch_dependents();
     pdl_wait();
+
+    // Chunk c is packed by the CTA of cluster rank c % CLUSTER, as its local chunk c / CLUSTER.
+    uint8_t* xs = smem + WARPS * RING * STAGE;
+    const uint32_t rank = cluster_rank();
+    pack_chunks<KIND, NB>(p.x, p.batch, p.cols, rank, CLUSTER, p.chunks_per_cta, p.chunks, xs, p.status);
+    cluster_sync();
 
     const int r0 = tile_row<KIND>(g), r1 = tile_row<KIND>(g + 8);
     const int gl = t / NB, v = t % NB;                  // what this lane's accumulator columns mean
@@ -245,17 +289,18 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     const int boff = bv * 64 + (g & 1) * 32 + t * 8;    // fragment offset within a group
     float tot0 = 0.f, tot1 = 0.f;
 
-    // The lane's share of a chunk's packed activations, straight from global memory (L2): the
-    // B fragments of the TILES groups its MMA column stands for, and (2^(e-14), sum) of the
-    // TILES groups its accumulator columns stand for. Loaded one chunk ahead.
+    // The lane's share of a chunk's packed activations, from the shared memory of the CTA that
+    // packed it: the B fragments of the TILES groups its MMA column stands for, and
+    // (2^(e-14), sum) of the TILES groups its accumulator columns stand for. Loaded one chunk ahead.
     uint2 bq[TILES], bq_next[TILES];
     float2 mq[TILES], mq_next[TILES];
+    const uint32_t xs32 = smem_u32(xs);
     auto load_x = [&](uint32_t chunk, uint2 (&q)[TILES], float2 (&m)[TILES]) {
-        const uint8_t* cb = p.blob + uint64_t(chunk) * X_BYTES;
+        const uint32_t cb = map_to_rank(xs32 + (chunk / CLUSTER) * X_BYTES, chunk % CLUSTER);
 #pragma unroll
         for (int tl = 0; tl < TILES; ++tl) {
-            q[tl] = ldg64_cg(cb + (tl * GPT + bgl) * (64 * NB) + boff);
-            const uint2 mm = ldg64_cg(cb + FRAG + 8 * ((tl * GPT + gl) * NB + v));
+            q[tl] = ld_cluster64(cb + (tl * GPT + bgl) * (64 * NB) + boff);
+            const uint2 mm = ld_cluster64(cb + FRAG + 8 * ((tl * GPT + gl) * NB + v));
             m[tl] = make_float2(__uint_as_float(mm.x), __uint_as_float(mm.y));
         }
     };
@@ -423,31 +468,37 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
             *o = p.accumulate ? __fadd_rn(*o, val) : val;
         }
     }
+    cluster_sync();  // no CTA may leave while another still reads its packed activations
 }
 
 template <uint32_t KIND, int NB, int RING = Geo<KIND>::RING>
-int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, uint32_t tiles, cudaStream_t s) {
+int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cudaStream_t s) {
     constexpr int W_BYTES = ROWS * Geo<KIND>::BOX;
     constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
-    constexpr size_t DYN = size_t(WARPS) * RING * STAGE + 128;
+    constexpr size_t RING_BYTES = size_t(WARPS) * RING * STAGE + 128;
     auto kern = k_matvec_decode_i8<KIND, NB, RING>;
     static int cached_device = -1;
     if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(DYN)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RING_BYTES + MAX_X_SMEM)),
+                 "raising the shared memory limit");
         cached_device = ctx->device;
     }
     CUtensorMap map;
     memcpy(&map, w->tmap16, sizeof(map));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles);
+    cfg.gridDim = dim3((p.tiles + CLUSTER - 1) / CLUSTER * CLUSTER);
     cfg.blockDim = dim3(WARPS * 32);
-    cfg.dynamicSmemBytes = DYN;
+    cfg.dynamicSmemBytes = RING_BYTES + size_t(p.chunks_per_cta) * iblob_bytes(KIND, NB);
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CLUSTER;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, map, p), "launching the integer decode matvec kernel");
     ctx->launches += 1;
     return BHD_OK;
@@ -455,7 +506,8 @@ int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, ui
 
 }  // namespace
 
-// Decode path of bhd_matvec for one or two activation vectors.
+// Decode path of bhd_matvec for one or two activation vectors. One launch: the activations are
+// packed inside the kernel, once per cluster.
 int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                     uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled) {
     *handled = false;
@@ -464,37 +516,33 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     const uint32_t chunks = uint32_t((w->cols + CHUNK_K - 1) / CHUNK_K);
     const uint32_t tiles = uint32_t((w->rows + ROWS - 1) / ROWS);
     const int nb = int(batch);
-    int32_t st = bhd_ensure_workspace(ctx, size_t(chunks) * iblob_bytes(w->kind, nb), s);
-    if (st != BHD_OK) return st;
-    uint8_t* blob = ctx->workspace;
-    {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(chunks);
-        cfg.blockDim = dim3(256);
-        cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_pack_x_i8, w->kind, x, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev),
-                 "launching the activation packing kernel");
-        ctx->launches += 1;
-    }
+    // Where this kernel wins, by measurement on B200 against the fp16 decode kernel: one vector
+    // of Q4_K or Q8_0 at every shape tried; one vector of Q6_K, or two of Q4_K, only for tall
+    // matrices of up to 4096 columns (rows are not split over CTAs here, so wide rows leave
+    // too few CTAs, and the wider operand sets of those variants cost occupancy).
+    const bool tall = w->rows >= 8192 && w->cols <= 4096;
+    if (nb == 1 && w->kind == BHD_TYPE_Q6_K && !tall) return BHD_OK;
+    if (nb == 2 && !(w->kind == BHD_TYPE_Q4_K && tall)) return BHD_OK;
+    const uint32_t per_cta = (chunks + CLUSTER - 1) / CLUSTER;
+    if (size_t(per_cta) * iblob_bytes(w->kind, nb) > size_t(MAX_X_SMEM)) return BHD_OK;  // very wide rows: other paths
     DecodeI8Params p;
-    p.blob = blob;
+    p.x = x;
     p.y = y;
     p.status = ctx->status_dev;
     p.rows = uint32_t(w->rows);
     p.row_base = uint32_t(slab * w->rows);
     p.chunks = chunks;
     p.batch = batch;
+    p.cols = uint32_t(w->cols);
+    p.tiles = tiles;
+    p.chunks_per_cta = per_cta;
     p.scale = scale;
     p.accumulate = accumulate;
-#define BHD_CASE(K)                                                 \
-    case K:                                                         \
-        if (nb == 1) st = launch_i8<K, 1>(ctx, w, p, tiles, s);     \
-        else st = launch_i8<K, 2>(ctx, w, p, tiles, s);             \
+    int32_t st = BHD_OK;
+#define BHD_CASE(K)                                          \
+    case K:                                                  \
+        if (nb == 1) st = launch_i8<K, 1>(ctx, w, p, s);     \
+        else st = launch_i8<K, 2>(ctx, w, p, s);             \
         break;
     switch (w->kind) {
         BHD_CASE(BHD_TYPE_Q8_0)
