@@ -366,8 +366,9 @@ def run_gpu_arm(args):
     bytes_per_step = head["copies"] * head["bytes_per_matvec"]
     value = world * bytes_per_step * steps / secs / 1e9
 
+    sections = set(v for v in args.sections.split(",") if v)
     detail = {}
-    if not args.quick and not args.skip_matvec_detail:
+    if not args.quick and not args.skip_matvec_detail and "detail" in sections:
         for kind in (8, 12, 14):
             for batch in (1, 2, 4, 8):
                 if kind == HEAD_KIND and batch == 1:
@@ -376,21 +377,21 @@ def run_gpu_arm(args):
                 detail[f"{KIND_NAME[kind]}_b{batch}"] = {"gbs": round(r["gbs"], 1), "us": round(r["us_per_matvec"], 2),
                                                         "frac_of_peak": round(r["gbs"] / peak, 4)}
     prefill = {}
-    if not args.quick and not args.skip_matvec_detail and world == 1:
+    if not args.quick and "prefill" in sections and world == 1:
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
                 tpeak = float(json.load(fh)["bf16_tflops_sustained"])
         except Exception:
             tpeak = 1400.0
-        for M in (128, 512, 2048):
-            for N in (12288, 4096):
-                try:
-                    prefill[f"M{M}_N{N}"] = bench_prefill(dev, torch, M, N, 4096, max(2, steps // 4), 3, tpeak)
-                except Exception as e:
-                    prefill[f"M{M}_N{N}"] = {"error": repr(e)}
+        shapes = [tuple(int(d) for d in v.split("x")) for v in args.prefill_shapes.split(",") if v]
+        for (M, N) in shapes:
+            try:
+                prefill[f"M{M}_N{N}"] = bench_prefill(dev, torch, M, N, 4096, max(2, steps // 4), 3, tpeak)
+            except Exception as e:
+                prefill[f"M{M}_N{N}"] = {"error": repr(e)}
     moe = {}
     try:
-        for T in (() if args.quick else tuple(int(v) for v in args.moe_tokens.split(",") if v)):
+        for T in (() if (args.quick or "moe" not in sections) else tuple(int(v) for v in args.moe_tokens.split(",") if v)):
             moe[f"T{T}"] = bench_moe(dev, torch, T, max(2, steps // 4), 3, rank, world, barrier)
     except Exception as e:  # the headline number must still be reported
         moe["error"] = repr(e)
@@ -441,6 +442,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--moe-tokens", default="1,16,64,512", help="token counts of the routed-layer detail runs")
     ap.add_argument("--skip-matvec-detail", action="store_true", help="skip the other formats / batch sizes")
+    ap.add_argument("--sections", default="detail,prefill,moe", help="which detail runs follow the headline workload")
+    ap.add_argument("--prefill-shapes", default="128x12288,128x4096,512x12288,512x4096,2048x12288,2048x4096",
+                    help="MxN cases of the Q8_0 K=4096 prefill matmul detail run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

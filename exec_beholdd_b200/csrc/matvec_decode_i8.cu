@@ -124,8 +124,18 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+// Publishes this CTA's shared-memory writes to the cluster and waits for everyone else's. The
+// CTA barrier makes all threads' writes visible to thread 0, whose single cluster-scope fence
+// then covers them (cumulativity); one fence per CTA is much cheaper than one per thread.
 __device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("fence.acq_rel.cluster;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Rendezvous that publishes nothing (no fence): used only to keep shared memory alive until
+// every CTA of the cluster has finished reading it.
+__device__ __forceinline__ void cluster_rendezvous() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
@@ -468,7 +478,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
             *o = p.accumulate ? __fadd_rn(*o, val) : val;
         }
     }
-    cluster_sync();  // no CTA may leave while another still reads its packed activations
+    cluster_rendezvous();  // no CTA may leave while another still reads its packed activations
 }
 
 template <uint32_t KIND, int NB, int RING = Geo<KIND>::RING>
