@@ -329,6 +329,34 @@ def bench_moe(dev, torch, T, steps, warmup, rank=0, world=1, barrier=None):
     return out
 
 
+def bench_row_split(dev, torch, kind, batch, steps, warmup, rank, world, barrier):
+    """One [ROWS x COLS] projection with its rows split over the ranks, all-gather included.
+    Eager launches (the collective is not captured), device-timed, max over ranks."""
+    import torch.distributed as dist
+    from exec_beholdd_b200 import synth
+    from exec_beholdd_b200.row_parallel import RowSplitLinear
+
+    copies = 4  # distinct shards per step so that the weights come from HBM, not L2
+    lins = [RowSplitLinear.from_host(dev, synth.matrix(kind, SEED + i, ROWS, COLS), kind, ROWS, COLS, rank, world) for i in range(copies)]
+    x = torch.from_numpy(synth.activations(SEED + 1, (batch, COLS))).cuda()
+    y = torch.empty((batch, ROWS), device="cuda")
+
+    def step():
+        for lin in lins:
+            lin.forward(x, y)
+
+    secs = time_region(torch, step, steps, warmup, barrier, graph=False)
+    t = torch.tensor([secs], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs = float(t.item())
+    dev.check_status()
+    for lin in lins:
+        lin.free()
+    us = secs / steps / copies * 1e6
+    return {"us_per_matvec": round(us, 2), "gbs_whole_weight": round(algorithmic_bytes(kind, ROWS, COLS, batch) / us / 1e3, 1),
+            "rows_per_gpu": ROWS // world, "collective": "all_gather of y", "launch": "eager"}
+
+
 def run_gpu_arm(args):
     import torch
 
@@ -396,6 +424,13 @@ def run_gpu_arm(args):
     except Exception as e:  # the headline number must still be reported
         moe["error"] = repr(e)
 
+    row_split = None
+    if world > 1 and not args.quick and ROWS % world == 0:
+        try:
+            row_split = {f"b{b}": bench_row_split(dev, torch, HEAD_KIND, b, max(2, steps // 4), 3, rank, world, barrier) for b in (1, 4)}
+        except Exception as e:
+            row_split = {"error": repr(e)}
+
     e2e = bench_matvec_e2e(dev, torch, HEAD_KIND, max(2, steps // 4), 3, head["copies"]) if world == 1 else None
     if world > 1:
         e2e_local = bench_matvec_e2e(dev, torch, HEAD_KIND, max(2, steps // 4), 3, head["copies"])
@@ -425,6 +460,7 @@ def run_gpu_arm(args):
                          "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
             "clocks": clocks.summary(), "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "moe_layer": moe,
+            "row_split_projection": row_split,
         }
         print(json.dumps(line), flush=True)
     dev.close()

@@ -193,6 +193,30 @@ def test_matvec_matches_oracle_on_seeded_inputs(dev, oracle, kind, rows, cols, b
     w.free()
 
 
+@pytest.mark.parametrize("kind,rows,cols,batch,world", [(12, 1024, 4096, 1, 2), (8, 768, 2048, 4, 4), (14, 512, 1024, 2, 2)])
+def test_row_split_shards_reproduce_the_whole_projection(dev, oracle, kind, rows, cols, batch, world):
+    """Every rank's shard (whole packed rows) gives that rank's slice of y; the slices laid
+    side by side are the single-GPU result (one process plays all ranks here)."""
+    import torch
+    from exec_beholdd_b200 import synth
+    from exec_beholdd_b200.row_parallel import RowSplitLinear
+
+    packed = synth.matrix(kind, 21, rows, cols)
+    x = synth.activations(22, (batch, cols))
+    want = oracle.matvec_batch(packed, kind, rows, cols, x)
+    xd = cuda(x)
+    per = rows // world
+    got = np.empty((batch, rows), dtype=np.float32)
+    for r in range(world):
+        lin = RowSplitLinear.from_host(dev, packed, kind, rows, cols, r, world)
+        yl = torch.full((batch, per), float("nan"), device="cuda")
+        lin._local(xd, yl)
+        got[:, r * per:(r + 1) * per] = yl.cpu().numpy()
+        lin.free()
+    assert max_rel_err(got, want) <= TOL
+    dev.check_status()
+
+
 @pytest.mark.parametrize("kind,rows,cols", [(12, 12288, 4096), (12, 4096, 12288), (14, 12288, 4096), (8, 12288, 4096)])
 def test_full_size_matvec_properties(dev, kind, rows, cols):
     """Full benchmark sizes, where the scalar oracle is too slow: compare with the f64 product
