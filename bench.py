@@ -41,8 +41,8 @@ HEAD_KIND = 12                     # Q4_K
 KIND_NAME = {8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu
-# capture summarised in profiles/matvec_decode_q4k_12288x4096_b1.md (same workload, same sizes).
-HEAD_TRAFFIC_BYTES = 28_344_832
+# capture summarised in profiles/matvec_decode_i8_q4k_12288x4096_b1.md (same workload, same sizes).
+HEAD_TRAFFIC_BYTES = 28_345_088
 MOE = dict(n_experts=128, dim=2048, ff=768, top_k=8)
 
 
@@ -456,7 +456,7 @@ def run_gpu_arm(args):
                                    f"> 2x L2, so inputs exceed L2 between reuses)",
                        "parallelism": "replicas" if world > 1 else "single"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": HEAD_TRAFFIC_BYTES, "peak_source": peak_kind, "kernel": "matvec (dominant kernel of the step)",
+                         "traffic": HEAD_TRAFFIC_BYTES, "peak_source": peak_kind, "kernel": "k_matvec_decode_i8 (the only kernel of the step)",
                          "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
             "clocks": clocks.summary(), "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "moe_layer": moe,
