@@ -197,4 +197,11 @@ int32_t bhd_launch_moe_slots_f16(bhd_ctx* ctx, int mode, const void* hdr, const 
                                  const float* src, const float* src2, uint32_t K, uint32_t max_slots, void* out16,
                                  cudaStream_t s);
 bool bhd_moe_tcgen05_usable(const bhd_ctx* ctx, const bhd_weight* w);
+int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
+                                  const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* xq, uint32_t n_slots,
+                                  float* out0, float* out1, const float* slot_weight, cudaStream_t s);
+int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
+                                const float* src, const float* src2, uint32_t K, uint32_t n_slots, void* out, cudaStream_t s);
+size_t bhd_moe_slots_i8_bytes(uint32_t K, uint32_t n_slots);
+bool bhd_moe_i8_usable(const bhd_weight* w);
 

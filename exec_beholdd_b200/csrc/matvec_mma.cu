@@ -842,30 +842,43 @@ int32_t launch_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1,
     return BHD_OK;
 }
 
-// x16: fp16 rows in slot order for the tensor-core path (nullptr: every class uses the mma.sync kernel).
+// Size classes from this one on run on the integer tensor-core kernel (moe_grouped_i8.cu)
+// when the tensors qualify; 0 = every class.
+constexpr uint32_t I8_FROM_CLS = 0;
+
+// xq: block-floating byte activations in slot order for the integer kernel; x16: fp16 rows in slot
+// order for the tcgen05 kernel (both nullptr: every class uses the fp16 mma.sync kernel).
 int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, MoeRun run, const int32_t* glist,
                            uint32_t gmax, uint32_t tiles, uint32_t n_routes, uint32_t n_local, cudaStream_t s,
-                           const void* x16 = nullptr) {
+                           const void* x16 = nullptr, const void* xq = nullptr) {
     // A class can only occur when there are enough routes for its smallest group.
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
     int32_t st = BHD_OK;
+    auto i8 = [&](uint32_t cls, uint32_t bound) {
+        return bhd_launch_moe_grouped_i8(ctx, w0, w1, run.hdr, run.groups, glist + cls * gmax, cls, bound, xq, n_routes, run.out0, run.out1,
+                                         run.slot_weight, s);
+    };
     run.glist = glist + 0 * gmax;
-    st = launch_grouped<0>(ctx, w0, w1, run, tiles, small, s);
+    st = (xq && I8_FROM_CLS <= 0) ? i8(0, small) : launch_grouped<0>(ctx, w0, w1, run, tiles, small, s);
     if (st != BHD_OK) return st;
     if (n_routes >= 5) {
         run.glist = glist + 1 * gmax;
-        if ((st = launch_grouped<1>(ctx, w0, w1, run, tiles, small < n_routes / 5 ? small : n_routes / 5, s)) != BHD_OK) return st;
+        const uint32_t bound = small < n_routes / 5 ? small : n_routes / 5;
+        st = (xq && I8_FROM_CLS <= 1) ? i8(1, bound) : launch_grouped<1>(ctx, w0, w1, run, tiles, bound, s);
+        if (st != BHD_OK) return st;
     }
     if (n_routes >= 9) {
         const uint32_t bound = small < n_routes / 9 ? small : n_routes / 9;
         run.glist = glist + 2 * gmax;
-        if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 2, bound, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
+        if (xq && I8_FROM_CLS <= 2) st = i8(2, bound);
+        else if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 2, bound, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
         else st = launch_grouped<2>(ctx, w0, w1, run, tiles, bound, s);
         if (st != BHD_OK) return st;
     }
     if (n_routes >= 17) {
         run.glist = glist + 3 * gmax;
-        if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 3, n_routes / 17, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
+        if (xq && I8_FROM_CLS <= 3) st = i8(3, n_routes / 17);
+        else if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 3, n_routes / 17, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
         else st = launch_grouped<3>(ctx, w0, w1, run, tiles, n_routes / 17, s);
         if (st != BHD_OK) return st;
     }
@@ -903,8 +916,12 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const size_t o_bitmap = take(4 * size_t(E) * words), o_prefix = take(4 * size_t(E) * words);
     const size_t o_g = take(4 * size_t(R) * ff), o_u = take(4 * size_t(R) * ff), o_d = take(4 * size_t(R) * dim);
     const size_t o_bx = take(nt_sum * unit * chunks_x), o_ba = take(nt_sum * unit * chunks_a);
-    const bool tc = R >= 9 && R <= 65535 && bhd_moe_tcgen05_usable(ctx, gate) && bhd_moe_tcgen05_usable(ctx, up) && bhd_moe_tcgen05_usable(ctx, down);
+    const bool i8 = bhd_moe_i8_usable(gate) && bhd_moe_i8_usable(up) && bhd_moe_i8_usable(down) && dim % 8 == 0 && ff % 8 == 0;
+    const bool tc = !(i8 && I8_FROM_CLS <= 2) && R >= 9 && R <= 65535 && bhd_moe_tcgen05_usable(ctx, gate) &&
+                    bhd_moe_tcgen05_usable(ctx, up) && bhd_moe_tcgen05_usable(ctx, down);
+    const bool fp16_pack = !(i8 && I8_FROM_CLS == 0);  // some class still runs on the fp16 mma.sync kernel
     const size_t o_x16 = take(tc ? 4 * size_t(R) * dim : 0), o_a16 = take(tc ? 4 * size_t(R) * ff : 0);  // hi + lo fp16 rows
+    const size_t o_xq = take(i8 ? bhd_moe_slots_i8_bytes(uint32_t(dim), R) : 0), o_aq = take(i8 ? bhd_moe_slots_i8_bytes(uint32_t(ff), R) : 0);
     int32_t st = bhd_ensure_workspace(ctx, off, s);
     if (st != BHD_OK) return st;
     uint8_t* ws = ctx->workspace;
@@ -932,10 +949,14 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
                                   ctx->status_dev, plan_on_chip);
     BHD_LAUNCHED(ctx, "route planning kernel");
     const uint32_t group_bound = gmax < R ? gmax : R;
-    const int skip_cls = tc ? 2 : 4;  // groups of 9+ routes go to the tensor-core kernel
-    k_moe_pack<<<dim3(chunks_x, group_bound), STEPS * 32, 0, s>>>(0, hdr, groups, slot_route, top_k, x, nullptr, uint32_t(dim),
-                                                                  ws + o_bx, ctx->status_dev, skip_cls);
-    BHD_LAUNCHED(ctx, "token gather and packing kernel");
+    // classes from skip_cls on do not read the fp16 fragment blobs
+    const int skip_cls = i8 ? int(I8_FROM_CLS) : (tc ? 2 : 4);
+    if (fp16_pack) {
+        k_moe_pack<<<dim3(chunks_x, group_bound), STEPS * 32, 0, s>>>(0, hdr, groups, slot_route, top_k, x, nullptr, uint32_t(dim),
+                                                                      ws + o_bx, ctx->status_dev, skip_cls);
+        BHD_LAUNCHED(ctx, "token gather and packing kernel");
+    }
+    if (i8 && (st = bhd_launch_moe_slots_i8(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
     if (tc && (st = bhd_launch_moe_slots_f16(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_x16, s)) != BHD_OK) return st;
 
     MoeRun run;
@@ -951,11 +972,15 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     run.rows = uint32_t(ff);
     run.chunks = chunks_x;
     run.use_blob_a = 0;
-    st = launch_grouped_all(ctx, gate, up, run, glist, gmax, uint32_t((ff + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_x16 : nullptr);
+    st = launch_grouped_all(ctx, gate, up, run, glist, gmax, uint32_t((ff + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_x16 : nullptr,
+                            i8 ? ws + o_xq : nullptr);
     if (st != BHD_OK) return st;
-    k_moe_pack<<<dim3(chunks_a, group_bound), STEPS * 32, 0, s>>>(1, hdr, groups, slot_route, top_k, gbuf, ubuf, uint32_t(ff),
-                                                                  ws + o_ba, ctx->status_dev, skip_cls);
-    BHD_LAUNCHED(ctx, "gating and packing kernel");
+    if (fp16_pack) {
+        k_moe_pack<<<dim3(chunks_a, group_bound), STEPS * 32, 0, s>>>(1, hdr, groups, slot_route, top_k, gbuf, ubuf, uint32_t(ff),
+                                                                      ws + o_ba, ctx->status_dev, skip_cls);
+        BHD_LAUNCHED(ctx, "gating and packing kernel");
+    }
+    if (i8 && (st = bhd_launch_moe_slots_i8(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
     if (tc && (st = bhd_launch_moe_slots_f16(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_a16, s)) != BHD_OK) return st;
     // down: [dim x ff] per expert, each output row scaled by its route weight
     run.blob = ws + o_ba;
@@ -965,7 +990,8 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     run.rows = uint32_t(dim);
     run.chunks = chunks_a;
     run.use_blob_a = 1;
-    st = launch_grouped_all(ctx, down, nullptr, run, glist, gmax, uint32_t((dim + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_a16 : nullptr);
+    st = launch_grouped_all(ctx, down, nullptr, run, glist, gmax, uint32_t((dim + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_a16 : nullptr,
+                            i8 ? ws + o_aq : nullptr);
     if (st != BHD_OK) return st;
     const uint64_t n = T * dim;
     k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, route_slot, y, n, uint32_t(dim), top_k, accumulate);
