@@ -560,14 +560,58 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
         if (lane == 0) s_counts[e] = run;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t off = 0, ng = 0, bx = 0, ba = 0, gc[4] = {0, 0, 0, 0};
-        for (uint32_t e = 0; e < n_local; ++e) {
-            s_offsets[e] = off;
-            uint32_t n = s_counts[e], s0 = off;
-            off += n;
-            while (n > 0 && ng < gmax) {
-                const uint32_t nb = n < 32 ? n : 32;
+    // Groups of up to 32 routes per expert, in expert order. Thread e describes expert e's groups
+    // (n / 32 full ones and a remainder); a block-wide exclusive scan of eight per-expert totals
+    // (routes, groups, groups per size class, fragment-blob units of the two inputs) gives every
+    // expert its first slot, first group index, first index in each class list and blob offsets,
+    // so the lists come out exactly as a sequential walk over the experts would write them.
+    // Requires n_local <= blockDim.x.
+    {
+        __shared__ uint32_t s_warp[32][8];
+        const uint32_t e = threadIdx.x;
+        const uint32_t n = e < n_local ? s_counts[e] : 0u;
+        const uint32_t full = n / 32, rem = n % 32;
+        const int rcls = rem ? moe_cls(int(rem)) : 0;
+        const uint32_t u3 = uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(3)) / 256);
+        const uint32_t ur = rem ? uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(rcls)) / 256) : 0u;
+        uint32_t v[8];
+        v[0] = n;
+        v[1] = full + (rem ? 1u : 0u);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[2 + c] = (c == 3 ? full : 0u) + ((rem && rcls == c) ? 1u : 0u);
+        v[6] = chunks_x * (full * u3 + ur);
+        v[7] = chunks_a * (full * u3 + ur);
+        uint32_t incl[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            incl[q] = v[q];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t o = __shfl_up_sync(0xffffffffu, incl[q], d);
+                if (lane >= d) incl[q] += o;
+            }
+            if (lane == 31) s_warp[warp][q] = incl[q];
+        }
+        __syncthreads();
+        uint32_t base[8], total[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            base[q] = 0;
+            total[q] = 0;
+            for (int w = 0; w < n_warps; ++w) {
+                const uint32_t t = s_warp[w][q];
+                if (w < warp) base[q] += t;
+                total[q] += t;
+            }
+            base[q] += incl[q] - v[q];  // exclusive prefix of this expert
+        }
+        if (e < n_local) {
+            s_offsets[e] = base[0];
+            uint32_t s0 = base[0], ng = base[1], bx = base[6], ba = base[7];
+            uint32_t gc[4] = {base[2], base[3], base[4], base[5]};
+            uint32_t left = n;
+            while (left > 0 && ng < gmax) {
+                const uint32_t nb = left < 32 ? left : 32;
                 const int cls = moe_cls(int(nb));
                 MoeGroup g;
                 g.expert_local = int32_t(e); g.slot0 = int32_t(s0); g.nb = int32_t(nb); g.cls = cls;
@@ -577,13 +621,16 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
                 glist[cls * gmax + gc[cls]++] = int32_t(ng);
                 groups[ng++] = g;
                 s0 += nb;
-                n -= nb;
+                left -= nb;
             }
         }
-        s_offsets[n_local] = off;
-        for (int c = 0; c < 4; ++c) hdr->gcount[c] = gc[c];
-        hdr->total_groups = ng;
-        hdr->local_routes = off;
+        if (threadIdx.x == 0) {
+            s_offsets[n_local] = total[0];
+            // gmax = n_local + n_routes / 32 + 1 bounds the number of groups, so none is cut off
+            for (int c = 0; c < 4; ++c) hdr->gcount[c] = total[2 + c];
+            hdr->total_groups = total[1];
+            hdr->local_routes = total[0];
+        }
     }
     __syncthreads();
     for (uint32_t e = threadIdx.x; e <= n_local; e += blockDim.x) {
@@ -942,7 +989,8 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
         BHD_CUDA(ctx, cudaFuncSetAttribute(k_moe_plan, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), "raising the shared memory limit");
         plan_device = ctx->device;
     }
-    k_moe_plan<<<1, R <= 256 ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
+    // one thread per local expert in the group-building step
+    k_moe_plan<<<1, (R <= 256 && E <= 256) ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
                                   reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
                                   route_slot, slot_route, slot_weight, groups, glist, gmax,
                                   reinterpret_cast<uint32_t*>(ws + o_bitmap), reinterpret_cast<uint32_t*>(ws + o_prefix),

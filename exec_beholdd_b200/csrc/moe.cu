@@ -98,45 +98,46 @@ __global__ void k_route_select(float* __restrict__ probs, uint32_t n_experts, ui
     }
 }
 
-// Router logits for an F32 router in the CPU's summation order, fast: logits[t][e] is one f32
-// accumulator walked over the columns left to right with separately rounded product and sum
-// (crates/beholdd-backend/src/cpu.rs:198-218), so only the additions are sequential. A CTA owns
-// 32 experts x up to 8 positions; all threads stream 128-column tiles of the router weights and
-// of the activations into shared memory with cp.async (4 tiles in flight), and warp t walks the
-// tile for position t, lane e adding the products of expert e in column order. Bit-identical to
-// the order-exact matvec kernel.
-constexpr int RT_TOK = 8, RT_COLS = 128, RT_BUF = 4;
-constexpr int RT_W_FLOATS = RT_COLS * 33, RT_X_FLOATS = RT_TOK * RT_COLS;
+// Router logits in the reference's summation order: logits[t][e] = ((0 + w[e][0]*x[t][0]) +
+// w[e][1]*x[t][1]) + ..., every product and every sum rounded to f32 (forward.rs:1330-1336 ->
+// cpu.rs:198-218). The chain of 'dim' dependent additions per (position, expert) is the floor
+// (about 4 us for 2048 columns); everything else is arranged to stay out of its way:
+//   * CTA = 8 experts x 32 positions, warp = 8 experts x 4 positions, one chain per lane;
+//   * 128-column tiles of w and x staged by 16-byte cp.async, three tiles in flight;
+//   * rows padded to 132 floats: the eight experts of a quarter-warp read 16 bytes each from
+//     disjoint banks, the position's x is a broadcast.
+constexpr int RT_EXP = 8, RT_TOK = 32, RT_COLS = 128, RT_BUF = 3, RT_LD = RT_COLS + 4;
+constexpr int RT_W_FLOATS = RT_EXP * RT_LD, RT_X_FLOATS = RT_TOK * RT_LD;
 constexpr size_t RT_SMEM = size_t(RT_BUF) * (RT_W_FLOATS + RT_X_FLOATS) * sizeof(float);
 
-__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
 }
 
+// Requires dim % 4 == 0 and 16-byte aligned w and x.
 __global__ void __launch_bounds__(256) k_router_logits_f32(const float* __restrict__ w, uint32_t n_experts, uint32_t dim,
                                                            const float* __restrict__ x, uint32_t n_positions,
                                                            float* __restrict__ out) {
-    extern __shared__ float rt_smem[];
-    float* ws = rt_smem;                          // [buf][col][33]: expert-minor, so lane e reads bank e + col
-    float* xs = rt_smem + RT_BUF * RT_W_FLOATS;   // [buf][position][col]
+    extern __shared__ __align__(16) float rt_smem[];
+    float* ws = rt_smem;                          // [buf][expert][RT_LD]
+    float* xs = rt_smem + RT_BUF * RT_W_FLOATS;   // [buf][position][RT_LD]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t e0 = blockIdx.x * 32, t0 = blockIdx.y * RT_TOK;
+    const uint32_t e0 = blockIdx.x * RT_EXP, t0 = blockIdx.y * RT_TOK;
     const uint32_t tiles = (dim + RT_COLS - 1) / RT_COLS;
     auto load = [&](uint32_t tile, int buf) {
         const uint32_t c0 = tile * RT_COLS;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint32_t idx = threadIdx.x + 256 * i, e = idx >> 7, c = idx & 127;
-            float* dst = ws + buf * RT_W_FLOATS + c * 33 + e;
-            if (e0 + e < n_experts && c0 + c < dim) cp_async4(dst, w + uint64_t(e0 + e) * dim + c0 + c);
-            else *dst = 0.0f;
+        {   // w: 8 experts x 32 float4, one per thread
+            const uint32_t e = threadIdx.x >> 5, c = (threadIdx.x & 31) * 4;
+            float* dst = ws + buf * RT_W_FLOATS + e * RT_LD + c;
+            if (e0 + e < n_experts && c0 + c < dim) cp_async16(dst, w + uint64_t(e0 + e) * dim + c0 + c);
+            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t idx = threadIdx.x + 256 * i, t = idx >> 7, c = idx & 127;
-            float* dst = xs + buf * RT_X_FLOATS + t * RT_COLS + c;
-            if (t0 + t < n_positions && c0 + c < dim) cp_async4(dst, x + uint64_t(t0 + t) * dim + c0 + c);
-            else *dst = 0.0f;
+        for (int i = 0; i < 4; ++i) {  // x: 32 positions x 32 float4
+            const uint32_t idx = threadIdx.x + 256 * i, t = idx >> 5, c = (idx & 31) * 4;
+            float* dst = xs + buf * RT_X_FLOATS + t * RT_LD + c;
+            if (t0 + t < n_positions && c0 + c < dim) cp_async16(dst, x + uint64_t(t0 + t) * dim + c0 + c);
+            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
     for (uint32_t i = 0; i < RT_BUF - 1; ++i) {
@@ -144,30 +145,27 @@ __global__ void __launch_bounds__(256) k_router_logits_f32(const float* __restri
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     float acc = 0.0f;
-    const bool chain = t0 + warp < n_positions;  // warp t walks position t0 + t
+    const uint32_t el = lane & 7, tl = uint32_t(warp) * 4 + (lane >> 3);  // this lane's expert and position within the CTA
+    const bool chain = t0 + uint32_t(warp) * 4 < n_positions;            // whole warps skip tiles they have no position for
     for (uint32_t tile = 0; tile < tiles; ++tile) {
         const int buf = tile % RT_BUF;
+        asm volatile("cp.async.wait_group %0;" ::"n"(RT_BUF - 2) : "memory");
+        __syncthreads();  // tile is visible to everyone, and everyone is done with the buffer refilled below
         if (tile + RT_BUF - 1 < tiles) load(tile + RT_BUF - 1, (tile + RT_BUF - 1) % RT_BUF);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group %0;" ::"n"(RT_BUF - 1) : "memory");
-        __syncthreads();
         if (chain) {
-            const uint32_t n = min(uint32_t(RT_COLS), dim - tile * RT_COLS);
-            const float* wt = ws + buf * RT_W_FLOATS + lane;
-            const float* xt = xs + buf * RT_X_FLOATS + warp * RT_COLS;
-            uint32_t c = 0;
-            for (; c + 16 <= n; c += 16) {  // products first, then the ordered additions
-                float v[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(wt[(c + i) * 33], xt[c + i]);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc = __fadd_rn(acc, v[i]);
+            const uint32_t n = min(uint32_t(RT_COLS), dim - tile * RT_COLS);  // a multiple of 4
+            const float4* wt = reinterpret_cast<const float4*>(ws + buf * RT_W_FLOATS + el * RT_LD);
+            const float4* xt = reinterpret_cast<const float4*>(xs + buf * RT_X_FLOATS + tl * RT_LD);
+#pragma unroll 8
+            for (uint32_t c = 0; c < n / 4; ++c) {  // products first, then the ordered additions
+                const float4 a = wt[c], b = xt[c];
+                const float p0 = __fmul_rn(a.x, b.x), p1 = __fmul_rn(a.y, b.y), p2 = __fmul_rn(a.z, b.z), p3 = __fmul_rn(a.w, b.w);
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, p0), p1), p2), p3);
             }
-            for (; c < n; ++c) acc = __fadd_rn(acc, __fmul_rn(wt[c * 33], xt[c]));
         }
-        __syncthreads();
     }
-    if (chain && e0 + lane < n_experts) out[uint64_t(t0 + warp) * n_experts + e0 + lane] = acc;
+    if (t0 + tl < n_positions && e0 + el < n_experts) out[uint64_t(t0 + tl) * n_experts + e0 + el] = acc;
 }
 
 // ---- general expert kernels (any dim / expert_ff that are whole Q8_0 blocks) -----------
@@ -292,14 +290,15 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     }
     if (counts_dev) BHD_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, n_experts * sizeof(int32_t), s), "clearing expert counts");
     // Router logits in the CPU's summation order (forward.rs:1330-1336 -> cpu.rs:198-218).
-    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535 * RT_TOK) {
+    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535ull * RT_TOK && router->cols % 4 == 0 &&
+        (reinterpret_cast<uintptr_t>(router->dev) & 15) == 0 && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0) {
         static int cached_device = -1;
         if (cached_device != ctx->device) {
             BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RT_SMEM)),
                      "raising the shared memory limit");
             cached_device = ctx->device;
         }
-        k_router_logits_f32<<<dim3(unsigned((n_experts + 31) / 32), unsigned((n_positions + RT_TOK - 1) / RT_TOK)), 256, RT_SMEM, s>>>(
+        k_router_logits_f32<<<dim3(unsigned((n_experts + RT_EXP - 1) / RT_EXP), unsigned((n_positions + RT_TOK - 1) / RT_TOK)), 256, RT_SMEM, s>>>(
             reinterpret_cast<const float*>(router->dev), uint32_t(n_experts), uint32_t(router->cols), x_dev,
             uint32_t(n_positions), probs);
         BHD_LAUNCHED(ctx, "router logits kernel");

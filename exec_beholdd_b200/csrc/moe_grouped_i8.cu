@@ -227,29 +227,57 @@ __global__ void __launch_bounds__(THREADS) k_moe_grouped_i8(const __grid_constan
         float part[NT][2];  // sum over the chunk's blocks of d_block * (integer dot product)
 #pragma unroll
         for (int j = 0; j < NT; ++j) part[j][0] = part[j][1] = 0.f;
-#pragma unroll
-        for (int blk = 0; blk < 8; ++blk) {
-            uint32_t a[4];
+        // Operands of one 32-column block: the lane's A fragment (rows r0 / r1, two halves of
+        // k), the two block scales, and its B fragment for each of the NT MMAs. The loads of
+        // block b + 1 are issued between the MMAs of block b and the arithmetic on their
+        // results, so neither the shared-memory nor the MMA latency is ever waited for alone
+        // (the asm statements keep program order, so the order below is the issue order).
+        struct Ops { uint32_t raw[6]; uint32_t a[4]; uint32_t d0, d1; uint2 b[NT]; };
+        auto load_block = [&](int blk, Ops& o) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int off = 34 * blk + 2 + 16 * h + 4 * t;  // this lane's four quants of the half block
                 if (blk & 1) {
-                    a[2 * h] = lds32(w0 + off);
-                    a[2 * h + 1] = lds32(w1 + off);
-                } else {  // 2 mod 4: stitch two aligned words
-                    a[2 * h] = __funnelshift_r(lds32(w0 + off - 2), lds32(w0 + off + 2), 16);
-                    a[2 * h + 1] = __funnelshift_r(lds32(w1 + off - 2), lds32(w1 + off + 2), 16);
+                    o.a[2 * h] = lds32(w0 + off);
+                    o.a[2 * h + 1] = lds32(w1 + off);
+                } else {  // 2 mod 4: two aligned words, stitched when they are used
+                    o.raw[3 * h] = lds32(w0 + off - 2);
+                    o.raw[3 * h + 1] = lds32(w0 + off + 2);
+                    o.raw[3 * h + 2] = lds32(w1 + off - 2);
+                    o.a[2 * h + 1] = lds32(w1 + off + 2);
                 }
             }
-            const float d0 = h2f(lds16(w0 + 34 * blk)), d1 = h2f(lds16(w1 + 34 * blk));
+            o.d0 = lds16(w0 + 34 * blk);
+            o.d1 = lds16(w1 + 34 * blk);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) o.b[j] = lds64(xb + uint32_t(4 * j) * SLOT_BYTES + b_off + blk * 64);
+        };
+        auto finish_a = [&](int blk, Ops& o) {
+            if (!(blk & 1)) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    o.a[2 * h] = __funnelshift_r(o.raw[3 * h], o.raw[3 * h + 1], 16);
+                    o.a[2 * h + 1] = __funnelshift_r(o.raw[3 * h + 2], o.a[2 * h + 1], 16);
+                }
+            }
+        };
+        Ops cur, nxt;
+        load_block(0, cur);
+#pragma unroll
+        for (int blk = 0; blk < 8; ++blk) {
+            finish_a(blk, cur);
+            int ci[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) imma_s8(ci[j], cur.a, cur.b[j]);
+            if (blk < 7) load_block(blk + 1, nxt);
+            const float d0 = h2f(cur.d0), d1 = h2f(cur.d1);
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                int ci[4];
-                imma_s8(ci, a, lds64(xb + uint32_t(4 * j) * SLOT_BYTES + b_off + blk * 64));
                 // accumulator columns (2t, 2t+1) = route 4j + t, digits 0 and 1
-                part[j][0] = fmaf(d0, float(ci[0] * 256 + ci[1]), part[j][0]);
-                part[j][1] = fmaf(d1, float(ci[2] * 256 + ci[3]), part[j][1]);
+                part[j][0] = fmaf(d0, float(ci[j][0] * 256 + ci[j][1]), part[j][0]);
+                part[j][1] = fmaf(d1, float(ci[j][2] * 256 + ci[j][3]), part[j][1]);
             }
+            if (blk < 7) cur = nxt;
         }
 #pragma unroll
         for (int j = 0; j < NT; ++j) {

@@ -358,7 +358,7 @@ def test_routing_ties_break_to_the_lower_index(dev, oracle):
 
 @pytest.mark.parametrize("n_experts,dim,ff,top_k,T", [(128, 2048, 768, 8, 1), (128, 2048, 768, 8, 16),
                                                      (128, 2048, 768, 8, 64), (8, 64, 32, 2, 5), (16, 256, 96, 4, 33),
-                                                     (8, 512, 256, 2, 40), (4, 512, 256, 2, 150), (4, 256, 512, 4, 3)])
+                                                     (8, 512, 256, 2, 40), (4, 512, 256, 2, 150), (4, 256, 512, 4, 3), (4, 320, 96, 2, 70)])
 def test_moe_layer_matches_oracle(dev, oracle, n_experts, dim, ff, top_k, T):
     import torch
 
