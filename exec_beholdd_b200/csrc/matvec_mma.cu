@@ -569,18 +569,22 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
     {
         __shared__ uint32_t s_warp[32][8];
         const uint32_t e = threadIdx.x;
+        // An expert with more than 32 routes is cut into ceil(n / 32) groups of equal size (+-1),
+        // `big` of them one route larger: equal sizes fall into the same size class, so the
+        // groups of one expert run in the same launch, next to each other, and share its weights
+        // through L2 instead of reading them from HBM once per launch.
         const uint32_t n = e < n_local ? s_counts[e] : 0u;
-        const uint32_t full = n / 32, rem = n % 32;
-        const int rcls = rem ? moe_cls(int(rem)) : 0;
-        const uint32_t u3 = uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(3)) / 256);
-        const uint32_t ur = rem ? uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(rcls)) / 256) : 0u;
+        const uint32_t parts = (n + 31) / 32, small_nb = parts ? n / parts : 0u, big = parts ? n % parts : 0u;
+        const int cls_small = small_nb ? moe_cls(int(small_nb)) : 0, cls_big = moe_cls(int(small_nb + 1));
+        const uint32_t u_small = small_nb ? uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls_small)) / 256) : 0u;
+        const uint32_t u_big = uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls_big)) / 256);
         uint32_t v[8];
         v[0] = n;
-        v[1] = full + (rem ? 1u : 0u);
+        v[1] = parts;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) v[2 + c] = (c == 3 ? full : 0u) + ((rem && rcls == c) ? 1u : 0u);
-        v[6] = chunks_x * (full * u3 + ur);
-        v[7] = chunks_a * (full * u3 + ur);
+        for (int c = 0; c < 4; ++c) v[2 + c] = (cls_big == c ? big : 0u) + ((small_nb && cls_small == c) ? parts - big : 0u);
+        v[6] = chunks_x * (big * u_big + (parts - big) * u_small);
+        v[7] = chunks_a * (big * u_big + (parts - big) * u_small);
         uint32_t incl[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -609,9 +613,8 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
             s_offsets[e] = base[0];
             uint32_t s0 = base[0], ng = base[1], bx = base[6], ba = base[7];
             uint32_t gc[4] = {base[2], base[3], base[4], base[5]};
-            uint32_t left = n;
-            while (left > 0 && ng < gmax) {
-                const uint32_t nb = left < 32 ? left : 32;
+            for (uint32_t part = 0; part < parts && ng < gmax; ++part) {
+                const uint32_t nb = small_nb + (part < big ? 1u : 0u);
                 const int cls = moe_cls(int(nb));
                 MoeGroup g;
                 g.expert_local = int32_t(e); g.slot0 = int32_t(s0); g.nb = int32_t(nb); g.cls = cls;
@@ -621,7 +624,6 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
                 glist[cls * gmax + gc[cls]++] = int32_t(ng);
                 groups[ng++] = g;
                 s0 += nb;
-                left -= nb;
             }
         }
         if (threadIdx.x == 0) {

@@ -102,22 +102,27 @@ __global__ void k_route_select(float* __restrict__ probs, uint32_t n_experts, ui
 // w[e][1]*x[t][1]) + ..., every product and every sum rounded to f32 (forward.rs:1330-1336 ->
 // cpu.rs:198-218). The chain of 'dim' dependent additions per (position, expert) is the floor
 // (about 4 us for 2048 columns); everything else is arranged to stay out of its way:
-//   * CTA = 8 experts x 32 positions, warp = 8 experts x 4 positions, one chain per lane;
-//   * 128-column tiles of w and x staged by 16-byte cp.async, three tiles in flight;
+//   * CTA = 8 experts x 8 positions = two warps (8 experts x 4 positions each), one chain per
+//     lane; small CTAs, so that a single position already spreads over 16 SMs;
+//   * 128-column tiles of w and x staged by 16-byte cp.async, six tiles in flight (a tile is
+//     consumed in about 0.27 us, its fetch takes over 1 us);
 //   * rows padded to 132 floats: the eight experts of a quarter-warp read 16 bytes each from
 //     disjoint banks, the position's x is a broadcast.
-constexpr int RT_EXP = 8, RT_TOK = 32, RT_COLS = 128, RT_BUF = 3, RT_LD = RT_COLS + 4;
-constexpr int RT_W_FLOATS = RT_EXP * RT_LD, RT_X_FLOATS = RT_TOK * RT_LD;
-constexpr size_t RT_SMEM = size_t(RT_BUF) * (RT_W_FLOATS + RT_X_FLOATS) * sizeof(float);
+// Two shapes (measured): up to 64 positions, CTAs of 8 positions with seven tiles in flight;
+// beyond, CTAs of 32 positions with three.
+constexpr int RT_EXP = 8, RT_COLS = 128, RT_LD = RT_COLS + 4, RT_W_FLOATS = RT_EXP * RT_LD;
+constexpr size_t rt_smem_bytes(int tok, int buf) { return size_t(buf) * (RT_W_FLOATS + tok * RT_LD) * sizeof(float); }
 
 __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
 }
 
 // Requires dim % 4 == 0 and 16-byte aligned w and x.
-__global__ void __launch_bounds__(256) k_router_logits_f32(const float* __restrict__ w, uint32_t n_experts, uint32_t dim,
+template <int RT_TOK, int RT_BUF>
+__global__ void __launch_bounds__(RT_TOK * RT_EXP) k_router_logits_f32(const float* __restrict__ w, uint32_t n_experts, uint32_t dim,
                                                            const float* __restrict__ x, uint32_t n_positions,
                                                            float* __restrict__ out) {
+    constexpr int RT_THREADS = RT_TOK * RT_EXP, RT_X_FLOATS = RT_TOK * RT_LD;
     extern __shared__ __align__(16) float rt_smem[];
     float* ws = rt_smem;                          // [buf][expert][RT_LD]
     float* xs = rt_smem + RT_BUF * RT_W_FLOATS;   // [buf][position][RT_LD]
@@ -126,15 +131,16 @@ __global__ void __launch_bounds__(256) k_router_logits_f32(const float* __restri
     const uint32_t tiles = (dim + RT_COLS - 1) / RT_COLS;
     auto load = [&](uint32_t tile, int buf) {
         const uint32_t c0 = tile * RT_COLS;
-        {   // w: 8 experts x 32 float4, one per thread
-            const uint32_t e = threadIdx.x >> 5, c = (threadIdx.x & 31) * 4;
+#pragma unroll
+        for (int i = 0; i < RT_EXP * 32 / RT_THREADS; ++i) {  // w: 8 experts x 32 float4
+            const uint32_t idx = threadIdx.x + RT_THREADS * i, e = idx >> 5, c = (idx & 31) * 4;
             float* dst = ws + buf * RT_W_FLOATS + e * RT_LD + c;
             if (e0 + e < n_experts && c0 + c < dim) cp_async16(dst, w + uint64_t(e0 + e) * dim + c0 + c);
             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {  // x: 32 positions x 32 float4
-            const uint32_t idx = threadIdx.x + 256 * i, t = idx >> 5, c = (idx & 31) * 4;
+        for (int i = 0; i < RT_TOK * 32 / RT_THREADS; ++i) {  // x: positions x 32 float4
+            const uint32_t idx = threadIdx.x + RT_THREADS * i, t = idx >> 5, c = (idx & 31) * 4;
             float* dst = xs + buf * RT_X_FLOATS + t * RT_LD + c;
             if (t0 + t < n_positions && c0 + c < dim) cp_async16(dst, x + uint64_t(t0 + t) * dim + c0 + c);
             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -157,11 +163,38 @@ __global__ void __launch_bounds__(256) k_router_logits_f32(const float* __restri
             const uint32_t n = min(uint32_t(RT_COLS), dim - tile * RT_COLS);  // a multiple of 4
             const float4* wt = reinterpret_cast<const float4*>(ws + buf * RT_W_FLOATS + el * RT_LD);
             const float4* xt = reinterpret_cast<const float4*>(xs + buf * RT_X_FLOATS + tl * RT_LD);
-#pragma unroll 8
-            for (uint32_t c = 0; c < n / 4; ++c) {  // products first, then the ordered additions
-                const float4 a = wt[c], b = xt[c];
-                const float p0 = __fmul_rn(a.x, b.x), p1 = __fmul_rn(a.y, b.y), p2 = __fmul_rn(a.z, b.z), p3 = __fmul_rn(a.w, b.w);
-                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, p0), p1), p2), p3);
+            // 32 columns at a time: the loads of the next 32 are issued before the 32 dependent
+            // additions of the current ones, so the chain never waits for shared memory.
+            const uint32_t n4 = n / 4;
+            float4 a[8], b[8];
+            float pr[32];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a[i] = uint32_t(i) < n4 ? wt[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                b[i] = uint32_t(i) < n4 ? xt[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            for (uint32_t c = 0; c < n4; c += 8) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    pr[4 * i] = __fmul_rn(a[i].x, b[i].x);
+                    pr[4 * i + 1] = __fmul_rn(a[i].y, b[i].y);
+                    pr[4 * i + 2] = __fmul_rn(a[i].z, b[i].z);
+                    pr[4 * i + 3] = __fmul_rn(a[i].w, b[i].w);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t cn = c + 8 + i;
+                    if (cn < n4) { a[i] = wt[cn]; b[i] = xt[cn]; }
+                }
+                const uint32_t live = min(32u, (n4 - c) * 4);  // 32 except in a ragged last tile
+                if (live == 32) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc = __fadd_rn(acc, pr[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (uint32_t(i) < live) acc = __fadd_rn(acc, pr[i]);
+                }
             }
         }
     }
@@ -290,17 +323,24 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     }
     if (counts_dev) BHD_CUDA(ctx, cudaMemsetAsync(counts_dev, 0, n_experts * sizeof(int32_t), s), "clearing expert counts");
     // Router logits in the CPU's summation order (forward.rs:1330-1336 -> cpu.rs:198-218).
-    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535ull * RT_TOK && router->cols % 4 == 0 &&
+    if (router->kind == BHD_TYPE_F32 && n_positions <= 65535ull * 8 && router->cols % 4 == 0 &&
         (reinterpret_cast<uintptr_t>(router->dev) & 15) == 0 && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0) {
         static int cached_device = -1;
         if (cached_device != ctx->device) {
-            BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RT_SMEM)),
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32<8, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rt_smem_bytes(8, 7))),
+                     "raising the shared memory limit");
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32<32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rt_smem_bytes(32, 3))),
                      "raising the shared memory limit");
             cached_device = ctx->device;
         }
-        k_router_logits_f32<<<dim3(unsigned((n_experts + RT_EXP - 1) / RT_EXP), unsigned((n_positions + RT_TOK - 1) / RT_TOK)), 256, RT_SMEM, s>>>(
-            reinterpret_cast<const float*>(router->dev), uint32_t(n_experts), uint32_t(router->cols), x_dev,
-            uint32_t(n_positions), probs);
+        const float* rw = reinterpret_cast<const float*>(router->dev);
+        const unsigned gx = unsigned((n_experts + RT_EXP - 1) / RT_EXP);
+        if (n_positions <= 64)
+            k_router_logits_f32<8, 7><<<dim3(gx, unsigned((n_positions + 7) / 8)), 64, rt_smem_bytes(8, 7), s>>>(
+                rw, uint32_t(n_experts), uint32_t(router->cols), x_dev, uint32_t(n_positions), probs);
+        else
+            k_router_logits_f32<32, 3><<<dim3(gx, unsigned((n_positions + 31) / 32)), 256, rt_smem_bytes(32, 3), s>>>(
+                rw, uint32_t(n_experts), uint32_t(router->cols), x_dev, uint32_t(n_positions), probs);
         BHD_LAUNCHED(ctx, "router logits kernel");
     } else {
         const int32_t st = bhd_launch_matvec_strict(ctx, router, 0, x_dev, probs, uint32_t(n_positions), 1.0f, 0, s);

@@ -26,9 +26,9 @@
 
 namespace {
 
-constexpr int TILE_ROWS = 64, CHUNK_K = 256, CONSUMERS = 4, THREADS = (CONSUMERS + 1) * 32;
-constexpr int BOX = 272;                    // packed bytes per row per chunk
-constexpr int W_BYTES = TILE_ROWS * BOX;    // 17408
+constexpr int CHUNK_K = 256;
+constexpr int BOX = 272;        // packed bytes per row per chunk
+constexpr int BOX_ROWS = 64;    // rows of the weight tensor map's box
 // Packed activations of one (slot, chunk): 8 blocks x 2 digits x 32 bytes in fragment order,
 // then 2^(e-14) as f32; padded to 576 bytes so that the eight routes a warp reads at once fall
 // into different shared-memory banks (144 words = 16 mod 32).
@@ -174,9 +174,11 @@ struct GroupedI8Params {
 };
 
 // NT MMAs per block: routes 4j..4j+3 in MMA j (NT = 1, 2, 4, 8 for groups of up to 4, 8, 16, 32 routes).
-template <int NT>
-__global__ void __launch_bounds__(THREADS) k_moe_grouped_i8(const __grid_constant__ CUtensorMap tmap0,
+// CW consumer warps (4 or 8) = 16 * CW rows per CTA.
+template <int NT, int CW>
+__global__ void __launch_bounds__((CW + 1) * 32) k_moe_grouped_i8(const __grid_constant__ CUtensorMap tmap0,
                                                             const __grid_constant__ CUtensorMap tmap1, const GroupedI8Params p) {
+    constexpr int TILE_ROWS = 16 * CW, CONSUMERS = CW, W_BYTES = TILE_ROWS * BOX;
     constexpr int X_MAX = NT * 4 * SLOT_BYTES;
     constexpr int STAGE = (W_BYTES + X_MAX + 127) / 128 * 128;
     if (blockIdx.y >= p.hdr->gcount[p.cls]) return;  // whole CTA, before anything is set up
@@ -203,7 +205,9 @@ __global__ void __launch_bounds__(THREADS) k_moe_grouped_i8(const __grid_constan
                 if (!mbar_wait(&empty[s], ((c / R) & 1) ^ 1)) { atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT); break; }
                 const uint32_t dst = smem0 + s * STAGE;
                 mbar_arrive_expect_tx(&full[s], W_BYTES + nb * SLOT_BYTES);
-                tma_load_2d(dst, tmap, int(c * (BOX / 2)), y, &full[s]);
+#pragma unroll
+                for (int h = 0; h < TILE_ROWS / BOX_ROWS; ++h)
+                    tma_load_2d(dst + h * BOX_ROWS * BOX, tmap, int(c * (BOX / 2)), y + h * BOX_ROWS, &full[s]);
                 bulk_load_1d(dst + W_BYTES, p.xq + (uint64_t(c) * p.n_slots + slot0) * SLOT_BYTES, nb * SLOT_BYTES, &full[s]);
             }
         }
@@ -300,13 +304,14 @@ __global__ void __launch_bounds__(THREADS) k_moe_grouped_i8(const __grid_constan
     }
 }
 
-template <int NT>
-int32_t launch_nt(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, GroupedI8Params p, uint32_t tiles, uint32_t group_bound,
-                  cudaStream_t s) {
+template <int NT, int CW>
+int32_t launch_nt(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, GroupedI8Params p, uint32_t group_bound, cudaStream_t s) {
+    constexpr int TILE_ROWS = 16 * CW, W_BYTES = TILE_ROWS * BOX, THREADS = (CW + 1) * 32;
     constexpr int STAGE = (W_BYTES + NT * 4 * SLOT_BYTES + 127) / 128 * 128;
     constexpr int RING = NT >= 4 ? 2 : 3;  // several CTAs per SM cover the latency the short ring leaves open
     constexpr size_t DYN = size_t(RING) * STAGE + 128;
-    auto kern = k_moe_grouped_i8<NT>;
+    const uint32_t tiles = uint32_t((w0->rows + TILE_ROWS - 1) / TILE_ROWS);
+    auto kern = k_moe_grouped_i8<NT, CW>;
     static int cached_device = -1;
     if (cached_device != ctx->device) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(DYN)), "raising the shared memory limit");
@@ -358,11 +363,10 @@ int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_
     p.n_slots = n_slots;
     p.cls = cls;
     p.ring = 0;
-    const uint32_t tiles = uint32_t((w0->rows + TILE_ROWS - 1) / TILE_ROWS);
     switch (cls) {
-        case 0: return launch_nt<1>(ctx, w0, w1, p, tiles, group_bound, s);
-        case 1: return launch_nt<2>(ctx, w0, w1, p, tiles, group_bound, s);
-        case 2: return launch_nt<4>(ctx, w0, w1, p, tiles, group_bound, s);
-        default: return launch_nt<8>(ctx, w0, w1, p, tiles, group_bound, s);
+        case 0: return launch_nt<1, 4>(ctx, w0, w1, p, group_bound, s);
+        case 1: return launch_nt<2, 4>(ctx, w0, w1, p, group_bound, s);
+        case 2: return launch_nt<4, 4>(ctx, w0, w1, p, group_bound, s);
+        default: return launch_nt<8, 8>(ctx, w0, w1, p, group_bound, s);
     }
 }
