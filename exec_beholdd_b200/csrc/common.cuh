@@ -175,8 +175,7 @@ __device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q6_K>(const uint8_t* r
 // ---- routed-expert plan records (written by k_moe_plan, read by the grouped kernels) ------
 struct MoeGroup {
     int32_t expert_local, slot0, nb, cls;
-    uint32_t blob_x, blob_a;  // offsets of the packed inputs of gate/up and of down, in 256-byte units
-    uint32_t pad0, pad1;
+    uint32_t pad0, pad1, pad2, pad3;
 };
 struct MoeHeader {
     uint32_t gcount[4];
@@ -189,14 +188,6 @@ int32_t bhd_launch_matvec_strict(bhd_ctx* ctx, const bhd_weight* w, uint64_t sla
                                  uint32_t batch, float scale, int accumulate, cudaStream_t s);
 int32_t bhd_launch_matvec_general(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                   uint64_t batch, float scale, int accumulate, cudaStream_t s);
-int32_t bhd_launch_moe_grouped_tcgen05(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr,
-                                       const void* groups, const int32_t* glist, uint32_t cls, uint32_t group_bound,
-                                       const void* x16, uint32_t x_rows, float* out0, float* out1, const float* slot_weight,
-                                       cudaStream_t s);
-int32_t bhd_launch_moe_slots_f16(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
-                                 const float* src, const float* src2, uint32_t K, uint32_t max_slots, void* out16,
-                                 cudaStream_t s);
-bool bhd_moe_tcgen05_usable(const bhd_ctx* ctx, const bhd_weight* w);
 int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
                                   const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* xq, uint32_t n_slots,
                                   float* out0, float* out1, const float* slot_weight, cudaStream_t s);

@@ -140,7 +140,7 @@ __global__ void k_f32_to_f16(const float* __restrict__ x, __half* __restrict__ o
     *reinterpret_cast<__half2*>(out + i + 2) = b;
 }
 
-constexpr int PLAIN_NG = 1, GROUPED_NG = 2;  // converter groups per instance (measured)
+constexpr int PLAIN_NG = 1;  // converter groups (a second one measured no faster)
 
 struct GemmParams {
     float* y;            // [M x N]
@@ -151,49 +151,26 @@ struct GemmParams {
     uint32_t k;          // columns
     uint32_t tn;         // tokens per tile: 64, 128 or 256
     uint32_t stages;     // fp16 stages in the ring
-    // Grouped (routed experts) mode, when `groups` is set: blockIdx.y walks the class list
-    // `glist`; the tile's tokens are the group's slots, its weights the group's expert slab.
-    const MoeHeader* hdr;
-    const MoeGroup* groups;
-    const int32_t* glist;
-    uint32_t cls;
-    float* y1;                 // output of the second weight tensor (blockIdx.z == 1)
-    const float* slot_weight;  // optional per-slot factor (down projection)
-    // Split activations: x = hi + lo in fp16 (22 bits). The B tile then holds tn rows of hi followed by
-    // tn rows of lo (lo rows live `lo_row_offset` rows further down the activation matrix) and the
-    // epilogue adds the two column halves.
-    uint32_t split, lo_row_offset;
 };
 
-// GROUPED = false: plain prefill matmul. GROUPED = true: routed experts (group list, two weight tensors, split
-// operands); compile-time so that the prefill instance carries none of the grouped code.
-template <bool GROUPED, int NG>
+template <int NG>
 __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const __grid_constant__ CUtensorMap tmap_w0,
-                                                                const __grid_constant__ CUtensorMap tmap_w1,
                                                                 const __grid_constant__ CUtensorMap tmap_x,
                                                                 const GemmParams p) {
-    constexpr bool SPLIT = GROUPED;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t pk_full[2], pk_empty[2], a_full[8], b_full[8], st_empty[8], tmem_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-    const uint32_t bn = SPLIT ? 2 * p.tn : p.tn;  // MMA N = rows of the B tile
-    const uint32_t a_bytes = SPLIT ? 2 * A_BYTES : A_BYTES;  // split mode keeps a second tile: the rounding remainder of d*q
+    const uint32_t bn = p.tn;  // MMA N = rows of the B tile
+    const uint32_t a_bytes = A_BYTES;
     const uint32_t stage_bytes = a_bytes + bn * 128u;
     const uint32_t pack_addr = smem0, stage_addr = smem0 + 2 * PACK_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint32_t m0 = blockIdx.y * p.tn, m_end = p.m, row_base = p.row_base;
-    if (GROUPED) {
-        if (blockIdx.y >= p.hdr->gcount[p.cls]) return;  // whole CTA, before anything is set up
-        const MoeGroup g = p.groups[p.glist[blockIdx.y]];
-        m0 = uint32_t(g.slot0);
-        m_end = m0 + uint32_t(g.nb);
-        row_base = uint32_t(g.expert_local) * p.n_rows;
-    }
-    const CUtensorMap* tmap_w = (GROUPED && blockIdx.z) ? &tmap_w1 : &tmap_w0;
-    float* const yout = (GROUPED && blockIdx.z) ? p.y1 : p.y;
+    const uint32_t m0 = blockIdx.y * p.tn, m_end = p.m, row_base = p.row_base;
+    const CUtensorMap* tmap_w = &tmap_w0;
+    float* const yout = p.y;
     const uint32_t n0 = blockIdx.x * TILE_N;
     const uint32_t slices = (p.k + SLICE_K - 1) / SLICE_K, chunks = (p.k + CHUNK_K - 1) / CHUNK_K;
     const uint32_t S = p.stages;
@@ -228,9 +205,6 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                     if (!mbar_wait(&st_empty[s], ((it / S) & 1) ^ 1)) { give_up(); break; }
                     mbar_arrive_expect_tx(&b_full[s], bn * 128u);
                     tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
-                    if (SPLIT)
-                        tma_load_2d(stage_addr + s * stage_bytes + a_bytes + p.tn * 128u, &tmap_x, int(it * SLICE_K),
-                                    int(p.lo_row_offset + m0), &b_full[s]);
                 }
             }
         }
@@ -244,19 +218,15 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                 if (aborted() || !mbar_wait(&b_full[s], par) || !mbar_wait(&a_full[s], par)) { give_up(); ok = false; break; }
                 tc_fence_after();
                 const uint64_t da = umma_desc(stage_addr + s * stage_bytes), db = umma_desc(stage_addr + s * stage_bytes + a_bytes);
-                const uint64_t dl = umma_desc(stage_addr + s * stage_bytes + A_BYTES);
 #pragma unroll
-                for (uint32_t k16 = 0; k16 < 4; ++k16) {  // 32 bytes (16 fp16) further along the swizzled row per step
+                for (uint32_t k16 = 0; k16 < 4; ++k16)  // 32 bytes (16 fp16) further along the swizzled row per step
                     tc_mma_f16(tmem_base, da + 2 * k16, db + 2 * k16, idesc, (it | k16) ? 1u : 0u);
-                    if (SPLIT) tc_mma_f16(tmem_base, dl + 2 * k16, db + 2 * k16, idesc, 1u);
-                }
                 tc_commit(&st_empty[s]);  // arrives when these MMAs have finished reading the stage
             }
             tc_commit(&tmem_full);        // arrives when every MMA issued so far is complete
         }
     } else {
-        // ---- converters: two groups of four warps take alternating 64-column slices, so the latency of one
-        // group's convert -> fence -> arrive chain hides behind the other's; thread = one weight row ----
+        // ---- converters: NG groups of four warps take alternating 64-column slices; thread = one weight row ----
         const uint32_t ct = threadIdx.x - 64;   // 0..255
         const uint32_t row = ct & 127, grp = ct >> 7;  // grp is uniform per warp
         const uint32_t sw = row & 7, a_row_off = (row >> 3) * 1024 + sw * 128;
@@ -288,7 +258,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                             const int i = 2 * ch + j;
                             q[j] = blk == 0 ? __funnelshift_r(w[i], w[i + 1], 16) : w[9 + i];
                         }
-                        uint32_t h[4], l[4];
+                        uint32_t h[4];
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const uint32_t u = q[j] ^ 0x80808080u;  // 0x6400 | (q + 128) is the fp16 q + 1152
@@ -298,15 +268,9 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                             const __half2 a = __hmul2(qa, d2), b = __hmul2(qb, d2);
                             h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
                             h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
-                            if (SPLIT) {  // q*d - fp16(q*d), exact in one fused operation
-                                const __half2 ra = __hfma2(qa, d2, __hneg2(a)), rb = __hfma2(qb, d2, __hneg2(b));
-                                l[2 * j] = *reinterpret_cast<const uint32_t*>(&ra);
-                                l[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&rb);
-                            }
                         }
                         const uint32_t chunk16 = uint32_t(blk * 4 + ch) ^ sw;  // 128B swizzle: chunk index XOR row mod 8
                         sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
-                        if (SPLIT) sts128(a_dst + A_BYTES + chunk16 * 16, make_uint4(l[0], l[1], l[2], l[3]));
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
@@ -327,20 +291,12 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                 if (m0 + col >= m_end) break;            // uniform across the warp
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((q * 32u) << 16) + col, r);
-                if (SPLIT) {  // add the lo half of the columns
-                    uint32_t r2[32];
-                    tc_ld32(tmem_base + ((q * 32u) << 16) + p.tn + col, r2);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-                }
                 if (n < p.n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t m = m0 + col + j;
                         if (m < m_end) {
-                            float v = __uint_as_float(r[j]);
-                            if (GROUPED && p.slot_weight) v = __fmul_rn(v, p.slot_weight[m]);
-                            yout[uint64_t(m) * p.n_rows + n] = v;
+                            yout[uint64_t(m) * p.n_rows + n] = __uint_as_float(r[j]);
                         }
                     }
                 }
@@ -406,7 +362,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     }
     static int cached_device = -1;
     if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<false, PLAIN_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<PLAIN_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
                  "raising the shared memory limit");
         cached_device = ctx->device;
     }
@@ -419,131 +375,8 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     p.k = K;
     p.tn = tn;
     p.stages = stages;
-    p.hdr = nullptr;
-    p.groups = nullptr;
-    p.glist = nullptr;
-    p.cls = 0;
-    p.y1 = nullptr;
-    p.slot_weight = nullptr;
-    p.split = 0;
-    p.lo_row_offset = 0;
-    k_gemm_q8_tcgen05<false, PLAIN_NG><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), gemm_threads(PLAIN_NG), dyn, s>>>(map_w, map_w, map_x, p);
+    k_gemm_q8_tcgen05<PLAIN_NG><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), gemm_threads(PLAIN_NG), dyn, s>>>(map_w, map_x, p);
     BHD_LAUNCHED(ctx, "tcgen05 matmul kernel");
     *handled = true;
-    return BHD_OK;
-}
-
-namespace {
-
-// fp16 activations of the routed experts in slot order (routes sorted by expert):
-// mode 0: row of slot = x[position of the slot's route] (the token-to-expert gather);
-// mode 1: row of slot = silu(g[slot]) * u[slot] (crates/beholdd-kernel/src/vecops.rs:91-111, limit 0).
-__global__ void k_moe_slots_f16(int mode, const MoeHeader* __restrict__ hdr, const int32_t* __restrict__ slot_route,
-                                uint32_t top_k, const float* __restrict__ src, const float* __restrict__ src2, uint32_t K,
-                                __half* __restrict__ out, uint32_t lo_row_offset, uint32_t* __restrict__ status) {
-    const uint32_t slot = blockIdx.y;
-    if (slot >= hdr->local_routes) return;
-    const uint32_t k = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (k >= K) return;
-    float4 v;
-    if (mode == 0) {
-        v = *reinterpret_cast<const float4*>(src + uint64_t(uint32_t(slot_route[slot]) / top_k) * K + k);
-    } else {
-        v = *reinterpret_cast<const float4*>(src + uint64_t(slot) * K + k);
-        const float4 u = *reinterpret_cast<const float4*>(src2 + uint64_t(slot) * K + k);
-        v.x = __fmul_rn(__fdiv_rn(v.x, __fadd_rn(1.0f, expf(-v.x))), u.x);
-        v.y = __fmul_rn(__fdiv_rn(v.y, __fadd_rn(1.0f, expf(-v.y))), u.y);
-        v.z = __fmul_rn(__fdiv_rn(v.z, __fadd_rn(1.0f, expf(-v.z))), u.z);
-        v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.0f, expf(-v.w))), u.w);
-    }
-    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-    const float2 fa = __half22float2(a), fb = __half22float2(b);
-    if (!(fabsf(fa.x) <= 65504.f && fabsf(fa.y) <= 65504.f && fabsf(fb.x) <= 65504.f && fabsf(fb.y) <= 65504.f))
-        atomicOr(status, BHD_DEV_ACTIVATION_RANGE);
-    __half* dst = out + uint64_t(slot) * K + k;
-    *reinterpret_cast<__half2*>(dst) = a;
-    *reinterpret_cast<__half2*>(dst + 2) = b;
-    // remainder x - hi, so that hi + lo carries 22 bits
-    __half* dlo = out + uint64_t(lo_row_offset + slot) * K + k;
-    *reinterpret_cast<__half2*>(dlo) = __floats2half2_rn(v.x - fa.x, v.y - fa.y);
-    *reinterpret_cast<__half2*>(dlo + 2) = __floats2half2_rn(v.z - fb.x, v.w - fb.y);
-}
-
-bool encode_weight_map(bhd_ctx* ctx, const bhd_weight* w, CUtensorMap* map) {
-    const cuuint64_t dims[2] = {w->row_bytes / 2, w->rows * w->slabs};
-    const cuuint64_t strides[1] = {w->row_bytes};
-    const cuuint32_t box[2] = {PACK_ROW / 2, TILE_N};
-    const cuuint32_t estr[2] = {1, 1};
-    return reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->dev, dims, strides, box, estr,
-                                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-}  // namespace
-
-bool bhd_moe_tcgen05_usable(const bhd_ctx* ctx, const bhd_weight* w) {
-    return ctx->tmap_encode && w->kind == BHD_TYPE_Q8_0 && w->row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(w->dev) & 15) == 0 &&
-           w->cols % 32 == 0 && w->cols > 0 && w->rows * w->slabs <= 0x7fffffffull;
-}
-
-int32_t bhd_launch_moe_slots_f16(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
-                                 const float* src, const float* src2, uint32_t K, uint32_t max_slots, void* out16,
-                                 cudaStream_t s) {
-    if (max_slots == 0) return BHD_OK;
-    // out16 holds 2 * max_slots rows: the hi halves, then the lo halves
-    k_moe_slots_f16<<<dim3((K / 4 + 127) / 128, max_slots), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, top_k,
-                                                                         src, src2, K, static_cast<__half*>(out16), max_slots,
-                                                                         ctx->status_dev);
-    BHD_LAUNCHED(ctx, mode ? "expert gating kernel" : "token gather kernel");
-    return BHD_OK;
-}
-
-// Grouped expert matmul on the tensor cores for the groups of one size class (9..32 routes):
-// one CTA per (group, 128-row tile of the expert matrix[, gate|up]).
-int32_t bhd_launch_moe_grouped_tcgen05(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr,
-                                       const void* groups, const int32_t* glist, uint32_t cls, uint32_t group_bound,
-                                       const void* x16, uint32_t x_rows, float* out0, float* out1, const float* slot_weight,
-                                       cudaStream_t s) {
-    if (group_bound == 0) return BHD_OK;
-    const uint32_t K = uint32_t(w0->cols), N = uint32_t(w0->rows), tn = 32, stages = 3;
-    const size_t dyn = 1024 + 2 * size_t(PACK_BYTES) + size_t(stages) * (2 * A_BYTES + 2 * tn * 128u);
-    CUtensorMap m0, m1, mx;
-    if (!encode_weight_map(ctx, w0, &m0) || !encode_weight_map(ctx, w1 ? w1 : w0, &m1))
-        return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the expert tensor map", bhd_device_name());
-    const cuuint64_t dims[2] = {K, 2 * uint64_t(x_rows)};  // hi rows, then lo rows
-    const cuuint64_t strides[1] = {uint64_t(K) * 2};
-    const cuuint32_t box[2] = {SLICE_K, tn};
-    const cuuint32_t estr[2] = {1, 1};
-    if (reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode)(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x16), dims, strides, box,
-                                                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the activation tensor map", bhd_device_name());
-    static int cached_device = -1;
-    if (cached_device != ctx->device) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<true, GROUPED_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
-                 "raising the shared memory limit");
-        cached_device = ctx->device;
-    }
-    GemmParams p;
-    p.y = out0;
-    p.status = ctx->status_dev;
-    p.n_rows = N;
-    p.row_base = 0;
-    p.m = 0;
-    p.k = K;
-    p.tn = tn;
-    p.stages = stages;
-    p.hdr = static_cast<const MoeHeader*>(hdr);
-    p.groups = static_cast<const MoeGroup*>(groups);
-    p.glist = glist;
-    p.cls = cls;
-    p.y1 = out1;
-    p.slot_weight = slot_weight;
-    p.split = 1;
-    p.lo_row_offset = x_rows;
-    k_gemm_q8_tcgen05<true, GROUPED_NG><<<dim3((N + TILE_N - 1) / TILE_N, group_bound, w1 ? 2 : 1), gemm_threads(GROUPED_NG), dyn, s>>>(m0, m1, mx, p);
-    BHD_LAUNCHED(ctx, "tcgen05 grouped expert kernel");
     return BHD_OK;
 }

@@ -505,20 +505,18 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
 }
 
 // ---- grouped experts (qwen3moe routed block) ---------------------------------------------------
-// Routes are sorted by expert; every expert's routes are cut into groups of up to 32 vectors and
-// each (group, 64-row tile) of an expert matrix is one CTA streaming all columns. Group sizes
-// pick the column layout: up to 8 vectors use split (hi + lo) activations, larger groups use
-// plain fp16 activations with 8 vectors per n-tile.
+// Routes are sorted by expert; every expert's routes are cut into groups of up to 32 and each
+// (group, row tile) of an expert matrix is one CTA of the integer grouped kernel
+// (moe_grouped_i8.cu) streaming all columns. The size class of a group (up to 4 / 8 / 16 / 32
+// routes) picks the kernel instance.
 
-__host__ __device__ constexpr int moe_nt(int cls) { return cls == 0 ? 1 : (cls == 3 ? 4 : 2); }
-__host__ __device__ constexpr bool moe_split(int cls) { return cls < 2; }
 __host__ __device__ constexpr int moe_cls(int nb) { return nb <= 4 ? 0 : (nb <= 8 ? 1 : (nb <= 16 ? 2 : 3)); }
 
 // One CTA. Sorts the local routes by (expert, route index) -- a stable counting sort through a
 // route bitmap per expert, so the order is deterministic -- and lists the groups.
 __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ experts, const float* __restrict__ weights,
                                                    uint32_t n_routes, uint32_t first_expert, uint32_t n_local,
-                                                   uint32_t chunks_x, uint32_t chunks_a, MoeHeader* hdr,
+                                                   MoeHeader* hdr,
                                                    uint32_t* counts, uint32_t* offsets, int32_t* route_slot,
                                                    int32_t* slot_route, float* slot_weight, MoeGroup* groups,
                                                    int32_t* glist, uint32_t gmax, uint32_t* bitmap, uint32_t* prefix,
@@ -561,13 +559,13 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
     }
     __syncthreads();
     // Groups of up to 32 routes per expert, in expert order. Thread e describes expert e's groups
-    // (n / 32 full ones and a remainder); a block-wide exclusive scan of eight per-expert totals
-    // (routes, groups, groups per size class, fragment-blob units of the two inputs) gives every
-    // expert its first slot, first group index, first index in each class list and blob offsets,
+    // (n / 32 full ones and a remainder); a block-wide exclusive scan of six per-expert totals
+    // (routes, groups, groups per size class) gives every expert its first slot, first group
+    // index and first index in each class list,
     // so the lists come out exactly as a sequential walk over the experts would write them.
     // Requires n_local <= blockDim.x.
     {
-        __shared__ uint32_t s_warp[32][8];
+        __shared__ uint32_t s_warp[32][6];
         const uint32_t e = threadIdx.x;
         // An expert with more than 32 routes is cut into ceil(n / 32) groups of equal size (+-1),
         // `big` of them one route larger: equal sizes fall into the same size class, so the
@@ -576,18 +574,14 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
         const uint32_t n = e < n_local ? s_counts[e] : 0u;
         const uint32_t parts = (n + 31) / 32, small_nb = parts ? n / parts : 0u, big = parts ? n % parts : 0u;
         const int cls_small = small_nb ? moe_cls(int(small_nb)) : 0, cls_big = moe_cls(int(small_nb + 1));
-        const uint32_t u_small = small_nb ? uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls_small)) / 256) : 0u;
-        const uint32_t u_big = uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls_big)) / 256);
-        uint32_t v[8];
+        uint32_t v[6];
         v[0] = n;
         v[1] = parts;
 #pragma unroll
         for (int c = 0; c < 4; ++c) v[2 + c] = (cls_big == c ? big : 0u) + ((small_nb && cls_small == c) ? parts - big : 0u);
-        v[6] = chunks_x * (big * u_big + (parts - big) * u_small);
-        v[7] = chunks_a * (big * u_big + (parts - big) * u_small);
-        uint32_t incl[8];
+        uint32_t incl[6];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < 6; ++q) {
             incl[q] = v[q];
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
@@ -597,9 +591,9 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
             if (lane == 31) s_warp[warp][q] = incl[q];
         }
         __syncthreads();
-        uint32_t base[8], total[8];
+        uint32_t base[6], total[6];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < 6; ++q) {
             base[q] = 0;
             total[q] = 0;
             for (int w = 0; w < n_warps; ++w) {
@@ -611,16 +605,14 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
         }
         if (e < n_local) {
             s_offsets[e] = base[0];
-            uint32_t s0 = base[0], ng = base[1], bx = base[6], ba = base[7];
+            uint32_t s0 = base[0], ng = base[1];
             uint32_t gc[4] = {base[2], base[3], base[4], base[5]};
             for (uint32_t part = 0; part < parts && ng < gmax; ++part) {
                 const uint32_t nb = small_nb + (part < big ? 1u : 0u);
                 const int cls = moe_cls(int(nb));
                 MoeGroup g;
                 g.expert_local = int32_t(e); g.slot0 = int32_t(s0); g.nb = int32_t(nb); g.cls = cls;
-                g.blob_x = bx; g.blob_a = ba; g.pad0 = g.pad1 = 0;
-                bx += chunks_x * uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls)) / 256);
-                ba += chunks_a * uint32_t(xblob_bytes(BHD_TYPE_Q8_0, moe_nt(cls)) / 256);
+                g.pad0 = g.pad1 = g.pad2 = g.pad3 = 0;
                 glist[cls * gmax + gc[cls]++] = int32_t(ng);
                 groups[ng++] = g;
                 s0 += nb;
@@ -650,70 +642,6 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
             slot_weight[slot] = weights[r];
         }
     }
-}
-
-// Packs the inputs of every group. mode 0: rows of x gathered by position (the token-to-expert
-// gather); mode 1: silu(gate) * up of the group's slots. grid (chunks, max groups), 512 threads.
-__global__ void k_moe_pack(int mode, const MoeHeader* __restrict__ hdr, const MoeGroup* __restrict__ groups,
-                           const int32_t* __restrict__ slot_route, uint32_t top_k, const float* __restrict__ src,
-                           const float* __restrict__ src2, uint32_t K, uint8_t* __restrict__ blob,
-                           uint32_t* __restrict__ status, int skip_from_cls) {
-    __shared__ float stepsum[STEPS][8];
-    if (blockIdx.y >= hdr->total_groups) return;
-    const MoeGroup g = groups[blockIdx.y];
-    if (g.cls >= skip_from_cls) return;  // those groups take the tcgen05 path, which reads plain fp16 rows
-    const int nt = moe_nt(g.cls);
-    const bool split = moe_split(g.cls);
-    const int col = (threadIdx.x & 31) >> 2;
-    uint8_t* cb = blob + uint64_t(mode ? g.blob_a : g.blob_x) * 256 + uint64_t(blockIdx.x) * xblob_bytes(BHD_TYPE_Q8_0, nt);
-    for (int j = 0; j < nt; ++j) {
-        const int b = split ? 4 * j + (col >> 1) : 8 * j + col;
-        const float* row = nullptr;
-        const float* row2 = nullptr;
-        if (b < g.nb) {
-            const uint32_t slot = uint32_t(g.slot0 + b);
-            if (mode == 0) row = src + uint64_t(uint32_t(slot_route[slot]) / top_k) * K;
-            else { row = src + uint64_t(slot) * K; row2 = src2 + uint64_t(slot) * K; }
-        }
-        pack_tile(BHD_TYPE_Q8_0, row, row2, split && (col & 1), blockIdx.x, K, nt, j, cb, stepsum, status);
-    }
-}
-
-struct MoeRun {
-    const MoeHeader* hdr;
-    const MoeGroup* groups;
-    const int32_t* glist;      // the class's group indices
-    const uint8_t* blob;
-    float* out0;               // [slot][rows] of matrix 0 (gate, or down)
-    float* out1;               // [slot][rows] of matrix 1 (up)
-    const float* slot_weight;  // down only: route weight per slot
-    uint32_t* status;
-    uint32_t rows, chunks;
-    int use_blob_a;
-};
-
-template <int CLS>
-__global__ void __launch_bounds__(THREADS) k_moe_grouped(const __grid_constant__ CUtensorMap tmap0,
-                                                         const __grid_constant__ CUtensorMap tmap1, const MoeRun r,
-                                                         int n_stages_ring) {
-    if (blockIdx.y >= r.hdr->gcount[CLS]) return;
-    const MoeGroup g = r.groups[r.glist[blockIdx.y]];
-    MatvecParams p;
-    p.xblob = r.blob + uint64_t(r.use_blob_a ? g.blob_a : g.blob_x) * 256;
-    p.y = (blockIdx.z ? r.out1 : r.out0) + uint64_t(g.slot0) * r.rows;
-    p.partial = nullptr;
-    p.counters = nullptr;
-    p.status = r.status;
-    p.rows = r.rows;
-    p.row_base = uint32_t(g.expert_local) * r.rows;
-    p.batch = uint32_t(g.nb);
-    p.chunks = r.chunks;
-    p.total_stages = (blockIdx.x + 1) * r.chunks;  // this CTA streams exactly one whole tile
-    p.per_cta = r.chunks;
-    p.scale = 1.0f;
-    p.accumulate = 0;
-    p.vec_scale = r.slot_weight ? r.slot_weight + g.slot0 : nullptr;
-    run_stage_range<BHD_TYPE_Q8_0, moe_nt(CLS), moe_split(CLS)>(blockIdx.z ? &tmap1 : &tmap0, p, blockIdx.x, n_stages_ring);
 }
 
 // y[t] (+)= ((0 + d[slot(t,0)]) + d[slot(t,1)]) + ...: the reference's accumulation order
@@ -868,67 +796,19 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
 
 namespace {
 
-template <int CLS>
-int32_t launch_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const MoeRun& run, uint32_t tiles,
-                       uint32_t group_bound, cudaStream_t s) {
-    using S = Smem<BHD_TYPE_Q8_0, moe_nt(CLS)>;
-    auto kern = k_moe_grouped<CLS>;
-    static int ring = 0, cached_device = -1;
-    if (cached_device != ctx->device) {
-        int r = 4;
-        size_t dyn = size_t(r) * S::STAGE + 128;
-        if (dyn > 200 * 1024) { r = 3; dyn = size_t(r) * S::STAGE + 128; }
-        BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
-        ring = r;
-        cached_device = ctx->device;
-    }
-    if (group_bound == 0) return BHD_OK;
-    CUtensorMap m0, m1;
-    memcpy(&m0, w0->tmap, sizeof(m0));
-    memcpy(&m1, (w1 ? w1 : w0)->tmap, sizeof(m1));
-    kern<<<dim3(tiles, group_bound, w1 ? 2 : 1), THREADS, size_t(ring) * S::STAGE + 128, s>>>(m0, m1, run, ring);
-    BHD_LAUNCHED(ctx, "grouped expert kernel");
-    return BHD_OK;
-}
-
-// Size classes from this one on run on the integer tensor-core kernel (moe_grouped_i8.cu)
-// when the tensors qualify; 0 = every class.
-constexpr uint32_t I8_FROM_CLS = 0;
-
-// xq: block-floating byte activations in slot order for the integer kernel; x16: fp16 rows in slot
-// order for the tcgen05 kernel (both nullptr: every class uses the fp16 mma.sync kernel).
-int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, MoeRun run, const int32_t* glist,
-                           uint32_t gmax, uint32_t tiles, uint32_t n_routes, uint32_t n_local, cudaStream_t s,
-                           const void* x16 = nullptr, const void* xq = nullptr) {
-    // A class can only occur when there are enough routes for its smallest group.
+// One launch of the integer grouped kernel per size class that can occur: a class only exists
+// when there are enough routes for its smallest group (5 / 9 / 17).
+int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
+                           const int32_t* glist, uint32_t gmax, uint32_t n_routes, uint32_t n_local, const void* xq, float* out0,
+                           float* out1, const float* slot_weight, cudaStream_t s) {
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
-    int32_t st = BHD_OK;
-    auto i8 = [&](uint32_t cls, uint32_t bound) {
-        return bhd_launch_moe_grouped_i8(ctx, w0, w1, run.hdr, run.groups, glist + cls * gmax, cls, bound, xq, n_routes, run.out0, run.out1,
-                                         run.slot_weight, s);
-    };
-    run.glist = glist + 0 * gmax;
-    st = (xq && I8_FROM_CLS <= 0) ? i8(0, small) : launch_grouped<0>(ctx, w0, w1, run, tiles, small, s);
-    if (st != BHD_OK) return st;
-    if (n_routes >= 5) {
-        run.glist = glist + 1 * gmax;
-        const uint32_t bound = small < n_routes / 5 ? small : n_routes / 5;
-        st = (xq && I8_FROM_CLS <= 1) ? i8(1, bound) : launch_grouped<1>(ctx, w0, w1, run, tiles, bound, s);
-        if (st != BHD_OK) return st;
-    }
-    if (n_routes >= 9) {
-        const uint32_t bound = small < n_routes / 9 ? small : n_routes / 9;
-        run.glist = glist + 2 * gmax;
-        if (xq && I8_FROM_CLS <= 2) st = i8(2, bound);
-        else if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 2, bound, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
-        else st = launch_grouped<2>(ctx, w0, w1, run, tiles, bound, s);
-        if (st != BHD_OK) return st;
-    }
-    if (n_routes >= 17) {
-        run.glist = glist + 3 * gmax;
-        if (xq && I8_FROM_CLS <= 3) st = i8(3, n_routes / 17);
-        else if (x16) st = bhd_launch_moe_grouped_tcgen05(ctx, w0, w1, run.hdr, run.groups, run.glist, 3, n_routes / 17, x16, n_routes, run.out0, run.out1, run.slot_weight, s);
-        else st = launch_grouped<3>(ctx, w0, w1, run, tiles, n_routes / 17, s);
+    const uint32_t least[4] = {1, 5, 9, 17};
+    for (uint32_t cls = 0; cls < 4; ++cls) {
+        if (n_routes < least[cls]) break;
+        const uint32_t by_size = n_routes / least[cls];
+        const uint32_t bound = cls == 3 ? by_size : (small < by_size ? small : by_size);
+        const int32_t st = bhd_launch_moe_grouped_i8(ctx, w0, w1, hdr, groups, glist + cls * gmax, cls, bound, xq, n_routes, out0, out1,
+                                                     slot_weight, s);
         if (st != BHD_OK) return st;
     }
     return BHD_OK;
@@ -936,27 +816,24 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
 
 }  // namespace
 
-// Fast path of bhd_moe_experts: plan (sort routes by expert), gather + pack, grouped gate/up,
-// SiLU gating fused into the packing of the down input, grouped down scaled by the route
-// weight, combine in route order. Sets *handled = false when the tensors do not meet the
-// alignment rules of the TMA path.
+// Fast path of bhd_moe_experts: plan (sort routes by expert, cut into groups), token gather +
+// block-floating packing, grouped gate/up, SiLU gating fused into the packing of the down
+// input, grouped down scaled by the route weight, combine in route order. Sets *handled = false
+// when the tensors do not meet the rules of the TMA path (Q8_0, 16-byte aligned rows).
 int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
                              const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
                              uint32_t first_expert, uint32_t n_local, float* y, int accumulate, cudaStream_t s,
                              bool* handled) {
     *handled = false;
-    if (!gate->tmap_ok || !up->tmap_ok || !down->tmap_ok) return BHD_OK;
+    if (!bhd_moe_i8_usable(gate) || !bhd_moe_i8_usable(up) || !bhd_moe_i8_usable(down)) return BHD_OK;
     if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return BHD_OK;
     const uint64_t ff = gate->rows, dim = gate->cols;
-    if (dim % 4 != 0 || ff % 4 != 0) return BHD_OK;
+    if (dim % 8 != 0 || ff % 8 != 0) return BHD_OK;
     const uint64_t R64 = T * top_k;
     if (R64 > (1u << 22) || n_local > 1024) return BHD_OK;
     const uint32_t R = uint32_t(R64), E = n_local;
-    const uint32_t chunks_x = uint32_t((dim + CHUNK_K - 1) / CHUNK_K), chunks_a = uint32_t((ff + CHUNK_K - 1) / CHUNK_K);
     const uint32_t words = (R + 31) / 32;
     const uint32_t gmax = E + R / 32 + 1;
-    const uint64_t nt_sum = R / 4 + gmax;  // every group has nt <= nb / 4 + 1
-    const size_t unit = size_t(xblob_bytes(BHD_TYPE_Q8_0, 1));
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 256); return o; };
     const size_t o_hdr = take(sizeof(MoeHeader)), o_counts = take(4 * size_t(E)), o_offsets = take(4 * size_t(E + 1));
@@ -964,13 +841,7 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const size_t o_groups = take(sizeof(MoeGroup) * size_t(gmax)), o_glist = take(4 * 4 * size_t(gmax));
     const size_t o_bitmap = take(4 * size_t(E) * words), o_prefix = take(4 * size_t(E) * words);
     const size_t o_g = take(4 * size_t(R) * ff), o_u = take(4 * size_t(R) * ff), o_d = take(4 * size_t(R) * dim);
-    const size_t o_bx = take(nt_sum * unit * chunks_x), o_ba = take(nt_sum * unit * chunks_a);
-    const bool i8 = bhd_moe_i8_usable(gate) && bhd_moe_i8_usable(up) && bhd_moe_i8_usable(down) && dim % 8 == 0 && ff % 8 == 0;
-    const bool tc = !(i8 && I8_FROM_CLS <= 2) && R >= 9 && R <= 65535 && bhd_moe_tcgen05_usable(ctx, gate) &&
-                    bhd_moe_tcgen05_usable(ctx, up) && bhd_moe_tcgen05_usable(ctx, down);
-    const bool fp16_pack = !(i8 && I8_FROM_CLS == 0);  // some class still runs on the fp16 mma.sync kernel
-    const size_t o_x16 = take(tc ? 4 * size_t(R) * dim : 0), o_a16 = take(tc ? 4 * size_t(R) * ff : 0);  // hi + lo fp16 rows
-    const size_t o_xq = take(i8 ? bhd_moe_slots_i8_bytes(uint32_t(dim), R) : 0), o_aq = take(i8 ? bhd_moe_slots_i8_bytes(uint32_t(ff), R) : 0);
+    const size_t o_xq = take(bhd_moe_slots_i8_bytes(uint32_t(dim), R)), o_aq = take(bhd_moe_slots_i8_bytes(uint32_t(ff), R));
     int32_t st = bhd_ensure_workspace(ctx, off, s);
     if (st != BHD_OK) return st;
     uint8_t* ws = ctx->workspace;
@@ -992,57 +863,18 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
         plan_device = ctx->device;
     }
     // one thread per local expert in the group-building step
-    k_moe_plan<<<1, (R <= 256 && E <= 256) ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, chunks_x, chunks_a, hdr,
+    k_moe_plan<<<1, (R <= 256 && E <= 256) ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, hdr,
                                   reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
                                   route_slot, slot_route, slot_weight, groups, glist, gmax,
                                   reinterpret_cast<uint32_t*>(ws + o_bitmap), reinterpret_cast<uint32_t*>(ws + o_prefix),
                                   ctx->status_dev, plan_on_chip);
     BHD_LAUNCHED(ctx, "route planning kernel");
-    const uint32_t group_bound = gmax < R ? gmax : R;
-    // classes from skip_cls on do not read the fp16 fragment blobs
-    const int skip_cls = i8 ? int(I8_FROM_CLS) : (tc ? 2 : 4);
-    if (fp16_pack) {
-        k_moe_pack<<<dim3(chunks_x, group_bound), STEPS * 32, 0, s>>>(0, hdr, groups, slot_route, top_k, x, nullptr, uint32_t(dim),
-                                                                      ws + o_bx, ctx->status_dev, skip_cls);
-        BHD_LAUNCHED(ctx, "token gather and packing kernel");
-    }
-    if (i8 && (st = bhd_launch_moe_slots_i8(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
-    if (tc && (st = bhd_launch_moe_slots_f16(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_x16, s)) != BHD_OK) return st;
-
-    MoeRun run;
-    run.hdr = hdr;
-    run.groups = groups;
-    run.glist = glist;
-    run.status = ctx->status_dev;
-    // gate and up: [ff x dim] per expert, both matrices in one launch
-    run.blob = ws + o_bx;
-    run.out0 = gbuf;
-    run.out1 = ubuf;
-    run.slot_weight = nullptr;
-    run.rows = uint32_t(ff);
-    run.chunks = chunks_x;
-    run.use_blob_a = 0;
-    st = launch_grouped_all(ctx, gate, up, run, glist, gmax, uint32_t((ff + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_x16 : nullptr,
-                            i8 ? ws + o_xq : nullptr);
-    if (st != BHD_OK) return st;
-    if (fp16_pack) {
-        k_moe_pack<<<dim3(chunks_a, group_bound), STEPS * 32, 0, s>>>(1, hdr, groups, slot_route, top_k, gbuf, ubuf, uint32_t(ff),
-                                                                      ws + o_ba, ctx->status_dev, skip_cls);
-        BHD_LAUNCHED(ctx, "gating and packing kernel");
-    }
-    if (i8 && (st = bhd_launch_moe_slots_i8(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
-    if (tc && (st = bhd_launch_moe_slots_f16(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_a16, s)) != BHD_OK) return st;
+    // gate and up: [ff x dim] per expert, both matrices in one launch per size class
+    if ((st = bhd_launch_moe_slots_i8(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, gate, up, hdr, groups, glist, gmax, R, E, ws + o_xq, gbuf, ubuf, nullptr, s)) != BHD_OK) return st;
     // down: [dim x ff] per expert, each output row scaled by its route weight
-    run.blob = ws + o_ba;
-    run.out0 = dbuf;
-    run.out1 = nullptr;
-    run.slot_weight = slot_weight;
-    run.rows = uint32_t(dim);
-    run.chunks = chunks_a;
-    run.use_blob_a = 1;
-    st = launch_grouped_all(ctx, down, nullptr, run, glist, gmax, uint32_t((dim + TILE_ROWS - 1) / TILE_ROWS), R, E, s, tc ? ws + o_a16 : nullptr,
-                            i8 ? ws + o_aq : nullptr);
-    if (st != BHD_OK) return st;
+    if ((st = bhd_launch_moe_slots_i8(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, down, nullptr, hdr, groups, glist, gmax, R, E, ws + o_aq, dbuf, nullptr, slot_weight, s)) != BHD_OK) return st;
     const uint64_t n = T * dim;
     k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, route_slot, y, n, uint32_t(dim), top_k, accumulate);
     BHD_LAUNCHED(ctx, "route combine kernel");
