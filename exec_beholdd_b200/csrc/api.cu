@@ -369,14 +369,24 @@ int32_t bhd_matvec_host(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const 
     if (batch == 0 || w->rows == 0) return BHD_OK;
     cudaSetDevice(ctx->device);
     const size_t xb = size_t(batch) * w->cols * sizeof(float), yb = size_t(batch) * w->rows * sizeof(float);
-    if ((st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb ? xb : 16, "activation staging")) != BHD_OK) return st;
-    if ((st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb, "output staging")) != BHD_OK) return st;
     cudaStream_t s = 0;
+    // A page-locked output buffer is addressable from the device (unified addressing): the
+    // kernel then writes y across PCIe itself, which saves one copy operation and its launch
+    // latency per call. x is always staged, because every cluster of CTAs reads all of it.
+    float* y_direct = nullptr;
+    if (!accumulate) {
+        cudaPointerAttributes ay;
+        if (cudaPointerGetAttributes(&ay, y_host) == cudaSuccess && ay.type == cudaMemoryTypeHost && ay.devicePointer)
+            y_direct = static_cast<float*>(ay.devicePointer);
+        cudaGetLastError();  // a pageable pointer is reported as an error by older drivers: not ours to keep
+    }
+    if ((st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb ? xb : 16, "activation staging")) != BHD_OK) return st;
+    if (!y_direct && (st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb, "output staging")) != BHD_OK) return st;
     if (xb) BHD_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, s), "copying activations in");
     if (accumulate) BHD_CUDA(ctx, cudaMemcpyAsync(ctx->stage_y, y_host, yb, cudaMemcpyHostToDevice, s), "copying outputs in");
-    st = bhd_matvec(ctx, w, slab, ctx->stage_x, ctx->stage_y, batch, scale, accumulate, s);
+    st = bhd_matvec(ctx, w, slab, ctx->stage_x, y_direct ? y_direct : ctx->stage_y, batch, scale, accumulate, s);
     if (st != BHD_OK) return st;
-    BHD_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s), "copying outputs back");
+    if (!y_direct) BHD_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s), "copying outputs back");
     BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the matvec");
     return BHD_OK;
 }

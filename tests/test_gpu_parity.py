@@ -193,6 +193,39 @@ def test_matvec_matches_oracle_on_seeded_inputs(dev, oracle, kind, rows, cols, b
     w.free()
 
 
+@pytest.mark.parametrize("kind,rows,cols,batch", [(12, 1536, 4096, 1), (8, 768, 2048, 3), (14, 512, 1024, 6)])
+def test_matvec_host_gives_the_same_result_for_pageable_and_page_locked_buffers(dev, oracle, kind, rows, cols, batch):
+    """bhd_matvec_host stages pageable buffers through device memory and lets the kernels
+    address page-locked ones directly; both must produce the bits of the device-resident call."""
+    import torch
+    from exec_beholdd_b200 import Weight, synth
+
+    packed = synth.matrix(kind, 31, rows, cols)
+    x = synth.activations(32, (batch, cols))
+    base = synth.activations(33, (batch, rows))
+    want = oracle.matvec_batch(packed, kind, rows, cols, x)
+    w = dev.upload_weight(Weight(packed, kind, rows, cols))
+    yd = torch.empty((batch, rows), device="cuda")
+    dev.matvec_resident(w, cuda(x), yd)
+    resident = yd.cpu().numpy()
+    assert max_rel_err(resident, want) <= TOL
+    # pageable numpy arrays
+    y_page = np.full((batch, rows), np.nan, dtype=np.float32)
+    dev.matvec_host_resident(w, x, y_page)
+    assert np.array_equal(bits(y_page), bits(resident))
+    # page-locked buffers
+    xp = torch.from_numpy(x.copy()).pin_memory()
+    yp = torch.full((batch, rows), float("nan")).pin_memory()
+    dev.matvec_host_resident(w, xp.numpy(), yp.numpy())
+    assert np.array_equal(bits(yp.numpy()), bits(resident))
+    # scaled accumulate into page-locked y
+    yp.copy_(torch.from_numpy(base))
+    dev.matvec_host_resident(w, xp.numpy(), yp.numpy(), scale=0.5, accumulate=True)
+    assert max_rel_err(yp.numpy(), base + want * np.float32(0.5)) <= TOL
+    dev.check_status()
+    w.free()
+
+
 @pytest.mark.parametrize("kind,rows,cols,batch,world", [(12, 1024, 4096, 1, 2), (8, 768, 2048, 4, 4), (14, 512, 1024, 2, 2)])
 def test_row_split_shards_reproduce_the_whole_projection(dev, oracle, kind, rows, cols, batch, world):
     """Every rank's shard (whole packed rows) gives that rank's slice of y; the slices laid
