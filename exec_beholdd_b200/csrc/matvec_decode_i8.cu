@@ -23,7 +23,6 @@
 namespace {
 
 constexpr int ROWS = 16, WARPS = 4, CHUNK_K = 256;
-constexpr int CLUSTER = 4;            // CTAs that share one packing of the activations
 constexpr int MAX_X_SMEM = 16 * 1024; // packed activations a CTA may hold
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
@@ -31,9 +30,13 @@ template <uint32_t KIND> struct Geo;
 // RING: stages per warp. Four stages of Q4_K hold all 4096 columns of a projection, so a CTA
 // that starts early (programmatic dependent launch) has requested all its weights before the
 // activations exist; the wider formats keep two stages to leave room for six CTAs per SM.
+// CLUSTER: CTAs that share one packing of the activations. Two measured fastest for Q4_K (8.6 us
+// against 9.0 with four and 9.2 with eight per 12288x4096 matvec); the wider formats keep four
+// and two vectors keep four so that the packed activations leave room for six CTAs per SM.
 template <> struct Geo<BHD_TYPE_Q8_0> { static constexpr int BOX = 272, GROUPS = 8, RING = 2; };
 template <> struct Geo<BHD_TYPE_Q4_K> { static constexpr int BOX = 144, GROUPS = 8, RING = 3; };
 template <> struct Geo<BHD_TYPE_Q6_K> { static constexpr int BOX = 240, GROUPS = 16, RING = 2; };
+__host__ __device__ constexpr int cluster_of(uint32_t kind, int nb) { return (kind == BHD_TYPE_Q4_K && nb == 1) ? 2 : 4; }
 __host__ __device__ constexpr int igroups(uint32_t kind) { return kind == BHD_TYPE_Q6_K ? 16 : 8; }
 
 // Packed activations of one chunk: [group][vector][digit][t] 8-byte B fragments (b0, b1), then
@@ -253,7 +256,7 @@ __device__ __forceinline__ int tile_row(int m) {
 // columns (2t, 2t+1) = (group gl = t / NB, vector v = t % NB) x (digit 0, digit 1).
 template <uint32_t KIND, int NB, int RING>
 __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_constant__ CUtensorMap tmap, const DecodeI8Params p) {
-    constexpr int BOX = Geo<KIND>::BOX, GROUPS = Geo<KIND>::GROUPS, GPT = 4 / NB, TILES = GROUPS / GPT;
+    constexpr int BOX = Geo<KIND>::BOX, GROUPS = Geo<KIND>::GROUPS, CLUSTER = cluster_of(KIND, NB), GPT = 4 / NB, TILES = GROUPS / GPT;
     constexpr int W_BYTES = ROWS * BOX, X_BYTES = iblob_bytes(KIND, NB), FRAG = iblob_frag_bytes(KIND, NB);
     constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     extern __shared__ uint8_t smem_raw[];
@@ -483,7 +486,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
 
 template <uint32_t KIND, int NB, int RING = Geo<KIND>::RING>
 int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cudaStream_t s) {
-    constexpr int W_BYTES = ROWS * Geo<KIND>::BOX;
+    constexpr int W_BYTES = ROWS * Geo<KIND>::BOX, CLUSTER = cluster_of(KIND, NB);
     constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     constexpr size_t RING_BYTES = size_t(WARPS) * RING * STAGE + 128;
     auto kern = k_matvec_decode_i8<KIND, NB, RING>;
@@ -533,7 +536,8 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     const bool tall = w->rows >= 8192 && w->cols <= 4096;
     if (nb == 1 && w->kind == BHD_TYPE_Q6_K && !tall) return BHD_OK;
     if (nb == 2 && !(w->kind == BHD_TYPE_Q4_K && tall)) return BHD_OK;
-    const uint32_t per_cta = (chunks + CLUSTER - 1) / CLUSTER;
+    const uint32_t cluster = uint32_t(cluster_of(w->kind, nb));
+    const uint32_t per_cta = (chunks + cluster - 1) / cluster;
     if (size_t(per_cta) * iblob_bytes(w->kind, nb) > size_t(MAX_X_SMEM)) return BHD_OK;  // very wide rows: other paths
     DecodeI8Params p;
     p.x = x;
