@@ -440,7 +440,7 @@ int32_t bhd_check_status(bhd_ctx* ctx, void* stream) {
                     (bits & BHD_DEV_BAD_EXPERT_ID) ? " expert id out of range;" : "",
                     (bits & BHD_DEV_WAIT_TIMEOUT) ? " a bounded wait gave up;" : "",
                     (bits & BHD_DEV_BAD_ROUTE_PROB) ? " router probabilities not finite, non-negative with a positive sum;" : "",
-                    (bits & BHD_DEV_ACTIVATION_RANGE) ? " an activation is NaN or beyond the fp16 range (|x| > 65504);" : "");
+                    (bits & BHD_DEV_ACTIVATION_RANGE) ? " an activation is NaN or infinite, or beyond the fp16 range (|x| > 65504) on a path with fp16 operands;" : "");
 }
 
 uint64_t bhd_launch_count(const bhd_ctx* ctx) { return valid_ctx(ctx) ? ctx->launches : 0; }

@@ -379,8 +379,9 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 }
                 {
                     const int j = 2 * pp + 1;
-                    const uint32_t a0 = (q0.x >> 4) & 0x0F0F0F0Fu, a1 = (q1.x >> 4) & 0x0F0F0F0Fu;
-                    const uint32_t a2 = (q0.y >> 4) & 0x0F0F0F0Fu, a3 = (q1.y >> 4) & 0x0F0F0F0Fu;
+                    // high nibbles stay where they are (16 * q, still a u8); the 1/16 is folded into the group's factor below
+                    const uint32_t a0 = q0.x & 0xF0F0F0F0u, a1 = q1.x & 0xF0F0F0F0u;
+                    const uint32_t a2 = q0.y & 0xF0F0F0F0u, a3 = q1.y & 0xF0F0F0F0u;
                     if (j % GPT == 0) imma<false, true>(acc[j / GPT], a0, a1, a2, a3, bfrag(j));
                     else imma<false, false>(acc[j / GPT], a0, a1, a2, a3, bfrag(j));
                 }
@@ -396,6 +397,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 f[3] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
             };
             uint32_t f0[4], f1[4];
+            const float nib = (gl & 1) ? 0.0625f : 1.0f;  // j = tl * GPT + gl is odd exactly when gl is (GPT is even)
             fields(h0, f0);
             fields(h1, f1);
 #pragma unroll
@@ -406,8 +408,9 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 const float sc0 = u2f((f0[2 * hi4] >> sh) & 0xffu), mn0 = u2f((f0[2 * hi4 + 1] >> sh) & 0xffu);
                 const float sc1 = u2f((f1[2 * hi4] >> sh) & 0xffu), mn1 = u2f((f1[2 * hi4 + 1] >> sh) & 0xffu);
                 const float2 m = mq[tl];
-                tot0 += fmaf(d0 * sc0 * m.x, float(acc[tl][0] * 256 + acc[tl][1]), -(m0 * mn0) * m.y);
-                tot1 += fmaf(d1 * sc1 * m.x, float(acc[tl][2] * 256 + acc[tl][3]), -(m1 * mn1) * m.y);
+                const float mx = m.x * nib;  // odd sub-blocks were fed as 16 * q
+                tot0 += fmaf(d0 * sc0 * mx, float(acc[tl][0] * 256 + acc[tl][1]), -(m0 * mn0) * m.y);
+                tot1 += fmaf(d1 * sc1 * mx, float(acc[tl][2] * 256 + acc[tl][3]), -(m1 * mn1) * m.y);
             }
         } else {  // Q6_K
             const uint32_t q6_off = (210u * chunk) & 15u;  // where the superblock starts in the staged window

@@ -226,6 +226,26 @@ def test_matvec_host_gives_the_same_result_for_pageable_and_page_locked_buffers(
     w.free()
 
 
+@pytest.mark.parametrize("kind,batch,bad", [(12, 1, np.nan), (8, 1, np.inf), (14, 1, -np.inf), (12, 3, np.nan), (8, 8, np.inf)])
+def test_non_finite_activation_is_reported_through_the_status_word(dev, kind, batch, bad):
+    """A NaN or infinite activation cannot be represented in the packed operand formats; the
+    kernels flag it (and feed zero) instead of producing silent garbage, and the next
+    check_status raises and clears the flag."""
+    import torch
+    from exec_beholdd_b200 import DeviceError, Weight, synth
+
+    rows, cols = 1536, 4096
+    w = dev.upload_weight(Weight(synth.matrix(kind, 41, rows, cols), kind, rows, cols))
+    x = synth.activations(42, (batch, cols))
+    x[batch - 1, 1234] = bad
+    y = torch.empty((batch, rows), device="cuda")
+    dev.matvec_resident(w, cuda(x), y)
+    with pytest.raises(DeviceError):
+        dev.check_status()
+    dev.check_status()  # the flag was cleared by the failed check
+    w.free()
+
+
 @pytest.mark.parametrize("kind,rows,cols,batch,world", [(12, 1024, 4096, 1, 2), (8, 768, 2048, 4, 4), (14, 512, 1024, 2, 2)])
 def test_row_split_shards_reproduce_the_whole_projection(dev, oracle, kind, rows, cols, batch, world):
     """Every rank's shard (whole packed rows) gives that rank's slice of y; the slices laid
