@@ -341,6 +341,13 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
         int acc[TILES][4];
 
         if constexpr (KIND == BHD_TYPE_Q8_0) {
+            // block scales first (the asm statements keep program order)
+            uint32_t dq0[TILES], dq1[TILES];
+#pragma unroll
+            for (int tl = 0; tl < TILES; ++tl) {
+                dq0[tl] = lds16(w0 + 34 * (tl * GPT + gl));
+                dq1[tl] = lds16(w1 + 34 * (tl * GPT + gl));
+            }
 #pragma unroll
             for (int blk = 0; blk < 8; ++blk) {
                 uint32_t a[4];
@@ -360,13 +367,15 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
             }
 #pragma unroll
             for (int tl = 0; tl < TILES; ++tl) {
-                const int blk = tl * GPT + gl;
                 const float2 m = mq[tl];
-                const float d0 = h2f(lds16(w0 + 34 * blk)) * m.x, d1 = h2f(lds16(w1 + 34 * blk)) * m.x;
+                const float d0 = h2f(dq0[tl]) * m.x, d1 = h2f(dq1[tl]) * m.x;
                 tot0 = fmaf(d0, float(acc[tl][0] * 256 + acc[tl][1]), tot0);
                 tot1 = fmaf(d1, float(acc[tl][2] * 256 + acc[tl][3]), tot1);
             }
         } else if constexpr (KIND == BHD_TYPE_Q4_K) {
+            // the superblock headers are requested first: the asm statements keep program order,
+            // so loads placed after the MMAs would be waited for on their own
+            const uint4 h0 = lds128(w0), h1 = lds128(w1);
 #pragma unroll
             for (int pp = 0; pp < 4; ++pp) {
                 const uint2 q0 = lds64(w0 + 16 + 32 * pp + 8 * t), q1 = lds64(w1 + 16 + 32 * pp + 8 * t);
@@ -386,7 +395,6 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                     else imma<false, false>(acc[j / GPT], a0, a1, a2, a3, bfrag(j));
                 }
             }
-            const uint4 h0 = lds128(w0), h1 = lds128(w1);
             const float d0 = h2f(h0.x & 0xffffu), m0 = h2f(h0.x >> 16), d1 = h2f(h1.x & 0xffffu), m1 = h2f(h1.x >> 16);
             // Packed 6-bit fields (crates/beholdd-kernel/src/kquant.rs:176-185), four per word:
             // scales 0-3, mins 0-3, scales 4-7, mins 4-7.
