@@ -159,15 +159,16 @@ __device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(0x4B00
 // x [nvec x K] f32; dst = this CTA's packed chunks [n_local][iblob_bytes].
 template <uint32_t KIND, int NB>
 __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_t nvec, uint32_t K, uint32_t chunk0,
-                                            uint32_t chunk_stride, uint32_t n_local, uint32_t chunks, uint8_t* dst,
-                                            uint32_t* status) {
+                                            uint32_t chunk_stride, uint32_t run, uint32_t n_local, uint32_t chunks,
+                                            uint8_t* dst, uint32_t* status) {
     constexpr int GROUPS = igroups(KIND), X_BYTES = iblob_bytes(KIND, NB), FRAG = iblob_frag_bytes(KIND, NB);
     constexpr int ITEMS = GROUPS * NB;  // per chunk
     static_assert(ITEMS % 8 == 0, "whole warps must run the same number of passes (full-mask shuffles below)");
     const int quad = threadIdx.x >> 2, t = threadIdx.x & 3, nquads = blockDim.x >> 2;
     const bool vec_ok = (K & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     for (uint32_t it = quad; it < n_local * ITEMS; it += nquads) {
-        const uint32_t lc = it / ITEMS, item = it % ITEMS, chunk = chunk0 + lc * chunk_stride;
+        // local chunk lc -> chunk: runs of `run` consecutive chunks, `chunk_stride` apart
+        const uint32_t lc = it / ITEMS, item = it % ITEMS, chunk = chunk0 + (lc / run) * chunk_stride + lc % run;
         const int grp = int(item) / NB, v = int(item) % NB;
         // columns (within the chunk) behind b0 and b1 of this lane
         int c0, c1;
@@ -254,18 +255,26 @@ __device__ __forceinline__ int tile_row(int m) {
 
 // NB vectors; GPT = 4 / NB scale groups share one accumulator tile; lane-in-quad t owns tile
 // columns (2t, 2t+1) = (group gl = t / NB, vector v = t % NB) x (digit 0, digit 1).
-template <uint32_t KIND, int NB, int RING>
+// KS = 1: a cluster is CLUSTER row tiles sharing one packing of x. KS = 4 (wide rows, few of
+// them): a cluster is one row tile cut four ways along the columns -- rank r takes chunks
+// c with (c / WARPS) % 4 == r, packs exactly those itself, and rank 0 adds the four partial
+// sums in rank order, so the result is as deterministic as without the split.
+template <uint32_t KIND, int NB, int RING, int KS>
 __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_constant__ CUtensorMap tmap, const DecodeI8Params p) {
-    constexpr int BOX = Geo<KIND>::BOX, GROUPS = Geo<KIND>::GROUPS, CLUSTER = cluster_of(KIND, NB), GPT = 4 / NB, TILES = GROUPS / GPT;
+    constexpr int BOX = Geo<KIND>::BOX, GROUPS = Geo<KIND>::GROUPS, CLUSTER = KS > 1 ? 1 : cluster_of(KIND, NB), GPT = 4 / NB, TILES = GROUPS / GPT;
+    constexpr uint32_t CSTEP = WARPS * KS;  // distance between consecutive chunks of one warp
     constexpr int W_BYTES = ROWS * BOX, X_BYTES = iblob_bytes(KIND, NB), FRAG = iblob_frag_bytes(KIND, NB);
     constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     __shared__ uint64_t bars[WARPS][RING];
     __shared__ float red[WARPS][ROWS][NB];
+    __shared__ float part[KS][ROWS * NB];  // rank 0's copy receives the partial sums of all ranks
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t tile = blockIdx.x;  // the grid is padded to whole clusters: tiles beyond the matrix only pack
+    const uint32_t rank = cluster_rank();
+    const uint32_t tile = blockIdx.x / KS;  // KS = 1: the grid is padded to whole clusters, tiles beyond the matrix only pack
+    const uint32_t first = uint32_t(warp) + (KS > 1 ? WARPS * rank : 0u);  // this warp's first chunk
     if (lane == 0) {
         for (int i = 0; i < RING; ++i) mbar_init(&bars[warp][i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -274,10 +283,10 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
 
     uint8_t* ring = smem + warp * (RING * STAGE);
     const uint32_t ring32 = smem_u32(ring);
-    const uint32_t my_chunks = (tile < p.tiles && p.chunks > uint32_t(warp)) ? (p.chunks - warp + WARPS - 1) / WARPS : 0;
+    const uint32_t my_chunks = (tile < p.tiles && p.chunks > first) ? (p.chunks - first + CSTEP - 1) / CSTEP : 0;
     // lane 0 only: stage the weights of the warp's i-th chunk.
     auto issue_w = [&](uint32_t i) {
-        const uint32_t chunk = warp + i * WARPS, slot = i % RING;
+        const uint32_t chunk = first + i * CSTEP, slot = i % RING;
         mbar_arrive_expect_tx(&bars[warp][slot], W_BYTES);
         const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : uint32_t(BOX) * chunk;
         tma_load_2d(ring + slot * STAGE, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
@@ -290,11 +299,16 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     pdl_launch_dependents();
     pdl_wait();
 
-    // Chunk c is packed by the CTA of cluster rank c % CLUSTER, as its local chunk c / CLUSTER.
     uint8_t* xs = smem + WARPS * RING * STAGE;
-    const uint32_t rank = cluster_rank();
-    pack_chunks<KIND, NB>(p.x, p.batch, p.cols, rank, CLUSTER, p.chunks_per_cta, p.chunks, xs, p.status);
-    cluster_sync();
+    if (KS == 1) {
+        // Chunk c is packed by the CTA of cluster rank c % CLUSTER, as its local chunk c / CLUSTER.
+        pack_chunks<KIND, NB>(p.x, p.batch, p.cols, rank, CLUSTER, 1, p.chunks_per_cta, p.chunks, xs, p.status);
+        cluster_sync();
+    } else {
+        // This CTA packs its own chunks: WARPS consecutive ones every CSTEP; local index = i * WARPS + warp.
+        pack_chunks<KIND, NB>(p.x, p.batch, p.cols, WARPS * rank, CSTEP, WARPS, p.chunks_per_cta, p.chunks, xs, p.status);
+        __syncthreads();
+    }
 
     const int r0 = tile_row<KIND>(g), r1 = tile_row<KIND>(g + 8);
     const int gl = t / NB, v = t % NB;                  // what this lane's accumulator columns mean
@@ -309,7 +323,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     float2 mq[TILES], mq_next[TILES];
     const uint32_t xs32 = smem_u32(xs);
     auto load_x = [&](uint32_t chunk, uint2 (&q)[TILES], float2 (&m)[TILES]) {
-        const uint32_t cb = map_to_rank(xs32 + (chunk / CLUSTER) * X_BYTES, chunk % CLUSTER);
+        const uint32_t cb = KS == 1 ? map_to_rank(xs32 + (chunk / CLUSTER) * X_BYTES, chunk % CLUSTER)
+                                    : map_to_rank(xs32 + ((chunk / CSTEP) * WARPS + chunk % WARPS) * X_BYTES, rank);
 #pragma unroll
         for (int tl = 0; tl < TILES; ++tl) {
             q[tl] = ld_cluster64(cb + (tl * GPT + bgl) * (64 * NB) + boff);
@@ -317,16 +332,16 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
             m[tl] = make_float2(__uint_as_float(mm.x), __uint_as_float(mm.y));
         }
     };
-    if (my_chunks > 0) load_x(warp, bq_next, mq_next);
+    if (my_chunks > 0) load_x(first, bq_next, mq_next);
 
     for (uint32_t i = 0; i < my_chunks; ++i) {
-        const uint32_t slot = i % RING, chunk = warp + i * WARPS;
+        const uint32_t slot = i % RING, chunk = first + i * CSTEP;
 #pragma unroll
         for (int tl = 0; tl < TILES; ++tl) {
             bq[tl] = bq_next[tl];
             mq[tl] = mq_next[tl];
         }
-        if (i + 1 < my_chunks) load_x(chunk + WARPS, bq_next, mq_next);
+        if (i + 1 < my_chunks) load_x(chunk + CSTEP, bq_next, mq_next);
         if (!mbar_wait(&bars[warp][slot], (i / RING) & 1)) {
             if (lane == 0) atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT);
             break;
@@ -480,11 +495,27 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
         red[warp][r1][t] = tot1;
     }
     __syncthreads();
+    float sum = 0.f;
+    const int r = threadIdx.x / NB, vv = threadIdx.x % NB;
     if (threadIdx.x < ROWS * NB) {
-        const int r = threadIdx.x / NB, vv = threadIdx.x % NB;
-        float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) sum += red[w][r][vv];
+    }
+    if (KS > 1) {
+        // every rank stores its partial sums into rank 0's `part`, then rank 0 adds them in rank order
+        if (threadIdx.x < ROWS * NB) {
+            const uint32_t dst = map_to_rank(smem_u32(&part[rank][threadIdx.x]), 0);
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(sum) : "memory");
+        }
+        cluster_sync();
+        if (rank != 0) return;
+        sum = 0.f;
+        if (threadIdx.x < ROWS * NB) {
+#pragma unroll
+            for (int k = 0; k < KS; ++k) sum += part[k][threadIdx.x];
+        }
+    }
+    if (threadIdx.x < ROWS * NB) {
         const uint32_t row = tile * ROWS + r;
         if (row < p.rows && uint32_t(vv) < p.batch) {
             const float val = __fmul_rn(sum, p.scale);
@@ -492,15 +523,15 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
             *o = p.accumulate ? __fadd_rn(*o, val) : val;
         }
     }
-    cluster_rendezvous();  // no CTA may leave while another still reads its packed activations
+    if (KS == 1) cluster_rendezvous();  // no CTA may leave while another still reads its packed activations
 }
 
-template <uint32_t KIND, int NB, int RING = Geo<KIND>::RING>
+template <uint32_t KIND, int NB, int KS, int RING = Geo<KIND>::RING>
 int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cudaStream_t s) {
-    constexpr int W_BYTES = ROWS * Geo<KIND>::BOX, CLUSTER = cluster_of(KIND, NB);
+    constexpr int W_BYTES = ROWS * Geo<KIND>::BOX, CLUSTER = KS > 1 ? KS : cluster_of(KIND, NB);
     constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     constexpr size_t RING_BYTES = size_t(WARPS) * RING * STAGE + 128;
-    auto kern = k_matvec_decode_i8<KIND, NB, RING>;
+    auto kern = k_matvec_decode_i8<KIND, NB, RING, KS>;
     static int cached_device = -1;
     if (cached_device != ctx->device) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RING_BYTES + MAX_X_SMEM)),
@@ -510,7 +541,7 @@ int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cu
     CUtensorMap map;
     memcpy(&map, w->tmap16, sizeof(map));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.tiles + CLUSTER - 1) / CLUSTER * CLUSTER);
+    cfg.gridDim = dim3(KS > 1 ? p.tiles * KS : (p.tiles + CLUSTER - 1) / CLUSTER * CLUSTER);
     cfg.blockDim = dim3(WARPS * 32);
     cfg.dynamicSmemBytes = RING_BYTES + size_t(p.chunks_per_cta) * iblob_bytes(KIND, NB);
     cfg.stream = s;
@@ -547,8 +578,14 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     const bool tall = w->rows >= 8192 && w->cols <= 4096;
     if (nb == 1 && w->kind == BHD_TYPE_Q6_K && !tall) return BHD_OK;
     if (nb == 2 && !(w->kind == BHD_TYPE_Q4_K && tall)) return BHD_OK;
+    // Few row tiles and long rows (a down projection, [4096 x 12288]): four CTAs per tile, each a
+    // quarter of the columns, so that the grid still fills the GPU.
+    // Measured: Q4_K 4096x12288 12.8 -> 11.7 us, 4096x4096 7.1 -> 6.2 us; Q8_0 gains only below
+    // about 160 row tiles (2048x8192 7.6 -> 5.8 us, but 4096x12288 13.4 -> 14.5 us).
+    const uint32_t ks_tiles = w->kind == BHD_TYPE_Q4_K ? 384u : (w->kind == BHD_TYPE_Q8_0 ? 160u : 0u);
+    const bool ksplit = nb == 1 && tiles <= ks_tiles && chunks >= 16;
     const uint32_t cluster = uint32_t(cluster_of(w->kind, nb));
-    const uint32_t per_cta = (chunks + cluster - 1) / cluster;
+    const uint32_t per_cta = ksplit ? WARPS * ((chunks + WARPS * 4 - 1) / (WARPS * 4)) : (chunks + cluster - 1) / cluster;
     if (size_t(per_cta) * iblob_bytes(w->kind, nb) > size_t(MAX_X_SMEM)) return BHD_OK;  // very wide rows: other paths
     DecodeI8Params p;
     p.x = x;
@@ -566,10 +603,12 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     int32_t st = BHD_OK;
 #define BHD_CASE(K)                                          \
     case K:                                                  \
-        if (nb == 1) st = launch_i8<K, 1>(ctx, w, p, s);     \
-        else st = launch_i8<K, 2>(ctx, w, p, s);             \
+        if (nb == 1) st = launch_i8<K, 1, 1>(ctx, w, p, s);  \
+        else st = launch_i8<K, 2, 1>(ctx, w, p, s);          \
         break;
-    switch (w->kind) {
+    if (ksplit && w->kind == BHD_TYPE_Q4_K) st = launch_i8<BHD_TYPE_Q4_K, 1, 4>(ctx, w, p, s);
+    else if (ksplit) st = launch_i8<BHD_TYPE_Q8_0, 1, 4>(ctx, w, p, s);
+    else switch (w->kind) {
         BHD_CASE(BHD_TYPE_Q8_0)
         BHD_CASE(BHD_TYPE_Q4_K)
         BHD_CASE(BHD_TYPE_Q6_K)

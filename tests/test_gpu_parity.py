@@ -155,6 +155,7 @@ MATVEC_CASES = [
     (8, 100, 32 * 7, 5), (12, 1536, 4096, 1), (12, 512, 12288, 2), (12, 1024, 4096, 4), (12, 768, 4096, 8),
     (12, 19, 256, 1), (12, 130, 768, 7), (14, 1536, 4096, 1), (14, 512, 12288, 2), (14, 1024, 4096, 8),
     (14, 21, 256, 3), (14, 70, 2304, 2), (13, 64, 512, 2), (0, 128, 2048, 4), (1, 33, 100, 2),
+    (8, 512, 8192, 1), (12, 100, 5120, 1), (12, 4096, 4096, 1),
 ]
 
 
