@@ -443,6 +443,49 @@ def test_moe_layer_matches_oracle(dev, oracle, n_experts, dim, ff, top_k, T):
         h.free()
 
 
+@pytest.mark.parametrize("T,top_k,pattern", [(100, 2, "two_hot"), (70, 1, "one_expert"), (33, 4, "round_robin"), (0, 2, "empty")])
+def test_moe_experts_with_skewed_and_empty_routing(dev, oracle, T, top_k, pattern):
+    """Routing given from outside: every position on the same experts (one expert gets more
+    than 32 routes and is cut into several groups), experts nobody selects, and no position
+    at all. Assignments are explicit, so only the expert arithmetic is under test."""
+    import torch
+    from exec_beholdd_b200 import DeviceError, Weight
+
+    n_experts, dim, ff = 8, 320, 96
+    _, gate, up, down, x = moe_inputs(777, n_experts, dim, ff, max(T, 1))
+    x = x[:T]
+    if pattern == "two_hot":
+        experts = np.tile(np.array([[5, 2]], dtype=np.int32), (T, 1))
+    elif pattern == "one_expert":
+        experts = np.full((T, 1), 3, dtype=np.int32)
+    elif pattern == "round_robin":
+        experts = (np.arange(T * top_k, dtype=np.int32).reshape(T, top_k) * 3) % n_experts
+    else:
+        experts = np.zeros((0, top_k), dtype=np.int32)
+    from exec_beholdd_b200 import synth
+    weights = np.abs(synth.activations(778, (max(T, 1), top_k)))[:T].astype(np.float32) + np.float32(0.25)
+    gw = dev.upload_weight(Weight(gate, 8, ff, dim), slabs=n_experts)
+    uw = dev.upload_weight(Weight(up, 8, ff, dim), slabs=n_experts)
+    dw = dev.upload_weight(Weight(down, 8, dim, ff), slabs=n_experts)
+    y = torch.full((T, dim), float("nan"), device="cuda")
+    dev.moe_experts(gw, uw, dw, cuda(x) if T else torch.empty((0, dim), device="cuda"),
+                    cuda(experts) if T else torch.empty((0, top_k), dtype=torch.int32, device="cuda"),
+                    cuda(weights) if T else torch.empty((0, top_k), device="cuda"), y)
+    dev.check_status()
+    if T:
+        want = oracle.moe_experts(gate, up, down, n_experts, dim, ff, x, experts, weights)
+        assert max_rel_err(y.cpu().numpy(), want) <= TOL
+        # a negative expert id is reported, not dereferenced (ids beyond the local range belong
+        # to other ranks of an expert-parallel group and are skipped)
+        bad = experts.copy()
+        bad[0, 0] = -2
+        dev.moe_experts(gw, uw, dw, cuda(x), cuda(bad), cuda(weights), y)
+        with pytest.raises(DeviceError):
+            dev.check_status()
+    for h in (gw, uw, dw):
+        h.free()
+
+
 def test_expert_parallel_partition_sums_to_the_whole(dev, oracle):
     """Each rank of an expert-parallel group applies only its experts; the partial outputs
     add up to the full layer."""
