@@ -1,7 +1,7 @@
 // Grouped routed-expert matmul for packed Q8_0 experts on sm_100a, integer tensor-core variant.
 //
-// One CTA = one group (up to 32 routes of one expert, sorted by the plan kernel) x one 64-row
-// tile of the expert matrix, streaming all columns once. With at most 32 routes per expert the
+// One CTA = one group (up to 32 routes of one expert, sorted by the plan kernel) x one 64- or
+// 128-row tile of the expert matrix, streaming all columns once. With at most 32 routes per expert the
 // layer is bound by weight traffic, so the goal is the decode kernel's: as few issue slots per
 // weight byte as possible.
 //   * Q8_0 quants go to mma.sync m16n8k32 (s8 x s8 -> s32) exactly as they lie in memory; no
@@ -12,9 +12,9 @@
 //     (2t, 2t+1) combines them without any exchange: v = 256 * c0 + c1, exact in s32.
 //   * Per block the lane adds d_block(row) * v into a per-chunk f32 sum; per chunk it folds in
 //     the route's 2^(e-14). Relative error 2^-15 of the largest activation of the chunk.
-//   * Four consumer warps (16 rows each) share the staged activations; one producer warp keeps
-//     a 2-3 stage ring full: one tiled TMA copy for the 64 x 272-byte weight box, one bulk copy
-//     for the group's packed activations (contiguous, because slots are sorted by expert).
+//   * Four or eight consumer warps (16 rows each) share the staged activations; one producer
+//     warp keeps a 2-3 stage ring full: one tiled TMA copy per 64 x 272-byte weight box, one bulk
+//     copy for the group's packed activations (contiguous, because slots are sorted by expert).
 // Every wait is bounded and reports through the status word.
 //
 // Reference semantics: crates/beholdd-model/src/qwen3moe/forward.rs:1363-1400 (gate/up matvec,
