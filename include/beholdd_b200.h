@@ -99,7 +99,9 @@ int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const 
                    uint32_t batch, float scale, int32_t accumulate, void* stream);
 
 /* The same operation through host buffers, the shape of the immediate Device trait whose
- * slices live in host memory: copies x in, runs, copies y back, synchronises. */
+ * slices live in host memory: copies x in, runs, copies y back, synchronises. When y_host is
+ * page-locked and accumulate == 0 the kernel writes y into it directly (unified addressing)
+ * and the copy back is skipped; x is always staged through device memory. */
 int32_t bhd_matvec_host(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_host, float* y_host,
                         uint32_t batch, float scale, int32_t accumulate);
 
