@@ -136,9 +136,17 @@ __device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(0x4B00
 
 // ---- activation packer ----------------------------------------------------------------------
 // One CTA per chunk. x [nb x K] f32 -> fragments [step][v][hi|lo][t] and per-(group, v) sums.
+// Programmatic dependent launch (no-ops when the kernel was launched without the attribute).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __global__ void k_pack_x_decode(uint32_t kind, const float* __restrict__ x, uint32_t nvec, uint32_t nb, uint32_t K,
                                 uint8_t* __restrict__ blob, uint32_t* __restrict__ status) {
     __shared__ float stepsum[STEPS][4];
+    // let the matvec kernel start its weight prefetch; wait for whatever produced x and for the
+    // previous matvec, which may still be reading the blob
+    pdl_launch_dependents();
+    pdl_wait();
     const int chunk = blockIdx.x;
     const int s = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = lane & 3, v = lane >> 2;  // lanes 4v..4v+3 handle vector v (v < nb <= 4); other lanes idle
@@ -196,6 +204,7 @@ struct DecodeParams {
     uint32_t rows, row_base, chunks, batch;
     float scale;
     int accumulate;
+    int pdl;  // launch with programmatic stream serialization (host-side switch only)
 };
 
 template <uint32_t KIND>
@@ -231,16 +240,25 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
     const uint32_t ring32 = smem_u32(ring);
     const uint32_t zeros32 = smem_u32(zero_area);
     const uint32_t my_chunks = p.chunks > uint32_t(warp) ? (p.chunks - warp + WARPS - 1) / WARPS : 0;
-    auto issue = [&](uint32_t i) {  // lane 0 only: stage the warp's i-th chunk
+    // lane 0 only: stage the warp's i-th chunk; weights and packed activations are separate
+    // copies on the same barrier, so that the first weights can be requested before the
+    // activation packer has finished (weights are never written by a preceding kernel).
+    auto issue_w = [&](uint32_t i) {
         const uint32_t chunk = warp + i * WARPS, slot = i % RING;
-        uint8_t* dst = ring + slot * STAGE;
         mbar_arrive_expect_tx(&bars[warp][slot], W_BYTES + X_BYTES);
         const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : uint32_t(BOX) * chunk;
-        tma_load_2d(dst, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
-        bulk_load_1d(dst + W_BYTES, p.blob + uint64_t(chunk) * X_BYTES, X_BYTES, &bars[warp][slot]);
+        tma_load_2d(ring + slot * STAGE, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
+    };
+    auto issue_x = [&](uint32_t i) {
+        const uint32_t chunk = warp + i * WARPS, slot = i % RING;
+        bulk_load_1d(ring + slot * STAGE + W_BYTES, p.blob + uint64_t(chunk) * X_BYTES, X_BYTES, &bars[warp][slot]);
     };
     if (lane == 0)
-        for (uint32_t i = 0; i < my_chunks && i < RING; ++i) issue(i);
+        for (uint32_t i = 0; i < my_chunks && i < RING; ++i) issue_w(i);
+    pdl_launch_dependents();
+    pdl_wait();  // the packer (and before it whatever produced x and y) has finished
+    if (lane == 0)
+        for (uint32_t i = 0; i < my_chunks && i < RING; ++i) issue_x(i);
 
     const int r0 = tile_row<KIND>(g), r1 = tile_row<KIND>(g + 8);
     const int gl = t / NB, v = t % NB;            // what this lane's accumulator columns mean
@@ -395,7 +413,10 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode(const __grid_const
             }
         }
         __syncwarp();
-        if (lane == 0 && i + RING < my_chunks) issue(i + RING);
+        if (lane == 0 && i + RING < my_chunks) {
+            issue_w(i + RING);
+            issue_x(i + RING);
+        }
     }
 
     // Sum over the groups handled by different lanes of the quad (same vector v), then over warps.
@@ -449,6 +470,21 @@ int32_t launch_decode(bhd_ctx* ctx, const bhd_weight* w, const DecodeParams& p, 
     }
     CUtensorMap map;
     memcpy(&map, w->tmap16, sizeof(map));
+    if (p.pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(tiles);
+        cfg.blockDim = dim3(WARPS * 32);
+        cfg.dynamicSmemBytes = DYN;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, map, p), "launching the decode matvec kernel");
+        ctx->launches += 1;
+        return BHD_OK;
+    }
     kern<<<tiles, WARPS * 32, DYN, s>>>(map, p);
     BHD_LAUNCHED(ctx, "decode matvec kernel");
     return BHD_OK;
@@ -491,9 +527,22 @@ int32_t bhd_launch_matvec_decode(bhd_ctx* ctx, const bhd_weight* w, uint64_t sla
     int32_t st = bhd_ensure_workspace(ctx, blob_bytes, s);
     if (st != BHD_OK) return st;
     uint8_t* blob = ctx->workspace;
-    k_pack_x_decode<<<chunks, STEPS * 32, 0, s>>>(w->kind, x, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev);
-    BHD_LAUNCHED(ctx, "activation packing kernel");
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(chunks);
+        cfg.blockDim = dim3(STEPS * 32);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_pack_x_decode, w->kind, x, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev),
+                 "launching the activation packing kernel");
+        ctx->launches += 1;
+    }
     DecodeParams p;
+    p.pdl = 1;
     p.blob = blob;
     p.y = y;
     p.status = ctx->status_dev;
@@ -586,6 +635,7 @@ extern "C" __attribute__((visibility("default"))) int32_t bhd_matvec_noalloc(bhd
     k_pack_x_decode<<<chunks, STEPS * 32, 0, s>>>(w->kind, x_dev, batch, uint32_t(nb), uint32_t(w->cols), blob, ctx->status_dev);
     BHD_LAUNCHED(ctx, "activation packing kernel");
     DecodeParams p;
+    p.pdl = 0;
     p.blob = blob;
     p.y = y_dev;
     p.status = ctx->status_dev;
