@@ -164,10 +164,18 @@ __device__ __forceinline__ void pack_tile(uint32_t kind, const float* row, const
     }
 }
 
+// Programmatic dependent launch (no-ops when the kernel was launched without the attribute).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // x [batch x K] f32 -> one blob per chunk, split mode. grid (chunks, nt), 512 threads.
 __global__ void k_pack_x(uint32_t kind, const float* __restrict__ x, uint64_t ldx, uint32_t batch, uint32_t K, int nt,
                          uint8_t* __restrict__ blob, uint32_t* __restrict__ status) {
     __shared__ float stepsum[STEPS][8];
+    // let the matvec kernel start its weight prefetch; wait for whatever produced x and for the
+    // previous matvec, which may still be reading the blob
+    pdl_launch_dependents();
+    pdl_wait();
     const int j = blockIdx.y, g = (threadIdx.x & 31) >> 2;
     const uint32_t b = 4 * j + (g >> 1);
     pack_tile(kind, b < batch ? x + uint64_t(b) * ldx : nullptr, nullptr, g & 1, blockIdx.x, K, nt, j,
@@ -386,27 +394,41 @@ __device__ __forceinline__ void run_stage_range(const CUtensorMap* tmap_ptr, con
     }
     __syncthreads();
 
+    pdl_launch_dependents();
     if (warp == CONSUMER_WARPS) {
-        // ---- producer: one lane issues the copies of every stage ---------------------------
+        // ---- producer: one lane issues the copies of every stage. The weights of the first
+        // ring of stages are requested before waiting for the grids this launch depends on
+        // (weights are never written by a preceding kernel); the packed activations after. ----
         if (lane == 0) {
-            for (uint32_t s = s_begin; s < s_end; ++s) {
+            auto copy_w = [&](uint32_t s, uint32_t slot) {
+                const uint32_t tile = s / p.chunks, chunk = s - tile * p.chunks;
+                mbar_arrive_expect_tx(&full_bar[slot], S::W_BYTES + S::X_BYTES);
+                // Inner coordinate in 2-byte elements; its byte offset is a multiple of 16.
+                const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : Fmt<KIND>::CHUNK_BYTES * chunk;
+                tma_load_2d(smem + slot * S::STAGE, tmap_ptr, int(byte0 >> 1), int(p.row_base + tile * TILE_ROWS), &full_bar[slot]);
+            };
+            auto copy_x = [&](uint32_t s, uint32_t slot) {
+                const uint32_t chunk = s % p.chunks;
+                bulk_load_1d(smem + slot * S::STAGE + S::X_OFF, p.xblob + uint64_t(chunk) * S::X_BYTES, S::X_BYTES, &full_bar[slot]);
+            };
+            const uint32_t head = min(uint32_t(n_stages_ring), s_end - s_begin);
+            for (uint32_t it = 0; it < head; ++it) copy_w(s_begin + it, it);
+            pdl_wait();
+            for (uint32_t it = 0; it < head; ++it) copy_x(s_begin + it, it);
+            for (uint32_t s = s_begin + head; s < s_end; ++s) {
                 const uint32_t it = s - s_begin, slot = it % n_stages_ring;
                 if (!mbar_wait(&empty_bar[slot], ((it / n_stages_ring) & 1) ^ 1) || *(volatile int*)&abort_flag) {
                     atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT);
                     abort_flag = 1;
                     break;
                 }
-                const uint32_t tile = s / p.chunks, chunk = s - tile * p.chunks;
-                uint8_t* dst = smem + slot * S::STAGE;
-                mbar_arrive_expect_tx(&full_bar[slot], S::W_BYTES + S::X_BYTES);
-                // Inner coordinate in 2-byte elements; its byte offset is a multiple of 16.
-                const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : Fmt<KIND>::CHUNK_BYTES * chunk;
-                tma_load_2d(dst, tmap_ptr, int(byte0 >> 1), int(p.row_base + tile * TILE_ROWS), &full_bar[slot]);
-                bulk_load_1d(dst + S::X_OFF, p.xblob + uint64_t(chunk) * S::X_BYTES, S::X_BYTES, &full_bar[slot]);
+                copy_w(s, slot);
+                copy_x(s, slot);
             }
         }
         return;
     }
+    pdl_wait();  // consumers touch y, the partial sums and the tile counters
 
     // ---- consumers: warp w owns rows [16w, 16w+16) of every tile --------------------------------
     const int g = lane >> 2, t = lane & 3;
@@ -696,8 +718,18 @@ int32_t launch_one(bhd_ctx* ctx, const bhd_weight* w, const MatvecParams& base, 
     const uint32_t ctas = (p.total_stages + p.per_cta - 1) / p.per_cta;
     CUtensorMap map;
     memcpy(&map, w->tmap, sizeof(map));
-    kern<<<ctas, THREADS, size_t(ring) * S::STAGE + 128, s>>>(map, p, ring);
-    BHD_LAUNCHED(ctx, "tensor-core matvec kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = size_t(ring) * S::STAGE + 128;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, map, p, ring), "launching the tensor-core matvec kernel");
+    ctx->launches += 1;
     return BHD_OK;
 }
 
@@ -752,9 +784,21 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
         if (st != BHD_OK) return st;
         uint8_t* blob = ctx->workspace;
 
-        k_pack_x<<<dim3(chunks, nt), STEPS * 32, 0, s>>>(w->kind, x + b0 * w->cols, w->cols, nb, uint32_t(w->cols), nt, blob,
-                                                         ctx->status_dev);
-        BHD_LAUNCHED(ctx, "activation packing kernel");
+        {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(chunks, nt);
+            cfg.blockDim = dim3(STEPS * 32);
+            cfg.stream = s;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_pack_x, w->kind, x + b0 * w->cols, uint64_t(w->cols), uint32_t(nb), uint32_t(w->cols),
+                                             int(nt), blob, ctx->status_dev),
+                     "launching the activation packing kernel");
+            ctx->launches += 1;
+        }
 
         MatvecParams p;
         p.xblob = blob;
