@@ -37,7 +37,8 @@ constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
 // warp 0 TMA, warp 1 MMA + TMEM, then NG groups of four converter warps (one thread per weight row) that take
 // alternating slices; the first group is also the epilogue.
-__host__ __device__ constexpr int gemm_threads(int ng) { return 64 + 128 * ng; }
+// after the converters: one warp that requests the activation tiles and the second MMA issuer
+__host__ __device__ constexpr int gemm_threads(int ng) { return 64 + 128 * ng + 64; }
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -140,7 +141,7 @@ __global__ void k_f32_to_f16(const float* __restrict__ x, __half* __restrict__ o
     *reinterpret_cast<__half2*>(out + i + 2) = b;
 }
 
-constexpr int PLAIN_NG = 1;  // converter groups (a second one measured no faster)
+constexpr int PLAIN_NG = 2;  // converter groups: one cannot feed two MMA issuers
 
 struct GemmParams {
     float* y;            // [M x N]
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     const uint32_t stage_bytes = a_bytes + bn * 128u;
     const uint32_t pack_addr = smem0, stage_addr = smem0 + 2 * PACK_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int XW = 2 + 4 * NG, MW = 3 + 4 * NG;  // activation-tile producer warp, second MMA issuer warp
     const uint32_t m0 = blockIdx.y * p.tn, m_end = p.m, row_base = p.row_base;
     const CUtensorMap* tmap_w = &tmap_w0;
     float* const yout = p.y;
@@ -178,11 +180,11 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 4 * NG); }
         for (uint32_t i = 0; i < S; ++i) { mbar_init(&a_full[i], 4); mbar_init(&b_full[i], 1); mbar_init(&st_empty[i], 1); }
-        mbar_init(&tmem_full, 1);
+        mbar_init(&tmem_full, 2);  // both MMA issuers
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(&tmem_base_slot, bn);  // a power of two >= 32
+    if (warp == 1) tmem_alloc(&tmem_base_slot, 2 * bn);  // two accumulators; a power of two >= 32
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -191,39 +193,46 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     auto aborted = [&]() { return *(volatile int*)&abort_flag != 0; };
 
     if (warp == 0) {
-        // ---- TMA producer ------------------------------------------------------------------------
+        // ---- TMA producers: two independent request streams in two warps. This one keeps the two packed
+        // weight chunks in flight (a chunk is requested as soon as its buffer is released); warp XW fetches the
+        // activation tile of each slice as its stage frees up. ----
         if (lane == 0) {
             for (uint32_t c = 0; c < chunks && !aborted(); ++c) {
                 const uint32_t pb = c & 1;
                 if (!mbar_wait(&pk_empty[pb], ((c >> 1) & 1) ^ 1)) { give_up(); break; }
                 mbar_arrive_expect_tx(&pk_full[pb], PACK_BYTES);
                 tma_load_2d(pack_addr + pb * PACK_BYTES, tmap_w, int(c * (PACK_ROW / 2)), int(row_base + n0), &pk_full[pb]);
-                for (uint32_t kb = 0; kb < 4; ++kb) {
-                    const uint32_t it = c * 4 + kb;
-                    if (it >= slices) break;
-                    const uint32_t s = it % S;
-                    if (!mbar_wait(&st_empty[s], ((it / S) & 1) ^ 1)) { give_up(); break; }
-                    mbar_arrive_expect_tx(&b_full[s], bn * 128u);
-                    tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
-                }
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA issuer --------------------------------------------------------------------------
+    } else if (warp == XW) {
+        if (lane == 0) {
+            for (uint32_t it = 0; it < slices && !aborted(); ++it) {
+                const uint32_t s = it % S;
+                if (!mbar_wait(&st_empty[s], ((it / S) & 1) ^ 1)) { give_up(); break; }
+                mbar_arrive_expect_tx(&b_full[s], bn * 128u);
+                tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
+            }
+        }
+    } else if (warp == 1 || warp == MW) {
+        // ---- MMA issuers. One thread needs about 0.6 us per slice just to get through its two barrier
+        // waits, four tcgen05.mma and the commit, whatever the tile width; so two threads take alternate
+        // slices, each accumulating into its own TMEM columns (no ordering is needed between them), and
+        // the epilogue adds the two accumulators. ----
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(TILE_N, bn);
+            const uint32_t first = warp == 1 ? 0u : 1u, acc = tmem_base + first * bn;
             bool ok = true;
-            for (uint32_t it = 0; it < slices && ok; ++it) {
+            for (uint32_t it = first; it < slices && ok; it += 2) {
                 const uint32_t s = it % S, par = (it / S) & 1;
                 if (aborted() || !mbar_wait(&b_full[s], par) || !mbar_wait(&a_full[s], par)) { give_up(); ok = false; break; }
                 tc_fence_after();
                 const uint64_t da = umma_desc(stage_addr + s * stage_bytes), db = umma_desc(stage_addr + s * stage_bytes + a_bytes);
 #pragma unroll
                 for (uint32_t k16 = 0; k16 < 4; ++k16)  // 32 bytes (16 fp16) further along the swizzled row per step
-                    tc_mma_f16(tmem_base, da + 2 * k16, db + 2 * k16, idesc, (it | k16) ? 1u : 0u);
+                    tc_mma_f16(acc, da + 2 * k16, db + 2 * k16, idesc, (it != first || k16) ? 1u : 0u);
                 tc_commit(&st_empty[s]);  // arrives when these MMAs have finished reading the stage
             }
-            tc_commit(&tmem_full);        // arrives when every MMA issued so far is complete
+            tc_commit(&tmem_full);        // arrives when every MMA this thread issued is complete
         }
     } else {
         // ---- converters: NG groups of four warps take alternating 64-column slices; thread = one weight row ----
@@ -291,6 +300,12 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                 if (m0 + col >= m_end) break;            // uniform across the warp
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((q * 32u) << 16) + col, r);
+                if (slices > 1) {  // the odd slices' accumulator
+                    uint32_t r2[32];
+                    tc_ld32(tmem_base + ((q * 32u) << 16) + bn + col, r2);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
                 if (n < p.n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -307,7 +322,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, bn);
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * bn);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
