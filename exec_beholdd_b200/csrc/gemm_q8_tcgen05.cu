@@ -13,9 +13,12 @@
 //     rounding (q and d are exact in fp16).
 //   * Activations are converted to fp16 once per call; TMA loads [TN x 64] slices with the
 //     128B swizzle straight into the B tiles.
-//   * One elected thread issues tcgen05.mma (kind::f16, M = 128, N = TN, K = 16) four times per
-//     64-column slice and commits to the stage's mbarrier; the converter warps then become the
-//     epilogue: tcgen05.ld the accumulator and store Y coalesced along n.
+//   * Two elected threads (in different warps) issue tcgen05.mma (kind::f16, M = 128, N = TN,
+//     K = 16) four times per 64-column slice, on alternate slices and into separate TMEM
+//     accumulators, and commit to the stage's mbarrier; one thread alone needs about 0.6 us per
+//     slice for its waits, issues and commit, which bounded the kernel at every tile width. The
+//     first converter group then becomes the epilogue: tcgen05.ld both accumulators, add, and
+//     store Y coalesced along n.
 // Rings: 2 packed chunks, 3-4 fp16 stages. Every wait is bounded; a wait that gives up sets
 // the status word, the roles drain and the CTA frees its TMEM before it returns.
 //
@@ -35,8 +38,8 @@ constexpr int SLICE_K = 64;            // columns per fp16 stage (one 128-byte s
 constexpr int PACK_ROW = 272;          // packed bytes per row per chunk
 constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
-// warp 0 TMA, warp 1 MMA + TMEM, then NG groups of four converter warps (one thread per weight row) that take
-// alternating slices; the first group is also the epilogue.
+// warp 0 weight-chunk TMA, warp 1 MMA (even slices) + TMEM, then NG groups of four converter warps (one thread
+// per weight row) that take alternating slices; the first group is also the epilogue.
 // after the converters: one warp that requests the activation tiles and the second MMA issuer
 __host__ __device__ constexpr int gemm_threads(int ng) { return 64 + 128 * ng + 64; }
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
