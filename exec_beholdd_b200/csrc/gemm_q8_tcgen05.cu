@@ -162,7 +162,11 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                                                                 const __grid_constant__ CUtensorMap tmap_x,
                                                                 const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[8], b_full[8], st_empty[8], tmem_full;
+    // st_empty[s][k & 1]: the MMAs of the k-th use of stage s have finished reading it. Two barriers per
+    // stage, alternating by use, because a converter group sees only every other use of a stage and the two
+    // MMA issuers are not ordered with each other: on a single barrier a parity wait could be a whole phase
+    // early. On its own barrier every waiter sees every phase.
+    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[8], b_full[8], st_empty[8][2], tmem_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -182,7 +186,12 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 4 * NG); }
-        for (uint32_t i = 0; i < S; ++i) { mbar_init(&a_full[i], 4); mbar_init(&b_full[i], 1); mbar_init(&st_empty[i], 1); }
+        for (uint32_t i = 0; i < S; ++i) {
+            mbar_init(&a_full[i], 4);
+            mbar_init(&b_full[i], 1);
+            mbar_init(&st_empty[i][0], 1);
+            mbar_init(&st_empty[i][1], 1);
+        }
         mbar_init(&tmem_full, 2);  // both MMA issuers
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -194,6 +203,13 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     const uint32_t tmem_base = tmem_base_slot;
     auto give_up = [&]() { atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT); *(volatile int*)&abort_flag = 1; };
     auto aborted = [&]() { return *(volatile int*)&abort_flag != 0; };
+    // wait until the previous user of slice it's stage is done with it (true at once for the first use)
+    auto stage_free = [&](uint32_t it) {
+        const uint32_t use = it / S;
+        if (use == 0) return true;
+        const uint32_t k = use - 1;
+        return mbar_wait(&st_empty[it % S][k & 1], (k >> 1) & 1);
+    };
 
     if (warp == 0) {
         // ---- TMA producers: two independent request streams in two warps. This one keeps the two packed
@@ -211,7 +227,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
         if (lane == 0) {
             for (uint32_t it = 0; it < slices && !aborted(); ++it) {
                 const uint32_t s = it % S;
-                if (!mbar_wait(&st_empty[s], ((it / S) & 1) ^ 1)) { give_up(); break; }
+                if (!stage_free(it)) { give_up(); break; }
                 mbar_arrive_expect_tx(&b_full[s], bn * 128u);
                 tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
             }
@@ -233,7 +249,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
 #pragma unroll
                 for (uint32_t k16 = 0; k16 < 4; ++k16)  // 32 bytes (16 fp16) further along the swizzled row per step
                     tc_mma_f16(acc, da + 2 * k16, db + 2 * k16, idesc, (it != first || k16) ? 1u : 0u);
-                tc_commit(&st_empty[s]);  // arrives when these MMAs have finished reading the stage
+                tc_commit(&st_empty[s][(it / S) & 1]);  // arrives when these MMAs have finished reading the stage
             }
             tc_commit(&tmem_full);        // arrives when every MMA this thread issued is complete
         }
@@ -251,7 +267,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                 const uint32_t it = c * 4 + kb;
                 if (it >= slices) break;
                 const uint32_t s = it % S;
-                if (!mbar_wait(&st_empty[s], ((it / S) & 1) ^ 1)) { give_up(); ok = false; break; }
+                if (!stage_free(it)) { give_up(); ok = false; break; }
                 // Two Q8_0 blocks = 68 bytes = 17 aligned words: [d0 | q0..q31 | d1 | q32..q63].
                 uint32_t w[17];
 #pragma unroll
