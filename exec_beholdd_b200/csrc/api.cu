@@ -22,6 +22,7 @@ int32_t bhd_launch_matvec_decode(bhd_ctx* ctx, const bhd_weight* w, uint64_t sla
                                  uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
 int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                     uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled);
+int32_t bhd_launch_stage_copy(bhd_ctx* ctx, const float* src_mapped, float* dst_dev, size_t n16, cudaStream_t s);
 
 int32_t bhd_fail(bhd_ctx* ctx, int32_t status, const char* fmt, ...) {
     if (ctx) {
@@ -124,16 +125,16 @@ int32_t bhd_ctx_create(int32_t device, bhd_ctx** out_ctx) {
     if (!out_ctx) return BHD_ERR_INVALID_ARGUMENT;
     *out_ctx = nullptr;
     int count = 0;
-    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count || device >= BHD_MAX_DEVICES) {
         cudaGetLastError();
         return BHD_ERR_BACKEND;
     }
-    if (cudaSetDevice(device) != cudaSuccess) return BHD_ERR_BACKEND;
     bhd_ctx* c = new (std::nothrow) bhd_ctx();
     if (!c) return BHD_ERR_ALLOCATION;
     memset(c, 0, sizeof(*c));
     c->magic = BHD_CTX_MAGIC;
     c->device = device;
+    bhd_device_guard guard(c);  // the caller's current device is put back when this call returns
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return BHD_ERR_BACKEND; }
     c->sm_count = prop.multiProcessorCount;
@@ -146,7 +147,8 @@ int32_t bhd_ctx_create(int32_t device, bhd_ctx** out_ctx) {
         cudaMemset(c->status_dev, 0, 256) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void**>(&c->status_host), 256) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&c->counters), 65536 * sizeof(uint32_t)) != cudaSuccess ||
-        cudaMemset(c->counters, 0, 65536 * sizeof(uint32_t)) != cudaSuccess) {
+        cudaMemset(c->counters, 0, 65536 * sizeof(uint32_t)) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess) {
         cudaGetLastError();
         delete c;
         return BHD_ERR_ALLOCATION;
@@ -164,8 +166,10 @@ int32_t bhd_ctx_create(int32_t device, bhd_ctx** out_ctx) {
 
 int32_t bhd_ctx_destroy(bhd_ctx* ctx) {
     if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
-    cudaSetDevice(ctx->device);
+    {
+    bhd_device_guard guard(ctx);
     cudaDeviceSynchronize();
+    if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -173,6 +177,7 @@ int32_t bhd_ctx_destroy(bhd_ctx* ctx) {
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    }
     ctx->magic = 0;
     delete ctx;
     return BHD_OK;
@@ -219,6 +224,7 @@ static int32_t make_weight(bhd_ctx* ctx, const void* src, bool src_is_device, ui
     const int32_t st = validate_storage(ctx, n_bytes, kind, rows, cols, slabs, &row_bytes);
     if (st != BHD_OK) return st;
     if (n_bytes > 0 && !src) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "weight upload: null bytes");
+    bhd_device_guard guard(ctx);
     bhd_weight* w = new (std::nothrow) bhd_weight();
     if (!w) return bhd_fail(ctx, BHD_ERR_ALLOCATION, "%s could not allocate host memory for a weight handle", bhd_device_name());
     memset(w, 0, sizeof(*w));
@@ -238,7 +244,6 @@ static int32_t make_weight(bhd_ctx* ctx, const void* src, bool src_is_device, ui
         w->dev = const_cast<uint8_t*>(static_cast<const uint8_t*>(src));
         w->owned = false;
     } else {
-        cudaSetDevice(ctx->device);
         void* p = nullptr;
         const cudaError_t e = cudaMalloc(&p, n_bytes ? n_bytes : 16);
         if (e != cudaSuccess) {
@@ -277,7 +282,7 @@ int32_t bhd_weight_wrap_device(bhd_ctx* ctx, const void* bytes_dev, uint64_t n_b
 int32_t bhd_weight_free(bhd_weight* w) {
     if (!w || w->magic != BHD_WEIGHT_MAGIC) return BHD_ERR_INVALID_ARGUMENT;
     if (w->owned && w->dev) {
-        cudaSetDevice(w->ctx->device);
+        bhd_device_guard guard(w->ctx);
         cudaDeviceSynchronize();
         cudaFree(w->dev);
     }
@@ -296,6 +301,7 @@ int32_t bhd_dequantize(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, float* 
                         (unsigned long long)(w->rows * w->cols), (unsigned long long)out_len);
     if (out_len == 0) return BHD_OK;
     if (!out_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "dequantize: null output");
+    bhd_device_guard guard(ctx);
     return bhd_launch_dequantize(ctx, w, slab, out_dev, cudaStream_t(stream));
 }
 
@@ -317,6 +323,7 @@ int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float
     const int32_t st = check_matvec_args(ctx, w, slab, x_dev, y_dev, batch, scale, "matvec");
     if (st != BHD_OK) return st;
     if (batch == 0 || w->rows == 0) return BHD_OK;
+    bhd_device_guard guard(ctx);
     cudaStream_t s = cudaStream_t(stream);
     bool handled = false;
     if (batch <= 2) {
@@ -337,6 +344,7 @@ int32_t bhd_matmul(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float
     const int32_t st = check_matvec_args(ctx, w, slab, x_dev, y_dev, m, 1.0f, "matmul");
     if (st != BHD_OK) return st;
     if (m == 0 || w->rows == 0) return BHD_OK;
+    bhd_device_guard guard(ctx);
     cudaStream_t s = cudaStream_t(stream);
     bool handled = false;
     const int32_t gs = bhd_launch_gemm_q8_tcgen05(ctx, w, slab, x_dev, y_dev, m, s, &handled);
@@ -362,33 +370,91 @@ static int32_t ensure_stage(bhd_ctx* ctx, float** buf, size_t* have, size_t byte
     return BHD_OK;
 }
 
+// The device address of a page-locked host buffer (unified addressing), or nullptr for pageable memory.
+static float* mapped_address(const void* host) {
+    cudaPointerAttributes a;
+    float* dev = nullptr;
+    if (cudaPointerGetAttributes(&a, host) == cudaSuccess && a.type == cudaMemoryTypeHost && a.devicePointer)
+        dev = static_cast<float*>(a.devicePointer);
+    cudaGetLastError();  // a pageable pointer is reported as an error by older drivers: not ours to keep
+    return dev;
+}
+
+// Reports what the kernels of the host-buffer stream flagged. `bits` was copied by the stream itself.
+static int32_t report_status_bits(bhd_ctx* ctx, uint32_t bits) {
+    if (bits == 0) return BHD_OK;
+    return bhd_fail(ctx, BHD_ERR_DEVICE_STATUS, "device status 0x%x:%s%s%s%s%s", bits,
+                    (bits & BHD_DEV_NAN_IN_SOFTMAX) ? " softmax input cannot contain NaN;" : "",
+                    (bits & BHD_DEV_BAD_EXPERT_ID) ? " expert id out of range;" : "",
+                    (bits & BHD_DEV_WAIT_TIMEOUT) ? " a bounded wait gave up;" : "",
+                    (bits & BHD_DEV_BAD_ROUTE_PROB) ? " router probabilities not finite, non-negative with a positive sum;" : "",
+                    (bits & BHD_DEV_ACTIVATION_RANGE) ? " an activation is NaN or infinite, or beyond the fp16 range (|x| > 65504) on a path with fp16 operands;" : "");
+}
+
+// Waits for the host-buffer stream and reports the status word (read and cleared in stream order).
+static int32_t finish_host_stream(bhd_ctx* ctx) {
+    cudaStream_t s = ctx->host_stream;
+    BHD_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, 4, cudaMemcpyDeviceToHost, s), "reading the status word");
+    BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the host-buffer stream");
+    const uint32_t bits = ctx->status_host[0];
+    if (bits == 0) return BHD_OK;
+    BHD_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, 4, s), "clearing the status word");
+    BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the host-buffer stream");
+    return report_status_bits(ctx, bits);
+}
+
+// Enqueues one host-buffer matvec on the context's own stream, without waiting for it.
+static int32_t enqueue_matvec_host(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x_host, float* y_host,
+                                   uint32_t batch, float scale, int32_t accumulate) {
+    const size_t xb = size_t(batch) * w->cols * sizeof(float), yb = size_t(batch) * w->rows * sizeof(float);
+    cudaStream_t s = ctx->host_stream;
+    int32_t st;
+    // A page-locked output buffer is addressable from the device (unified addressing): the
+    // kernel then writes y across PCIe itself, which saves one copy operation per call. x is
+    // always staged in device memory, because every cluster of CTAs reads all of it; a
+    // page-locked x is staged by a small kernel chained to the matvec by programmatic dependent
+    // launch (the fetch across PCIe hides behind the previous matvec), a pageable one by a copy.
+    float* y_direct = accumulate ? nullptr : mapped_address(y_host);
+    const float* x_mapped = mapped_address(x_host);
+    if ((st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb ? xb : 16, "activation staging")) != BHD_OK) return st;
+    if (!y_direct && (st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb, "output staging")) != BHD_OK) return st;
+    if (xb) {
+        if (x_mapped && (reinterpret_cast<uintptr_t>(x_mapped) & 15) == 0 && xb % 16 == 0) {
+            if ((st = bhd_launch_stage_copy(ctx, x_mapped, ctx->stage_x, xb / 16, s)) != BHD_OK) return st;
+        } else {
+            BHD_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, s), "copying activations in");
+        }
+    }
+    if (accumulate) BHD_CUDA(ctx, cudaMemcpyAsync(ctx->stage_y, y_host, yb, cudaMemcpyHostToDevice, s), "copying outputs in");
+    st = bhd_matvec(ctx, w, slab, ctx->stage_x, y_direct ? y_direct : ctx->stage_y, batch, scale, accumulate, s);
+    if (st != BHD_OK) return st;
+    if (!y_direct) BHD_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s), "copying outputs back");
+    return BHD_OK;
+}
+
 int32_t bhd_matvec_host(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x_host, float* y_host,
                         uint32_t batch, float scale, int32_t accumulate) {
     int32_t st = check_matvec_args(ctx, w, slab, x_host, y_host, batch, scale, "matvec_host");
     if (st != BHD_OK) return st;
     if (batch == 0 || w->rows == 0) return BHD_OK;
-    cudaSetDevice(ctx->device);
-    const size_t xb = size_t(batch) * w->cols * sizeof(float), yb = size_t(batch) * w->rows * sizeof(float);
-    cudaStream_t s = 0;
-    // A page-locked output buffer is addressable from the device (unified addressing): the
-    // kernel then writes y across PCIe itself, which saves one copy operation and its launch
-    // latency per call. x is always staged, because every cluster of CTAs reads all of it.
-    float* y_direct = nullptr;
-    if (!accumulate) {
-        cudaPointerAttributes ay;
-        if (cudaPointerGetAttributes(&ay, y_host) == cudaSuccess && ay.type == cudaMemoryTypeHost && ay.devicePointer)
-            y_direct = static_cast<float*>(ay.devicePointer);
-        cudaGetLastError();  // a pageable pointer is reported as an error by older drivers: not ours to keep
-    }
-    if ((st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb ? xb : 16, "activation staging")) != BHD_OK) return st;
-    if (!y_direct && (st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb, "output staging")) != BHD_OK) return st;
-    if (xb) BHD_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, s), "copying activations in");
-    if (accumulate) BHD_CUDA(ctx, cudaMemcpyAsync(ctx->stage_y, y_host, yb, cudaMemcpyHostToDevice, s), "copying outputs in");
-    st = bhd_matvec(ctx, w, slab, ctx->stage_x, y_direct ? y_direct : ctx->stage_y, batch, scale, accumulate, s);
+    bhd_device_guard guard(ctx);
+    if ((st = enqueue_matvec_host(ctx, w, slab, x_host, y_host, batch, scale, accumulate)) != BHD_OK) return st;
+    return finish_host_stream(ctx);
+}
+
+int32_t bhd_matvec_host_async(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x_host, float* y_host,
+                              uint32_t batch, float scale, int32_t accumulate) {
+    int32_t st = check_matvec_args(ctx, w, slab, x_host, y_host, batch, scale, "matvec_host_async");
     if (st != BHD_OK) return st;
-    if (!y_direct) BHD_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, s), "copying outputs back");
-    BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the matvec");
-    return BHD_OK;
+    if (batch == 0 || w->rows == 0) return BHD_OK;
+    bhd_device_guard guard(ctx);
+    return enqueue_matvec_host(ctx, w, slab, x_host, y_host, batch, scale, accumulate);
+}
+
+int32_t bhd_sync(bhd_ctx* ctx) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    bhd_device_guard guard(ctx);
+    return finish_host_stream(ctx);
 }
 
 int32_t bhd_moe_layer_host(bhd_ctx* ctx, const bhd_weight* router, const bhd_weight* gate_exps,
@@ -400,7 +466,7 @@ int32_t bhd_moe_layer_host(bhd_ctx* ctx, const bhd_weight* router, const bhd_wei
         return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_layer_host: tensors are not weights of this context");
     if (n_positions == 0) return BHD_OK;
     if (!x_host || !y_host) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_layer_host: null buffer");
-    cudaSetDevice(ctx->device);
+    bhd_device_guard guard(ctx);
     const uint64_t dim = router->cols, ne = router->rows;
     const size_t xb = size_t(n_positions) * dim * sizeof(float);
     const size_t rb = size_t(n_positions) * top_k * 4;
@@ -409,7 +475,7 @@ int32_t bhd_moe_layer_host(bhd_ctx* ctx, const bhd_weight* router, const bhd_wei
     int32_t st;
     if ((st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb, "activation staging")) != BHD_OK) return st;
     if ((st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb, "output staging")) != BHD_OK) return st;
-    cudaStream_t s = 0;
+    cudaStream_t s = ctx->host_stream;
     float* y_dev = ctx->stage_y;
     int32_t* e_dev = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(y_dev) + xb);
     float* w_dev = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(e_dev) + rb);
@@ -423,24 +489,24 @@ int32_t bhd_moe_layer_host(bhd_ctx* ctx, const bhd_weight* router, const bhd_wei
     if (experts_host) BHD_CUDA(ctx, cudaMemcpyAsync(experts_host, e_dev, rb, cudaMemcpyDeviceToHost, s), "copying experts back");
     if (weights_host) BHD_CUDA(ctx, cudaMemcpyAsync(weights_host, w_dev, rb, cudaMemcpyDeviceToHost, s), "copying route weights back");
     if (counts_host) BHD_CUDA(ctx, cudaMemcpyAsync(counts_host, c_dev, ne * 4, cudaMemcpyDeviceToHost, s), "copying counts back");
-    BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the routed layer");
-    return bhd_check_status(ctx, s);
+    return finish_host_stream(ctx);
 }
 
 int32_t bhd_check_status(bhd_ctx* ctx, void* stream) {
     if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    bhd_device_guard guard(ctx);
     cudaStream_t s = cudaStream_t(stream);
     BHD_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, 4, cudaMemcpyDeviceToHost, s), "reading the status word");
     BHD_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, 4, s), "clearing the status word");
     BHD_CUDA(ctx, cudaStreamSynchronize(s), "waiting for the status word");
-    const uint32_t bits = ctx->status_host[0];
-    if (bits == 0) return BHD_OK;
-    return bhd_fail(ctx, BHD_ERR_DEVICE_STATUS, "device status 0x%x:%s%s%s%s%s", bits,
-                    (bits & BHD_DEV_NAN_IN_SOFTMAX) ? " softmax input cannot contain NaN;" : "",
-                    (bits & BHD_DEV_BAD_EXPERT_ID) ? " expert id out of range;" : "",
-                    (bits & BHD_DEV_WAIT_TIMEOUT) ? " a bounded wait gave up;" : "",
-                    (bits & BHD_DEV_BAD_ROUTE_PROB) ? " router probabilities not finite, non-negative with a positive sum;" : "",
-                    (bits & BHD_DEV_ACTIVATION_RANGE) ? " an activation is NaN or infinite, or beyond the fp16 range (|x| > 65504) on a path with fp16 operands;" : "");
+    return report_status_bits(ctx, ctx->status_host[0]);
+}
+
+int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one_copy) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    ctx->spin_limit = spin_limit;
+    ctx->debug_drop = drop_one_copy ? 1u : 0u;
+    return BHD_OK;
 }
 
 uint64_t bhd_launch_count(const bhd_ctx* ctx) { return valid_ctx(ctx) ? ctx->launches : 0; }

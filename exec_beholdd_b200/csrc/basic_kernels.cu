@@ -144,6 +144,41 @@ int32_t bhd_launch_matvec_general(bhd_ctx* ctx, const bhd_weight* w, uint64_t sl
     return BHD_OK;
 }
 
+// ---- staging of page-locked host activations --------------------------------------------
+namespace {
+
+// Copies n16 16-byte words from a page-locked host buffer (addressed through unified addressing)
+// into device memory. Launched with programmatic stream serialization: the words are fetched
+// across PCIe before the wait, while the previous kernel of the stream (which may still read
+// dst) is running, and written after it has finished. Nothing on the GPU writes the source.
+__global__ void k_stage_copy(const uint4* src, uint4* __restrict__ dst, size_t n16) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (i < n16) v = __ldcv(src + i);  // never a cached copy: the host rewrites this buffer between calls
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (i < n16) dst[i] = v;
+}
+
+}  // namespace
+
+int32_t bhd_launch_stage_copy(bhd_ctx* ctx, const float* src_mapped, float* dst_dev, size_t n16, cudaStream_t s) {
+    if (n16 == 0) return BHD_OK;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned((n16 + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_stage_copy, reinterpret_cast<const uint4*>(src_mapped), reinterpret_cast<uint4*>(dst_dev), n16),
+             "launching the activation staging kernel");
+    ctx->launches += 1;
+    return BHD_OK;
+}
+
 // ---- elementwise operators --------------------------------------------------------------
 
 namespace {
@@ -172,6 +207,7 @@ extern "C" int32_t bhd_swiglu(bhd_ctx* ctx, float* gate_dev, const float* up_dev
     if (!ctx || ctx->magic != BHD_CTX_MAGIC) return BHD_ERR_INVALID_ARGUMENT;
     if (n == 0) return BHD_OK;
     if (!gate_dev || !up_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "swiglu: null buffer");
+    bhd_device_guard guard(ctx);
     k_swiglu<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(gate_dev, up_dev, n, limit);
     BHD_LAUNCHED(ctx, "swiglu kernel");
     return BHD_OK;
@@ -182,6 +218,7 @@ extern "C" int32_t bhd_add_in_place(bhd_ctx* ctx, float* output_dev, const float
     if (!ctx || ctx->magic != BHD_CTX_MAGIC) return BHD_ERR_INVALID_ARGUMENT;
     if (n == 0) return BHD_OK;
     if (!output_dev || !residual_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "add_in_place: null buffer");
+    bhd_device_guard guard(ctx);
     k_add_in_place<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(output_dev, residual_dev, n);
     BHD_LAUNCHED(ctx, "add_in_place kernel");
     return BHD_OK;

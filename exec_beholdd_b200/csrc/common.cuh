@@ -11,6 +11,7 @@
 #include "../../include/beholdd_b200.h"
 
 #define BHD_CTX_MAGIC 0x62686443u  // "bhdC"
+#define BHD_MAX_DEVICES 64  // contexts are refused on device indices beyond this
 #define BHD_WEIGHT_MAGIC 0x62686457u  // "bhdW"
 
 // Device status word bits (kernels OR them in; bhd_check_status reports and clears them).
@@ -35,6 +36,9 @@ struct bhd_ctx {
     size_t stage_x_bytes, stage_y_bytes;
     void* pinned;           // pinned bounce buffer for host entry points
     size_t pinned_bytes;
+    cudaStream_t host_stream;  // non-blocking stream of the host-buffer entry points
+    uint32_t spin_limit;    // polls a bounded wait makes before it gives up (0: the kernel's default)
+    uint32_t debug_drop;    // test hook: the next decode matvec leaves this many copies unrequested
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
 };
@@ -55,6 +59,37 @@ struct bhd_weight {
     uint32_t tmap_box_rows, tmap_box_bytes;
     alignas(64) unsigned char tmap16[128];  // same view with a 16-row box (decode kernel)
     bool tmap16_ok;
+};
+
+// Makes the context's GPU the calling thread's current device for the duration of one exported
+// call and puts the caller's device back afterwards, so a host with several GPUs (or a current
+// device that differs from the context's) launches on the right one. It also empties the
+// thread's "last error" slot: an error another library left there must not be mistaken for a
+// failure of the launch that follows.
+struct bhd_device_guard {
+    int prev = -1;
+    bool switched = false;
+    explicit bhd_device_guard(const bhd_ctx* ctx) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != ctx->device) {
+            cudaSetDevice(ctx->device);
+            switched = true;
+        }
+        cudaGetLastError();
+    }
+    ~bhd_device_guard() {
+        if (switched && prev >= 0) cudaSetDevice(prev);
+    }
+    bhd_device_guard(const bhd_device_guard&) = delete;
+    bhd_device_guard& operator=(const bhd_device_guard&) = delete;
+};
+
+// Work that must happen once per GPU (kernel attributes are per device): `static bhd_once_per_device once;`
+// at the launch site, then `if (once.first(ctx)) { ... }`.
+struct bhd_once_per_device {
+    bool done[BHD_MAX_DEVICES] = {};
+    bool pending(const bhd_ctx* ctx) const { return !done[ctx->device]; }
+    void mark(const bhd_ctx* ctx) { done[ctx->device] = true; }
 };
 
 int32_t bhd_fail(bhd_ctx* ctx, int32_t status, const char* fmt, ...);
@@ -193,6 +228,7 @@ int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_
                                   float* out0, float* out1, const float* slot_weight, cudaStream_t s);
 int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
                                 const float* src, const float* src2, uint32_t K, uint32_t n_slots, void* out, cudaStream_t s);
+int32_t bhd_launch_stage_copy(bhd_ctx* ctx, const float* src_mapped, float* dst_dev, size_t n16, cudaStream_t s);
 size_t bhd_moe_slots_i8_bytes(uint32_t K, uint32_t n_slots);
 bool bhd_moe_i8_usable(const bhd_weight* w);
 

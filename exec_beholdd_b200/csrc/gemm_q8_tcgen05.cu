@@ -166,7 +166,9 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     // stage, alternating by use, because a converter group sees only every other use of a stage and the two
     // MMA issuers are not ordered with each other: on a single barrier a parity wait could be a whole phase
     // early. On its own barrier every waiter sees every phase.
-    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[8], b_full[8], st_empty[8][2], tmem_full;
+    // a_full / b_full follow the same rule for the same reason: with an odd number of stages an MMA issuer
+    // (alternate slices) meets only every other use of a stage.
+    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[8][2], b_full[8][2], st_empty[8][2], tmem_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -187,8 +189,10 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 4 * NG); }
         for (uint32_t i = 0; i < S; ++i) {
-            mbar_init(&a_full[i], 4);
-            mbar_init(&b_full[i], 1);
+            mbar_init(&a_full[i][0], 4);
+            mbar_init(&a_full[i][1], 4);
+            mbar_init(&b_full[i][0], 1);
+            mbar_init(&b_full[i][1], 1);
             mbar_init(&st_empty[i][0], 1);
             mbar_init(&st_empty[i][1], 1);
         }
@@ -228,8 +232,9 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
             for (uint32_t it = 0; it < slices && !aborted(); ++it) {
                 const uint32_t s = it % S;
                 if (!stage_free(it)) { give_up(); break; }
-                mbar_arrive_expect_tx(&b_full[s], bn * 128u);
-                tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), &b_full[s]);
+                uint64_t* bf = &b_full[s][(it / S) & 1];
+                mbar_arrive_expect_tx(bf, bn * 128u);
+                tma_load_2d(stage_addr + s * stage_bytes + a_bytes, &tmap_x, int(it * SLICE_K), int(m0), bf);
             }
         }
     } else if (warp == 1 || warp == MW) {
@@ -242,8 +247,8 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
             const uint32_t first = warp == 1 ? 0u : 1u, acc = tmem_base + first * bn;
             bool ok = true;
             for (uint32_t it = first; it < slices && ok; it += 2) {
-                const uint32_t s = it % S, par = (it / S) & 1;
-                if (aborted() || !mbar_wait(&b_full[s], par) || !mbar_wait(&a_full[s], par)) { give_up(); ok = false; break; }
+                const uint32_t s = it % S, use = it / S, par = (use >> 1) & 1;
+                if (aborted() || !mbar_wait(&b_full[s][use & 1], par) || !mbar_wait(&a_full[s][use & 1], par)) { give_up(); ok = false; break; }
                 tc_fence_after();
                 const uint64_t da = umma_desc(stage_addr + s * stage_bytes), db = umma_desc(stage_addr + s * stage_bytes + a_bytes);
 #pragma unroll
@@ -303,7 +308,7 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&a_full[s]);  // one arrival per converter warp
+                if (lane == 0) mbar_arrive(&a_full[s][(it / S) & 1]);  // one arrival per converter warp
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&pk_empty[pb]);
@@ -394,11 +399,11 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the activation tensor map", bhd_device_name());
     }
-    static int cached_device = -1;
-    if (cached_device != ctx->device) {
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<PLAIN_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
                  "raising the shared memory limit");
-        cached_device = ctx->device;
+        once.mark(ctx);
     }
     GemmParams p;
     p.y = y;

@@ -463,10 +463,10 @@ int32_t launch_decode(bhd_ctx* ctx, const bhd_weight* w, const DecodeParams& p, 
     constexpr int STAGE = (W_BYTES + X_BYTES + 127) / 128 * 128;
     constexpr size_t DYN = size_t(WARPS) * RING * STAGE + 128;
     auto kern = k_matvec_decode<KIND, NB>;
-    static int cached_device = -1;
-    if (cached_device != ctx->device) {
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(DYN)), "raising the shared memory limit");
-        cached_device = ctx->device;
+        once.mark(ctx);
     }
     CUtensorMap map;
     memcpy(&map, w->tmap16, sizeof(map));
@@ -586,7 +586,7 @@ constexpr size_t BHD_NOALLOC_SCRATCH_BYTES = 288 * 1024;
 static __device__ __align__(256) uint8_t g_noalloc_scratch[BHD_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-constexpr int MAX_DEVICES = 64;
+constexpr int MAX_DEVICES = BHD_MAX_DEVICES;
 // Device address of g_noalloc_scratch per CUDA device. In host code the symbol's name is only a
 // handle for the runtime, not a device pointer, so the address is looked up once per device.
 uint8_t* g_noalloc_ptr[MAX_DEVICES] = {};
@@ -606,6 +606,7 @@ extern "C" __attribute__((visibility("default"))) int32_t bhd_matvec_noalloc(bhd
     if (!x_dev || !y_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "matvec_noalloc: null buffer");
     if (batch > 4)
         return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: matvec_noalloc serves at most 4 activation vectors, got %u", batch);
+    bhd_device_guard guard(ctx);  // the context's GPU is current for the rest of the call, the caller's afterwards
     cudaStream_t s = cudaStream_t(stream);
     const bool tma_path = w->tmap16_ok && w->cols != 0 && w->cols % 4 == 0 && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 &&
                           w->rows <= 0x7fffffffull;
@@ -623,8 +624,7 @@ extern "C" __attribute__((visibility("default"))) int32_t bhd_matvec_noalloc(bhd
     if (ctx->device < 0 || ctx->device >= MAX_DEVICES)
         return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "matvec_noalloc: device index %d out of range", ctx->device);
     if (!g_noalloc_ptr[ctx->device]) {
-        // First call on this device: resolve the array's device address (with the device current).
-        BHD_CUDA(ctx, cudaSetDevice(ctx->device), "selecting the device");
+        // First call on this device: resolve the array's device address (the guard above made the device current).
         void* p = nullptr;
         BHD_CUDA(ctx, cudaGetSymbolAddress(&p, g_noalloc_scratch), "resolving the fixed scratch array");
         g_noalloc_ptr[ctx->device] = static_cast<uint8_t*>(p);

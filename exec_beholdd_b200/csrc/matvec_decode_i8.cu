@@ -63,9 +63,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SPIN_LIMIT) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -245,6 +245,8 @@ struct DecodeI8Params {
     uint32_t rows, row_base, chunks, batch, cols, tiles, chunks_per_cta;
     float scale;
     int accumulate;
+    uint32_t spin_limit;  // polls a wait makes before it gives up
+    uint32_t drop_copy;   // test hook: warp 0 of tile 0 leaves its first weight copy unrequested, so its wait runs out
 };
 
 template <uint32_t KIND>
@@ -288,6 +290,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
     auto issue_w = [&](uint32_t i) {
         const uint32_t chunk = first + i * CSTEP, slot = i % RING;
         mbar_arrive_expect_tx(&bars[warp][slot], W_BYTES);
+        if (p.drop_copy && i == 0 && warp == 0 && blockIdx.x == 0) return;
         const uint32_t byte0 = (KIND == BHD_TYPE_Q6_K) ? ((210u * chunk) & ~15u) : uint32_t(BOX) * chunk;
         tma_load_2d(ring + slot * STAGE, &tmap, int(byte0 >> 1), int(p.row_base + tile * ROWS), &bars[warp][slot]);
     };
@@ -342,8 +345,11 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
             mq[tl] = mq_next[tl];
         }
         if (i + 1 < my_chunks) load_x(chunk + CSTEP, bq_next, mq_next);
-        if (!mbar_wait(&bars[warp][slot], (i / RING) & 1)) {
+        if (!mbar_wait(&bars[warp][slot], (i / RING) & 1, p.spin_limit)) {
             if (lane == 0) atomicOr(p.status, BHD_DEV_WAIT_TIMEOUT);
+            // Give up on this warp's rows, but not before the copies it has already requested into the other
+            // slots of its ring have landed (bounded again): the CTA must not end with copies in flight.
+            for (uint32_t j = i + 1; j < my_chunks && j < i + RING; ++j) mbar_wait(&bars[warp][j % RING], (j / RING) & 1, p.spin_limit);
             break;
         }
         const uint32_t st = ring32 + slot * STAGE;
@@ -532,11 +538,11 @@ int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cu
     constexpr int STAGE = (W_BYTES + 127) / 128 * 128;
     constexpr size_t RING_BYTES = size_t(WARPS) * RING * STAGE + 128;
     auto kern = k_matvec_decode_i8<KIND, NB, RING, KS>;
-    static int cached_device = -1;
-    if (cached_device != ctx->device) {
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RING_BYTES + MAX_X_SMEM)),
                  "raising the shared memory limit");
-        cached_device = ctx->device;
+        once.mark(ctx);
     }
     CUtensorMap map;
     memcpy(&map, w->tmap16, sizeof(map));
@@ -600,6 +606,9 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     p.chunks_per_cta = per_cta;
     p.scale = scale;
     p.accumulate = accumulate;
+    p.spin_limit = ctx->spin_limit ? ctx->spin_limit : SPIN_LIMIT;
+    p.drop_copy = ctx->debug_drop;
+    ctx->debug_drop = 0;  // one launch only
     int32_t st = BHD_OK;
 #define BHD_CASE(K)                                          \
     case K:                                                  \

@@ -538,7 +538,7 @@ __host__ __device__ constexpr int moe_cls(int nb) { return nb <= 4 ? 0 : (nb <= 
 // route bitmap per expert, so the order is deterministic -- and lists the groups.
 __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ experts, const float* __restrict__ weights,
                                                    uint32_t n_routes, uint32_t first_expert, uint32_t n_local,
-                                                   MoeHeader* hdr,
+                                                   uint32_t n_total, MoeHeader* hdr,
                                                    uint32_t* counts, uint32_t* offsets, int32_t* route_slot,
                                                    int32_t* slot_route, float* slot_weight, MoeGroup* groups,
                                                    int32_t* glist, uint32_t gmax, uint32_t* bitmap, uint32_t* prefix,
@@ -555,7 +555,7 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ e
     __syncthreads();
     for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
         const int32_t e = experts[r];
-        if (e < 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+        if (e < 0 || uint32_t(e) >= n_total) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);  // ids of other ranks are skipped, ids of no rank reported
         if (e >= int32_t(first_expert) && uint32_t(e) < first_expert + n_local)
             atomicOr(&bitmap[(uint32_t(e) - first_expert) * words + (r >> 5)], 1u << (r & 31));
         else
@@ -698,8 +698,9 @@ template <uint32_t KIND, int NT>
 int32_t launch_one(bhd_ctx* ctx, const bhd_weight* w, const MatvecParams& base, cudaStream_t s) {
     using S = Smem<KIND, NT>;
     auto kern = k_matvec_mma<KIND, NT>;
-    static int ring = 0, per_sm = 0, cached_device = -1;  // per instantiation
-    if (cached_device != ctx->device) {
+    static int ring = 0, per_sm = 0;  // per instantiation; every GPU this library accepts is the same part
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
         int r = 4;
         size_t dyn = size_t(r) * S::STAGE + 128;
         if (dyn > 200 * 1024) { r = 3; dyn = size_t(r) * S::STAGE + 128; }
@@ -709,7 +710,7 @@ int32_t launch_one(bhd_ctx* ctx, const bhd_weight* w, const MatvecParams& base, 
         if (occ < 1) return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: matvec kernel does not fit on an SM", bhd_device_name());
         per_sm = occ > 4 ? 4 : occ;
         ring = r;
-        cached_device = ctx->device;
+        once.mark(ctx);
     }
     MatvecParams p = base;
     const uint32_t slots = uint32_t(ctx->sm_count) * per_sm;
@@ -866,15 +867,17 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
 // when the tensors do not meet the rules of the TMA path (Q8_0, 16-byte aligned rows).
 int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
                              const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
-                             uint32_t first_expert, uint32_t n_local, float* y, int accumulate, cudaStream_t s,
-                             bool* handled) {
+                             uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y, int accumulate,
+                             cudaStream_t s, bool* handled) {
     *handled = false;
     if (!bhd_moe_i8_usable(gate) || !bhd_moe_i8_usable(up) || !bhd_moe_i8_usable(down)) return BHD_OK;
     if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return BHD_OK;
     const uint64_t ff = gate->rows, dim = gate->cols;
     if (dim % 8 != 0 || ff % 8 != 0) return BHD_OK;
     const uint64_t R64 = T * top_k;
-    if (R64 > (1u << 22) || n_local > 1024) return BHD_OK;
+    // 2^20 routes keep every grid dimension of the grouped kernels (at most routes / 17 groups of the
+    // largest class on grid.y) within 65535; more routes take the general kernels.
+    if (R64 > (1u << 20) || n_local > 1024) return BHD_OK;
     const uint32_t R = uint32_t(R64), E = n_local;
     const uint32_t words = (R + 31) / 32;
     const uint32_t gmax = E + R / 32 + 1;
@@ -901,13 +904,13 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
 
     const size_t plan_smem = size_t(E) * words * 8;
     const int plan_on_chip = plan_smem <= 160 * 1024;
-    static int plan_device = -1;
-    if (plan_device != ctx->device) {
+    static bhd_once_per_device plan_once;
+    if (plan_once.pending(ctx)) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(k_moe_plan, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), "raising the shared memory limit");
-        plan_device = ctx->device;
+        plan_once.mark(ctx);
     }
     // one thread per local expert in the group-building step
-    k_moe_plan<<<1, (R <= 256 && E <= 256) ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, hdr,
+    k_moe_plan<<<1, (R <= 256 && E <= 256) ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, n_total, hdr,
                                   reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
                                   route_slot, slot_route, slot_weight, groups, glist, gmax,
                                   reinterpret_cast<uint32_t*>(ws + o_bitmap), reinterpret_cast<uint32_t*>(ws + o_prefix),

@@ -253,8 +253,8 @@ __global__ void k_moe_gate_up_warp(const uint8_t* __restrict__ gate, const uint8
                                    const float* __restrict__ x, const int32_t* __restrict__ experts, uint32_t top_k,
                                    uint32_t first_expert, uint32_t n_local, uint32_t n_experts_total,
                                    float* __restrict__ act, uint32_t* __restrict__ status) {
-    const uint32_t route = blockIdx.y;
-    const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t route = blockIdx.x;
+    const uint32_t f = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (f >= ff) return;
     const int32_t e = experts[route];
@@ -286,8 +286,8 @@ __global__ void k_moe_down_warp(const uint8_t* __restrict__ down, uint64_t slab_
                                 const int32_t* __restrict__ experts, const float* __restrict__ weights,
                                 uint32_t top_k, uint32_t first_expert, uint32_t n_local, float* __restrict__ y,
                                 int accumulate) {
-    const uint32_t t = blockIdx.y;
-    const uint32_t h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t t = blockIdx.x;
+    const uint32_t h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (h >= dim) return;
     float out = 0.0f;
@@ -324,12 +324,30 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
 
+namespace {
+__global__ void k_expf_exact(const float* __restrict__ in, float* __restrict__ out, uint64_t n) {
+    const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (i < n) out[i] = bhd_expf_exact(in[i]);
+}
+}  // namespace
+
+extern "C" int32_t bhd_debug_expf(bhd_ctx* ctx, const float* in_dev, float* out_dev, uint64_t n, void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (n == 0) return BHD_OK;
+    if (!in_dev || !out_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "debug_expf: null buffer");
+    bhd_device_guard guard(ctx);
+    k_expf_exact<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(in_dev, out_dev, n);
+    BHD_LAUNCHED(ctx, "expf kernel");
+    return BHD_OK;
+}
+
 extern "C" int32_t bhd_softmax(bhd_ctx* ctx, float* v_dev, uint64_t n_rows, uint64_t n, void* stream) {
     if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
     if (n == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: softmax input cannot be empty");
     if (n > 1024) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: softmax rows longer than 1024 are not supported");
     if (n_rows == 0) return BHD_OK;
     if (!v_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "softmax: null buffer");
+    bhd_device_guard guard(ctx);
     // Reuses the router kernel with top_k = 0: softmax only.
     const unsigned threads = unsigned((n + 31) / 32 * 32);
     const size_t smem = n * sizeof(float) + 16;
@@ -351,6 +369,7 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     if (n_experts > 1024) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: more than 1024 experts are not supported");
     if (n_positions == 0) return BHD_OK;
     if (!x_dev || !experts_dev || !weights_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_route: null buffer");
+    bhd_device_guard guard(ctx);
     cudaStream_t s = cudaStream_t(stream);
     float* probs = probs_dev;
     if (!probs) {
@@ -362,13 +381,13 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     // Router logits in the CPU's summation order (forward.rs:1330-1336 -> cpu.rs:198-218).
     if (router->kind == BHD_TYPE_F32 && n_positions <= 65535ull * 8 && router->cols % 4 == 0 &&
         (reinterpret_cast<uintptr_t>(router->dev) & 15) == 0 && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0) {
-        static int cached_device = -1;
-        if (cached_device != ctx->device) {
+        static bhd_once_per_device once;
+        if (once.pending(ctx)) {
             BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32<8, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rt_smem_bytes(8, 7))),
                      "raising the shared memory limit");
             BHD_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_f32<32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rt_smem_bytes(32, 3))),
                      "raising the shared memory limit");
-            cached_device = ctx->device;
+            once.mark(ctx);
         }
         const float* rw = reinterpret_cast<const float*>(router->dev);
         const unsigned gx = unsigned((n_experts + RT_EXP - 1) / RT_EXP);
@@ -395,20 +414,22 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
 
 int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
                              const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
-                             uint32_t first_expert, uint32_t n_local, float* y, int accumulate, cudaStream_t s,
-                             bool* handled);
+                             uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y, int accumulate,
+                             cudaStream_t s, bool* handled);
 
-extern "C" int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps,
-                                   const bhd_weight* down_exps, const float* x_dev, uint64_t n_positions,
-                                   uint32_t top_k, const int32_t* experts_dev, const float* weights_dev,
-                                   uint32_t first_expert, uint32_t n_local, float* y_dev, int32_t accumulate,
-                                   void* stream) {
-    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+namespace {
+
+// Everything bhd_moe_experts checks before it touches an output; bhd_moe_layer runs the same
+// checks before it routes, so that a refused call leaves the routing outputs alone too.
+int32_t validate_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps, const bhd_weight* down_exps,
+                         const float* x_dev, uint64_t n_positions, uint32_t top_k, const int32_t* experts_dev,
+                         const float* weights_dev, uint32_t n_local, const float* y_dev) {
     if (!valid_w(ctx, gate_exps) || !valid_w(ctx, up_exps) || !valid_w(ctx, down_exps))
         return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_experts: expert tensors are not weights of this context");
     if (gate_exps->kind != BHD_TYPE_Q8_0 || up_exps->kind != BHD_TYPE_Q8_0 || down_exps->kind != BHD_TYPE_Q8_0)
         return bhd_fail(ctx, BHD_ERR_UNSUPPORTED_FORMAT, "%s cannot decode %s routed experts (Q8_0 only)",
-                        bhd_device_name(), bhd_kind_name(gate_exps->kind));
+                        bhd_device_name(), bhd_kind_name(gate_exps->kind != BHD_TYPE_Q8_0 ? gate_exps->kind
+                                                         : (up_exps->kind != BHD_TYPE_Q8_0 ? up_exps->kind : down_exps->kind)));
     const uint64_t ff = gate_exps->rows, dim = gate_exps->cols;
     if (up_exps->rows != ff || up_exps->cols != dim || down_exps->rows != dim || down_exps->cols != ff ||
         gate_exps->slabs != up_exps->slabs || gate_exps->slabs != down_exps->slabs)
@@ -428,29 +449,59 @@ extern "C" int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, co
         return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_experts: null buffer");
     if (n_positions * top_k > 0x7fffffffull || dim > 0x7fffffffull || ff > 0x7fffffffull)
         return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: routed block too large");
-    cudaStream_t s = cudaStream_t(stream);
+    return BHD_OK;
+}
 
+int32_t run_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps, const bhd_weight* down_exps,
+                    const float* x_dev, uint64_t n_positions, uint32_t top_k, const int32_t* experts_dev,
+                    const float* weights_dev, uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y_dev,
+                    int32_t accumulate, cudaStream_t s) {
+    const uint64_t ff = gate_exps->rows, dim = gate_exps->cols;
     bool handled = false;
     int32_t st = bhd_moe_experts_fast(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev,
-                                      weights_dev, first_expert, n_local, y_dev, accumulate, s, &handled);
+                                      weights_dev, first_expert, n_local, n_total, y_dev, accumulate, s, &handled);
     if (st != BHD_OK || handled) return st;
 
+    // General kernels: one warp per (route, row). Grids put the large dimension on x.
     const uint64_t routes = n_positions * top_k;
     st = bhd_ensure_workspace(ctx, align_up(routes * ff * sizeof(float), 256), s);
     if (st != BHD_OK) return st;
     float* act = reinterpret_cast<float*>(ctx->workspace);
     const int warps = 8;
-    // An expert id beyond every rank's range is an error; ids outside this rank's range are skipped.
-    const uint32_t total = 0x7fffffffu;
-    k_moe_gate_up_warp<<<dim3(unsigned((ff + warps - 1) / warps), unsigned(routes)), warps * 32, 0, s>>>(
+    const uint32_t ff_blocks = uint32_t((ff + warps - 1) / warps), dim_blocks = uint32_t((dim + warps - 1) / warps);
+    if (ff_blocks > 65535u || dim_blocks > 65535u)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: expert matrices of %llu x %llu are beyond the general kernels",
+                        (unsigned long long)ff, (unsigned long long)dim);
+    k_moe_gate_up_warp<<<dim3(unsigned(routes), ff_blocks), warps * 32, 0, s>>>(
         gate_exps->dev, up_exps->dev, gate_exps->slab_bytes, gate_exps->row_bytes, uint32_t(dim), uint32_t(ff), x_dev,
-        experts_dev, top_k, first_expert, n_local, total, act, ctx->status_dev);
+        experts_dev, top_k, first_expert, n_local, n_total, act, ctx->status_dev);
     BHD_LAUNCHED(ctx, "expert gate/up kernel");
-    k_moe_down_warp<<<dim3(unsigned((dim + warps - 1) / warps), unsigned(n_positions)), warps * 32, 0, s>>>(
+    k_moe_down_warp<<<dim3(unsigned(n_positions), dim_blocks), warps * 32, 0, s>>>(
         down_exps->dev, down_exps->slab_bytes, down_exps->row_bytes, uint32_t(dim), uint32_t(ff), act, experts_dev,
         weights_dev, top_k, first_expert, n_local, y_dev, accumulate);
     BHD_LAUNCHED(ctx, "expert down kernel");
     return BHD_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps,
+                                   const bhd_weight* down_exps, const float* x_dev, uint64_t n_positions,
+                                   uint32_t top_k, const int32_t* experts_dev, const float* weights_dev,
+                                   uint32_t first_expert, uint32_t n_local, uint32_t n_experts, float* y_dev,
+                                   int32_t accumulate, void* stream) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    const int32_t st = validate_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev,
+                                        weights_dev, n_local, y_dev);
+    if (st != BHD_OK || n_positions == 0) return st;
+    if (n_experts != 0 && uint64_t(first_expert) + n_local > n_experts)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: local experts %u..%llu exceed the %u experts of the layer",
+                        first_expert, (unsigned long long)first_expert + n_local, n_experts);
+    bhd_device_guard guard(ctx);
+    // n_experts == 0: the caller does not know the layer's expert count; only negative ids can then be told from
+    // ids that belong to another rank.
+    return run_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev, weights_dev,
+                       first_expert, n_local, n_experts ? n_experts : 0x7fffffffu, y_dev, accumulate, cudaStream_t(stream));
 }
 
 extern "C" int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, float* y_dev, uint64_t n_positions,
@@ -459,6 +510,7 @@ extern "C" int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, flo
     const uint64_t n = n_positions * dim;
     if (n == 0) return BHD_OK;
     if (!per_route_dev || !y_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_combine: null buffer");
+    bhd_device_guard guard(ctx);
     k_moe_combine<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(per_route_dev, y_dev, n, top_k, accumulate);
     BHD_LAUNCHED(ctx, "route combine kernel");
     return BHD_OK;
@@ -476,9 +528,13 @@ extern "C" int32_t bhd_moe_layer(bhd_ctx* ctx, const bhd_weight* router, const b
                         (unsigned long long)router->rows, (unsigned long long)router->cols,
                         (unsigned long long)gate_exps->slabs, (unsigned long long)gate_exps->cols);
     if (!experts_dev || !weights_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "moe_layer: null routing buffers");
-    int32_t st = bhd_moe_route(ctx, router, x_dev, n_positions, top_k, experts_dev, weights_dev, counts_dev, nullptr,
-                               nullptr, stream);
+    // every refusal of the expert half happens before the router writes anything
+    int32_t st = validate_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev, weights_dev,
+                                  uint32_t(gate_exps->slabs), y_dev);
     if (st != BHD_OK) return st;
-    return bhd_moe_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev, weights_dev, 0,
-                           uint32_t(gate_exps->slabs), y_dev, accumulate, stream);
+    bhd_device_guard guard(ctx);
+    st = bhd_moe_route(ctx, router, x_dev, n_positions, top_k, experts_dev, weights_dev, counts_dev, nullptr, nullptr, stream);
+    if (st != BHD_OK || n_positions == 0) return st;
+    return run_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev, weights_dev, 0,
+                       uint32_t(gate_exps->slabs), uint32_t(gate_exps->slabs), y_dev, accumulate, cudaStream_t(stream));
 }

@@ -103,7 +103,7 @@ __device__ __forceinline__ void imma_s8(int (&c)[4], const uint32_t (&a)[4], uin
 __global__ void k_moe_slots_i8(int mode, const MoeHeader* __restrict__ hdr, const int32_t* __restrict__ slot_route, uint32_t top_k,
                                const float* __restrict__ src, const float* __restrict__ src2, uint32_t K, uint32_t n_slots,
                                uint8_t* __restrict__ out, uint32_t* __restrict__ status) {
-    const uint32_t chunk = blockIdx.x, slot = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const uint32_t chunk = blockIdx.y, slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (slot >= hdr->local_routes || slot >= n_slots) return;  // whole warps
     const uint32_t k0 = chunk * CHUNK_K + 8 * lane;
     const uint64_t row = mode == 0 ? uint64_t(uint32_t(slot_route[slot]) / top_k) : uint64_t(slot);
@@ -312,10 +312,10 @@ int32_t launch_nt(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, Grou
     constexpr size_t DYN = size_t(RING) * STAGE + 128;
     const uint32_t tiles = uint32_t((w0->rows + TILE_ROWS - 1) / TILE_ROWS);
     auto kern = k_moe_grouped_i8<NT, CW>;
-    static int cached_device = -1;
-    if (cached_device != ctx->device) {
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
         BHD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(DYN)), "raising the shared memory limit");
-        cached_device = ctx->device;
+        once.mark(ctx);
     }
     if (group_bound == 0) return BHD_OK;
     CUtensorMap m0, m1;
@@ -338,7 +338,7 @@ size_t bhd_moe_slots_i8_bytes(uint32_t K, uint32_t n_slots) {
 int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
                                 const float* src, const float* src2, uint32_t K, uint32_t n_slots, void* out, cudaStream_t s) {
     if (n_slots == 0) return BHD_OK;
-    k_moe_slots_i8<<<dim3((K + CHUNK_K - 1) / CHUNK_K, (n_slots + 3) / 4), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, top_k,
+    k_moe_slots_i8<<<dim3((n_slots + 3) / 4, (K + CHUNK_K - 1) / CHUNK_K), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, top_k,
                                                                                          src, src2, K, n_slots, static_cast<uint8_t*>(out),
                                                                                          ctx->status_dev);
     BHD_LAUNCHED(ctx, mode ? "expert gating kernel" : "token gather kernel");

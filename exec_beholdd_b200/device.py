@@ -26,9 +26,9 @@ ERR_UNSUPPORTED_FORMAT, ERR_SHAPE, ERR_ALLOCATION, ERR_BACKEND, ERR_INVALID_ARGU
 #: every symbol include/beholdd_b200.h declares
 EXPORTS = [
     "bhd_error_text", "bhd_last_error_message", "bhd_device_name", "bhd_ctx_create", "bhd_ctx_destroy", "bhd_supports",
-    "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_noalloc", "bhd_matvec_host",
+    "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_noalloc", "bhd_matvec_host", "bhd_matvec_host_async", "bhd_sync",
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
-    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count",
+    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf",
 ]
 
 
@@ -80,16 +80,20 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_matvec.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32, vp]
     lib.bhd_matvec_noalloc.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32, vp]
     lib.bhd_matvec_host.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32]
+    lib.bhd_matvec_host_async.argtypes = [vp, vp, u64, vp, vp, u32, f32, i32]
+    lib.bhd_sync.argtypes = [vp]
     lib.bhd_matmul.argtypes = [vp, vp, u64, vp, vp, u64, vp]
     lib.bhd_softmax.argtypes = [vp, vp, u64, u64, vp]
     lib.bhd_swiglu.argtypes = [vp, vp, vp, u64, f32, vp]
     lib.bhd_add_in_place.argtypes = [vp, vp, vp, u64, vp]
     lib.bhd_moe_route.argtypes = [vp, vp, vp, u64, u32, vp, vp, vp, vp, vp, vp]
-    lib.bhd_moe_experts.argtypes = [vp, vp, vp, vp, vp, u64, u32, vp, vp, u32, u32, vp, i32, vp]
+    lib.bhd_moe_experts.argtypes = [vp, vp, vp, vp, vp, u64, u32, vp, vp, u32, u32, u32, vp, i32, vp]
     lib.bhd_moe_combine.argtypes = [vp, vp, vp, u64, u32, u64, i32, vp]
     lib.bhd_moe_layer.argtypes = [vp, vp, vp, vp, vp, vp, vp, u64, u32, vp, vp, vp, i32, vp]
     lib.bhd_moe_layer_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, u64, u32, vp, vp, vp, i32]
     lib.bhd_check_status.argtypes = [vp, vp]
+    lib.bhd_debug_wait_test.argtypes = [vp, u32, u32]
+    lib.bhd_debug_expf.argtypes = [vp, vp, vp, u64, vp]
     lib.bhd_launch_count.restype = u64
     lib.bhd_launch_count.argtypes = [vp]
     return lib
@@ -291,6 +295,21 @@ class CudaDevice:
         self._check(self.lib.bhd_matvec_host(self.ctx, w.handle, slab, x.ctypes.data_as(C.c_void_p),
                                              y.ctypes.data_as(C.c_void_p), batch, scale, 1 if accumulate else 0))
 
+    def matvec_host_async(self, w: ResidentWeight, x: np.ndarray, y: np.ndarray, scale: float = 1.0,
+                          accumulate: bool = False, slab: int = 0) -> None:
+        """matvec_host_resident without the wait: queued on the context's own stream; `sync()` waits
+        (ExecutionDevice::submit / wait, execution.rs:1101-1114). A page-locked x must stay unchanged
+        until then."""
+        batch = 1 if x.ndim == 1 else x.shape[0]
+        if x.size != batch * w.cols or y.size != batch * w.rows:
+            raise ShapeError(ERR_SHAPE, f"shape mismatch: weight is {w.rows}x{w.cols}, got x={x.shape} y={y.shape}")
+        self._check(self.lib.bhd_matvec_host_async(self.ctx, w.handle, slab, x.ctypes.data_as(C.c_void_p),
+                                                   y.ctypes.data_as(C.c_void_p), batch, scale, 1 if accumulate else 0))
+
+    def sync(self) -> None:
+        """Wait for the queued host-buffer calls; raises if a kernel flagged a problem."""
+        self._check(self.lib.bhd_sync(self.ctx))
+
     def matmul_resident(self, w: ResidentWeight, x, y, slab: int = 0) -> None:
         """Prefill: y[m][n] = sum_k x[m][k] * W[n][k]."""
         m = x.shape[0]
@@ -304,12 +323,13 @@ class CudaDevice:
                                            _ptr(counts), _ptr(near), _ptr(probs), self._stream()))
 
     def moe_experts(self, gate: ResidentWeight, up: ResidentWeight, down: ResidentWeight, x, experts, weights, y,
-                    first_expert: int = 0, n_local: int | None = None, accumulate: bool = False) -> None:
+                    first_expert: int = 0, n_local: int | None = None, accumulate: bool = False, n_experts: int = 0) -> None:
+        """`n_experts`: the layer's expert count over all ranks (0 = not known to the caller)."""
         T, k = experts.shape
         n_local = gate.slabs if n_local is None else n_local
         self._check(self.lib.bhd_moe_experts(self.ctx, gate.handle, up.handle, down.handle, _ptr(x), T, k, _ptr(experts),
-                                             _ptr(weights), first_expert, n_local, _ptr(y), 1 if accumulate else 0,
-                                             self._stream()))
+                                             _ptr(weights), first_expert, n_local, n_experts, _ptr(y),
+                                             1 if accumulate else 0, self._stream()))
 
     def moe_combine(self, per_route, y, accumulate: bool = False) -> None:
         """per_route [k, T, dim] (rows pre-scaled by their route weights) summed in route order into y."""

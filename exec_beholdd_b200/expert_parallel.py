@@ -49,9 +49,47 @@ class ExpertParallelLayer:
         assert exchange in ("gather", "alltoall")
         self.exchange = exchange
         self.last_counts = None
+        self._marks = None  # (name, event) pairs of an instrumented forward
+
+    #: whether forward() can be captured into a CUDA graph (the NCCL exchanges here read split sizes on the host)
+    @property
+    def capturable(self) -> bool:
+        return self.world == 1
+
+    #: whether the result equals the single-GPU layer over the same global batch to the bit
+    @property
+    def bit_identical(self) -> bool:
+        return self.world == 1 or self.exchange == "alltoall"
+
+    def _mark(self, name):
+        if self._marks is not None:
+            import torch
+
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def timed_phases(self, x, y, repeats: int = 5):
+        """Device time of each phase of forward() in microseconds (median over a few eager runs;
+        the collectives are timed where the compute stream waits for them)."""
+        import statistics
+
+        import torch
+
+        runs = []
+        for _ in range(repeats + 1):
+            self._marks = []
+            self._mark("start")
+            self.forward(x, y)
+            self._mark("end")
+            torch.cuda.synchronize()
+            marks, self._marks = self._marks, None
+            runs.append({b[0]: a[1].elapsed_time(b[1]) * 1e3 for a, b in zip(marks[:-1], marks[1:])})
+        runs = runs[1:]  # the first run warms the allocator up
+        return {k: round(statistics.median(r[k] for r in runs), 1) for k in runs[0]}
 
     @classmethod
-    def from_synthetic(cls, dev, seed, n_experts, dim, ff, top_k, rank=0, world=1, group=None):
+    def from_synthetic(cls, dev, seed, n_experts, dim, ff, top_k, rank=0, world=1, group=None, exchange="gather"):
         """Seeded weights of the benchmark configuration; this rank uploads only its experts."""
         from . import synth
         from .device import Weight
@@ -70,7 +108,7 @@ class ExpertParallelLayer:
                    dev.upload_weight(Weight(local(21, ff, dim, gu_slab), 8, ff, dim), slabs=per),
                    dev.upload_weight(Weight(local(22, ff, dim, gu_slab), 8, ff, dim), slabs=per),
                    dev.upload_weight(Weight(local(23, dim, ff, d_slab), 8, dim, ff), slabs=per),
-                   n_experts, dim, ff, top_k, rank, world, group)
+                   n_experts, dim, ff, top_k, rank, world, group, exchange)
 
     def free(self):
         for w in (self.router, self.gate, self.up, self.down):
@@ -83,13 +121,13 @@ class ExpertParallelLayer:
     def _local_experts(self, rows, expert_ids, route_weights, out):
         """rows [R, dim] each with one (global) expert id and weight -> out[r] = w * down(silu(gate)*up)."""
         self.dev.moe_experts(self.gate, self.up, self.down, rows, expert_ids.view(-1, 1), route_weights.view(-1, 1), out,
-                             first_expert=self.rank * self.per, n_local=self.per)
+                             first_expert=self.rank * self.per, n_local=self.per, n_experts=self.n_experts)
 
     def _local_partial(self, x_all, experts_all, weights_all, out):
         """All positions of all ranks, only this rank's experts: out[t] = sum over the local
         routes of t, in selection order (routes of other ranks contribute nothing)."""
         self.dev.moe_experts(self.gate, self.up, self.down, x_all, experts_all, weights_all, out,
-                             first_expert=self.rank * self.per, n_local=self.per)
+                             first_expert=self.rank * self.per, n_local=self.per, n_experts=self.n_experts)
 
     def _combine(self, per_route, y, accumulate):
         """per_route [k, T, dim] -> y[t] (+)= ((0 + r[0][t]) + r[1][t]) + ... in route order."""
@@ -113,6 +151,7 @@ class ExpertParallelLayer:
 
         self._route(x, experts, weights, counts)
         self.last_counts = counts
+        self._mark("route")
         if self.exchange == "gather":
             return self._forward_gather(x, y, experts, weights, accumulate)
         _, order, send_counts = route_plan(experts, self.n_experts, self.world)
@@ -130,13 +169,16 @@ class ExpertParallelLayer:
         meta_recv = torch.empty((n_recv, 2), dtype=torch.int32, device=x.device)
         dist.all_to_all_single(rows_recv, rows_send, recv_list, send_list, group=self.group)
         dist.all_to_all_single(meta_recv, meta_send, recv_list, send_list, group=self.group)
+        self._mark("dispatch")
 
         out_recv = torch.empty((n_recv, self.dim), dtype=x.dtype, device=x.device)
         if n_recv:
             self._local_experts(rows_recv, meta_recv[:, 0].contiguous(), meta_recv[:, 1].contiguous().view(torch.float32),
                                 out_recv)
+        self._mark("experts")
         out_back = torch.empty((T * self.top_k, self.dim), dtype=x.dtype, device=x.device)
         dist.all_to_all_single(out_back, out_recv, send_list, recv_list, group=self.group)
+        self._mark("return")
 
         # Un-permute into route-major [k, T, dim], then add in selection order.
         j_of_route = order % self.top_k
@@ -144,6 +186,7 @@ class ExpertParallelLayer:
         per_route = torch.empty((self.top_k * T, self.dim), dtype=x.dtype, device=x.device)
         per_route.index_copy_(0, slot, out_back)
         self._combine(per_route.view(self.top_k, T, self.dim), y, accumulate)
+        self._mark("combine")
         return experts, weights
 
     def _forward_gather(self, x, y, experts, weights, accumulate):
@@ -164,8 +207,10 @@ class ExpertParallelLayer:
         dist.all_gather_into_tensor(meta_all, meta, group=self.group)
         experts_all = meta_all[:, : self.top_k].contiguous()
         weights_all = meta_all[:, self.top_k:].contiguous().view(torch.float32)
+        self._mark("all_gather")
         partial = torch.empty((W * T, self.dim), dtype=x.dtype, device=x.device)
         self._local_partial(x_all, experts_all, weights_all, partial)
+        self._mark("experts")
         mine = torch.empty((T, self.dim), dtype=x.dtype, device=x.device) if accumulate else y
         if dist.get_backend(self.group) == "gloo":  # gloo has no reduce-scatter
             dist.all_reduce(partial, group=self.group)
@@ -174,4 +219,5 @@ class ExpertParallelLayer:
             dist.reduce_scatter_tensor(mine, partial, group=self.group)
         if accumulate:
             y.add_(mine)
+        self._mark("reduce_scatter")
         return experts, weights

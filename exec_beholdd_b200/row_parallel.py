@@ -46,6 +46,13 @@ class RowSplitLinear:
         self.rows, self.cols, self.rank, self.world, self.group = rows, cols, rank, world, group
         self.per = rows // world
 
+    #: how the slices of y travel, and whether forward() can be captured into a CUDA graph
+    exchange = "all_gather (NCCL)"
+
+    @property
+    def capturable(self) -> bool:
+        return self.world == 1
+
     @classmethod
     def from_host(cls, dev, packed: np.ndarray, kind: int, rows: int, cols: int, rank: int = 0, world: int = 1, group=None):
         """Upload only this rank's rows of a host-resident packed weight."""

@@ -47,6 +47,13 @@ extern "C" {
 #define BHD_TYPE_Q6_K 14u
 
 typedef struct bhd_ctx bhd_ctx;       /* one per GPU; owns the stream-ordered workspace */
+/* Device and workspace rules of a context:
+ *  - Every call makes the context's GPU the calling thread's current device while it runs and
+ *    restores the caller's device before it returns; the caller's current device need not match.
+ *  - The workspace grows on demand (first call of a larger size): growing synchronises the device,
+ *    frees the old block and allocates a new one. A CUDA graph captured earlier keeps the old
+ *    block's addresses, so capture only after one eager call of the largest shape, and never
+ *    during a capture call a shape larger than any eager call before it. */
 typedef struct bhd_weight bhd_weight; /* a packed weight resident in HBM */
 
 /* Static text for a status code (like exec_hag_error_text). */
@@ -105,8 +112,24 @@ int32_t bhd_matvec(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const 
 int32_t bhd_matvec_host(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_host, float* y_host,
                         uint32_t batch, float scale, int32_t accumulate);
 
-/* No counterpart in the reference. A decode matvec (same operation and results as bhd_matvec,
- * batch <= 4) for hosts that may not allocate device memory once they are serving: real-time
+/* bhd_matvec_host without the wait: the copies and the kernel are queued on the context's own
+ * (non-blocking) stream and the call returns. Results are in y_host, and problems the kernels
+ * flagged are reported, once bhd_sync has returned. A page-locked x_host is read by the GPU
+ * when the queued work runs, so it must stay unchanged until then; a pageable x_host is copied
+ * before the call returns. Calls are executed in the order they were made. This is the shape of
+ * ExecutionDevice::submit / wait (crates/beholdd-backend/src/execution.rs:1101-1114) for a single
+ * Linear command on host-visible buffers. */
+int32_t bhd_matvec_host_async(bhd_ctx* ctx, const bhd_weight* weight, uint64_t slab, const float* x_host,
+                              float* y_host, uint32_t batch, float scale, int32_t accumulate);
+
+/* Waits for everything the host-buffer entry points queued on this context
+ * (ExecutionDevice::wait, execution.rs:1111-1114) and returns BHD_ERR_DEVICE_STATUS if a kernel
+ * flagged a problem (the word is cleared). */
+int32_t bhd_sync(bhd_ctx* ctx);
+
+/* No counterpart in the reference. A decode matvec (the operation of bhd_matvec for batch <= 4;
+ * results agree with it within the path's tolerance, not to the bit, because bhd_matvec may pick
+ * a different kernel for the same shape) for hosts that may not allocate device memory once they are serving: real-time
  * decode loops that cannot take the allocator's locks or implicit synchronisation, processes
  * that gave all of HBM to their own arena at start-up. Its scratch (the packed fp16
  * activations) is a fixed 288 KiB array inside the library image, held by every GPU that loads
@@ -158,12 +181,14 @@ int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const float* x_dev
  * Only experts e with first_expert <= e < first_expert + n_local are applied (the others
  * contribute nothing), which is what one rank of an expert-parallel group computes; the
  * slabs of `gate/up/down` are then the local experts only. With first_expert = 0 and
- * n_local = n_experts this is the whole layer.
+ * n_local = n_experts this is the whole layer. `n_experts` is the layer's expert count over all
+ * ranks: an id outside [0, n_experts) is reported through the status word (pass 0 if unknown; only
+ * negative ids can then be told from another rank's).
  *   accumulate == 0: y[t] = out[t];  accumulate != 0: y[t] += out[t]  (forward.rs:1405-1407) */
 int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps,
                         const bhd_weight* down_exps, const float* x_dev, uint64_t n_positions, uint32_t top_k,
                         const int32_t* experts_dev, const float* weights_dev, uint32_t first_expert,
-                        uint32_t n_local, float* y_dev, int32_t accumulate, void* stream);
+                        uint32_t n_local, uint32_t n_experts, float* y_dev, int32_t accumulate, void* stream);
 
 /* Weighted combine of per-route outputs (forward.rs:1385-1398; cpu.rs:280-284): per_route is
  * [top_k][T][dim], each row already scaled by its route weight; for every position the rows
@@ -193,6 +218,21 @@ int32_t bhd_moe_layer_host(bhd_ctx* ctx, const bhd_weight* router, const bhd_wei
  * BHD_ERR_DEVICE_STATUS with the detail in bhd_last_error_message (NaN fed to softmax,
  * an out-of-range expert id, a bounded wait that gave up). Clears the word. */
 int32_t bhd_check_status(bhd_ctx* ctx, void* stream);
+
+/* Test hook, no counterpart in the reference. Every wait inside the kernels is bounded; this lets a
+ * test watch one run out without any fault: `spin_limit` (0 = default) replaces the number of polls
+ * the single-vector decode matvec makes before it gives up, and a non-zero `drop_one_copy` makes the
+ * next such matvec leave one weight copy unrequested, so that one warp's wait cannot complete. The
+ * kernel then sets the status word, lets the copies it did request land, and returns normally
+ * (the rows of that warp's tile are wrong, which is why the status word is set); the context
+ * stays usable. bhd_check_status reports BHD_ERR_DEVICE_STATUS once. */
+int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one_copy);
+
+/* Test hook, no counterpart in the reference: out[i] = the library's expf(in[i]), the function the
+ * router softmax uses on the device. The reference calls the host libm (Rust f32::exp,
+ * crates/beholdd-kernel/src/vecops.rs:70-87); expert selection is the CPU's only if both give
+ * the same floats, which a test checks over a sweep of arguments. */
+int32_t bhd_debug_expf(bhd_ctx* ctx, const float* in_dev, float* out_dev, uint64_t n, void* stream);
 
 /* How many kernels this library has launched on the context since it was created. */
 uint64_t bhd_launch_count(const bhd_ctx* ctx);

@@ -569,4 +569,10 @@ int32_t orc_moe_layer(const float* router, const uint8_t* gate_exps, const uint8
     return ORC_OK;
 }
 
+// The host libm's expf over an array: what the reference's softmax and SiLU call through Rust's
+// f32::exp (crates/beholdd-kernel/src/vecops.rs:70-93). Lets a test compare the device's expf with it.
+void orc_expf_array(const float* in, float* out, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) out[i] = expf(in[i]);
+}
+
 }  // extern "C"

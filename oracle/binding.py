@@ -69,6 +69,8 @@ class Oracle:
         L.orc_serial_matvec.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_uint8), C.c_uint64,
                                         C.c_uint32, C.c_uint64, C.c_uint64]
         L.orc_softmax.argtypes = [C.POINTER(C.c_float), C.c_uint64]
+        L.orc_expf_array.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64]
+        L.orc_expf_array.restype = None
         L.orc_swiglu.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64, C.c_float]
         L.orc_rmsnorm.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64, C.c_float]
         L.orc_stable_top_k.argtypes = [C.POINTER(C.c_float), C.c_uint64, C.c_uint64, C.POINTER(C.c_int32),
@@ -153,6 +155,13 @@ class Oracle:
         if st != OK:
             raise OracleError(st)
         return v
+
+    def expf(self, v) -> np.ndarray:
+        """The host libm's expf, element by element."""
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        out = np.empty_like(v)
+        self.lib.orc_expf_array(_f32(v), _f32(out), v.size)
+        return out
 
     def swiglu(self, gate, up, limit=0.0) -> np.ndarray:
         g = np.array(gate, dtype=np.float32)

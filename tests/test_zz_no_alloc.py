@@ -3,10 +3,13 @@
 Collected last on purpose (file name), so a run that stops at the first failure has already
 run everything else. The entry point exists for hosts that must not allocate device memory
 while serving (real-time decode loops, processes that handed all of HBM to their own arena):
-its scratch is a fixed array inside the library instead of the context workspace. Same kernels,
-so the results must agree with bhd_matvec to the bit; the check allows the path's stated
-tolerance. Two calls in a row with different inputs show that nothing of the first call's
-scratch contents survives into the second.
+its scratch is a fixed array inside the library instead of the context workspace. bhd_matvec may
+pick a different kernel for the same shape (the integer one for one or two vectors), so the two
+agree within the path's stated tolerance, not to the bit; both are also held against the CPU
+oracle. Two calls in a row with different inputs show that nothing of the first call's scratch
+contents survives into the second. The first call runs on a context that has done nothing else,
+and the free device memory the driver reports must be the same before and after it: the entry
+point may not allocate.
 """
 import ctypes as C
 
@@ -26,7 +29,7 @@ def max_rel_err(got, want):
 
 
 @pytest.mark.parametrize("kind,rows,cols,batch", [(12, 1536, 4096, 1), (8, 768, 2048, 2), (14, 512, 4096, 4), (8, 64, 1024, 3)])
-def test_noalloc_matvec_matches_the_allocating_entry_point_twice_in_a_row(kind, rows, cols, batch):
+def test_noalloc_matvec_matches_the_allocating_entry_point_twice_in_a_row(oracle, kind, rows, cols, batch):
     import torch
 
     if not torch.cuda.is_available():
@@ -34,18 +37,32 @@ def test_noalloc_matvec_matches_the_allocating_entry_point_twice_in_a_row(kind, 
     from exec_beholdd_b200 import CudaDevice, Weight, synth
 
     dev = CudaDevice(0)
-    w = dev.upload_weight(Weight(synth.matrix(kind, 61, rows, cols), kind, rows, cols))
+    packed = synth.matrix(kind, 61, rows, cols)
+    w = dev.upload_weight(Weight(packed, kind, rows, cols))
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # Load the library's device code first (the driver loads a module lazily, on its first launch, and that
+    # takes device memory) with a call that needs no workspace, so that the measurement below sees only
+    # what the entry point itself does.
+    probe = torch.zeros(8, device="cuda")
+    assert dev.lib.bhd_debug_expf(dev.ctx, C.c_void_p(probe.data_ptr()), C.c_void_p(probe.data_ptr()), 8, stream) == 0
     for call in range(2):
-        x = torch.from_numpy(synth.activations(70 + call, (batch, cols))).cuda()
-        want = torch.empty((batch, rows), device="cuda")
-        dev.matvec_resident(w, x, want)
+        x_np = synth.activations(70 + call, (batch, cols))
+        x = torch.from_numpy(x_np).cuda()
         got = torch.full((batch, rows), float("nan"), device="cuda")
+        want = torch.empty((batch, rows), device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        # first thing this context ever runs (call 0): its workspace does not exist yet
         st = dev.lib.bhd_matvec_noalloc(dev.ctx, w.handle, 0, C.c_void_p(x.data_ptr()), C.c_void_p(got.data_ptr()), batch,
                                         1.0, 0, stream)
         assert st == 0, dev._message()
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free entry point changed the free device memory"
+        dev.check_status()
+        dev.matvec_resident(w, x, want)
         dev.check_status()
         assert max_rel_err(got.cpu().numpy(), want.cpu().numpy()) <= TOL, f"call {call}"
+        assert max_rel_err(got.cpu().numpy(), oracle.matvec_batch(packed, kind, rows, cols, x_np)) <= TOL, f"call {call} vs oracle"
         # scaled accumulate form
         acc = torch.ones((batch, rows), device="cuda")
         st = dev.lib.bhd_matvec_noalloc(dev.ctx, w.handle, 0, C.c_void_p(x.data_ptr()), C.c_void_p(acc.data_ptr()), batch,
