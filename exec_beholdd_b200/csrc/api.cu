@@ -509,6 +509,14 @@ int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one
     return BHD_OK;
 }
 
+int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value) {
+    if (!valid_ctx(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    switch (key) {
+        case BHD_OPTION_MOE_TC_MIN_CLASS: ctx->moe_tc_min_cls = value; return BHD_OK;
+        default: return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "debug_option: unknown key %u", key);
+    }
+}
+
 uint64_t bhd_launch_count(const bhd_ctx* ctx) { return valid_ctx(ctx) ? ctx->launches : 0; }
 
 }  // extern "C"

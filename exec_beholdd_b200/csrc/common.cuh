@@ -39,6 +39,7 @@ struct bhd_ctx {
     cudaStream_t host_stream;  // non-blocking stream of the host-buffer entry points
     uint32_t spin_limit;    // polls a bounded wait makes before it gives up (0: the kernel's default)
     uint32_t debug_drop;    // test hook: the next decode matvec leaves this many copies unrequested
+    uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
 };
@@ -207,13 +208,20 @@ __device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q6_K>(const uint8_t* r
         default: break;                                  \
     }
 
-// ---- routed-expert plan records (written by k_moe_plan, read by the grouped kernels) ------
+// ---- routed-expert plan records (written by the plan kernels, read by the grouped kernels) ------
+// Routes are sorted by (expert, route index) into "slots"; an expert's slots are cut into groups of at
+// most `cap` routes and every group belongs to the size class of its route count.
+constexpr int BHD_MOE_CLASSES = 7;  // groups of up to 4, 8, 16, 32, 64, 128, 256 routes
+__host__ __device__ constexpr int bhd_moe_cls(int nb) {
+    return nb <= 4 ? 0 : (nb <= 8 ? 1 : (nb <= 16 ? 2 : (nb <= 32 ? 3 : (nb <= 64 ? 4 : (nb <= 128 ? 5 : 6)))));
+}
+__host__ __device__ constexpr uint32_t bhd_moe_cls_least(int cls) { return cls == 0 ? 1u : (4u << (cls - 1)) + 1u; }  // 1, 5, 9, 17, 33, 65, 129
 struct MoeGroup {
     int32_t expert_local, slot0, nb, cls;
     uint32_t pad0, pad1, pad2, pad3;
 };
 struct MoeHeader {
-    uint32_t gcount[4];
+    uint32_t gcount[8];  // groups per size class
     uint32_t total_groups, local_routes, pad0, pad1;
 };
 
@@ -226,9 +234,33 @@ int32_t bhd_launch_matvec_general(bhd_ctx* ctx, const bhd_weight* w, uint64_t sl
 int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
                                   const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* xq, uint32_t n_slots,
                                   float* out0, float* out1, const float* slot_weight, cudaStream_t s);
-int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
-                                const float* src, const float* src2, uint32_t K, uint32_t n_slots, void* out, cudaStream_t s);
+int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, const uint8_t* slot_cls,
+                                uint32_t max_cls, uint32_t top_k, const float* src, const float* src2, uint32_t K, uint32_t n_slots,
+                                void* out, cudaStream_t s);
+int32_t bhd_launch_moe_rows_f16(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, const uint8_t* slot_cls,
+                                uint32_t min_cls, uint32_t top_k, const float* src, const float* src2, uint32_t K, uint32_t n_slots,
+                                void* out16, const float* slot_weight, float* scale_out, cudaStream_t s);
+int32_t bhd_launch_gemm_q8_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
+                                   const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* x16, uint32_t n_slots,
+                                   float* out0, float* out1, const float* col_scale, cudaStream_t s);
+bool bhd_gemm_q8_grouped_usable(const bhd_ctx* ctx, const bhd_weight* w);
 int32_t bhd_launch_stage_copy(bhd_ctx* ctx, const float* src_mapped, float* dst_dev, size_t n16, cudaStream_t s);
 size_t bhd_moe_slots_i8_bytes(uint32_t K, uint32_t n_slots);
+// Sorts the routes of the local experts by (expert, route index) and lists the groups: see moe_plan.cu.
+struct MoePlanBuffers {
+    MoeHeader* hdr;
+    uint32_t *counts, *offsets;     // [n_local], [n_local + 1]
+    int32_t *route_slot;            // [routes]: slot of a local route, -1 for a route of another rank
+    int32_t *slot_route;            // [routes]: route of a slot
+    float* slot_weight;             // [routes]: route weight of a slot
+    uint8_t* slot_cls;              // [routes]: size class of the group the slot belongs to
+    MoeGroup* groups;               // [gmax]
+    int32_t* glist;                 // [BHD_MOE_CLASSES][gmax]: group indices per class, in expert order
+    uint32_t* whist;                // [route blocks * 8][n_local] scratch
+    uint32_t gmax;
+};
+size_t bhd_moe_plan_scratch_words(uint32_t n_routes, uint32_t n_local);
+int32_t bhd_launch_moe_plan(bhd_ctx* ctx, const int32_t* experts, const float* weights, uint32_t n_routes, uint32_t first_expert,
+                            uint32_t n_local, uint32_t n_total, uint32_t cap, const MoePlanBuffers& b, cudaStream_t s);
 bool bhd_moe_i8_usable(const bhd_weight* w);
 

@@ -80,6 +80,11 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
     return v;
 }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -147,20 +152,43 @@ __global__ void k_f32_to_f16(const float* __restrict__ x, __half* __restrict__ o
 constexpr int PLAIN_NG = 2;  // converter groups: one cannot feed two MMA issuers
 
 struct GemmParams {
-    float* y;            // [M x N]
+    float* y;            // [M x N]; grouped: [slot][N] of matrix 0
+    float* y1;           // grouped: [slot][N] of matrix 1 (blockIdx.z == 1), or null
     uint32_t* status;
-    uint32_t n_rows;     // N: weight rows of the slab
-    uint32_t row_base;   // tensor-map row of the slab's first row
-    uint32_t m;          // tokens
+    uint32_t n_rows;     // N: weight rows of one slab
+    uint32_t row_base;   // tensor-map row of the slab's first row (dense mode)
+    uint32_t m;          // tokens (dense mode)
     uint32_t k;          // columns
-    uint32_t tn;         // tokens per tile: 64, 128 or 256
+    uint32_t tn;         // tokens per tile: 32, 64, 128 or 256
     uint32_t stages;     // fp16 stages in the ring
+    // Grouped mode (groups != null): blockIdx.y walks the groups of one size class; a group is `nb`
+    // consecutive rows of the activation array (slots slot0 .. slot0 + nb) against the slab of its expert.
+    const MoeHeader* hdr;
+    const MoeGroup* groups;
+    const int32_t* glist;
+    uint32_t cls;
+    const float* col_scale;  // optional factor per activation row, applied to its outputs
 };
 
 template <int NG>
 __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const __grid_constant__ CUtensorMap tmap_w0,
+                                                                const __grid_constant__ CUtensorMap tmap_w1,
                                                                 const __grid_constant__ CUtensorMap tmap_x,
                                                                 const GemmParams p) {
+    // Which tokens and which slab this CTA works on. A CTA beyond the class's group count leaves at once
+    // (the whole CTA, before any barrier or tensor memory exists).
+    uint32_t m0, m_end, row_base;
+    if (p.groups) {
+        if (blockIdx.y >= p.hdr->gcount[p.cls]) return;
+        const MoeGroup grp = p.groups[p.glist[blockIdx.y]];
+        m0 = uint32_t(grp.slot0);
+        m_end = m0 + uint32_t(grp.nb);
+        row_base = uint32_t(grp.expert_local) * p.n_rows;
+    } else {
+        m0 = blockIdx.y * p.tn;
+        m_end = p.m;
+        row_base = p.row_base;
+    }
     extern __shared__ uint8_t smem_raw[];
     // st_empty[s][k & 1]: the MMAs of the k-th use of stage s have finished reading it. Two barriers per
     // stage, alternating by use, because a converter group sees only every other use of a stage and the two
@@ -179,9 +207,8 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
     const uint32_t pack_addr = smem0, stage_addr = smem0 + 2 * PACK_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int XW = 2 + 4 * NG, MW = 3 + 4 * NG;  // activation-tile producer warp, second MMA issuer warp
-    const uint32_t m0 = blockIdx.y * p.tn, m_end = p.m, row_base = p.row_base;
-    const CUtensorMap* tmap_w = &tmap_w0;
-    float* const yout = p.y;
+    const CUtensorMap* tmap_w = blockIdx.z ? &tmap_w1 : &tmap_w0;
+    float* const yout = blockIdx.z ? p.y1 : p.y;
     const uint32_t n0 = blockIdx.x * TILE_N;
     const uint32_t slices = (p.k + SLICE_K - 1) / SLICE_K, chunks = (p.k + CHUNK_K - 1) / CHUNK_K;
     const uint32_t S = p.stages;
@@ -268,15 +295,24 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
             const uint32_t pb = c & 1;
             if (aborted() || !mbar_wait(&pk_full[pb], (c >> 1) & 1)) { give_up(); ok = false; break; }
             const uint32_t src_row = pack_addr + pb * PACK_BYTES + row * PACK_ROW;
-            for (uint32_t kb = grp; kb < 4; kb += NG) {
+#pragma unroll
+            for (uint32_t kb = 0; kb < 4; ++kb) {  // unrolled so that the register indices below are constants
+                if (kb % NG != grp) continue;      // uniform per warp
                 const uint32_t it = c * 4 + kb;
                 if (it >= slices) break;
                 const uint32_t s = it % S;
                 if (!stage_free(it)) { give_up(); ok = false; break; }
-                // Two Q8_0 blocks = 68 bytes = 17 aligned words: [d0 | q0..q31 | d1 | q32..q63].
-                uint32_t w[17];
+                // Two Q8_0 blocks = 68 bytes = 17 words [d0 | q0..q31 | d1 | q32..q63], starting at word 17 * kb of
+                // the row. Read as five aligned 16-byte loads from word 16 * kb: rows are 272 bytes apart, so the
+                // eight lanes of a quarter-warp hit eight different 16-byte bank groups (no conflicts), and the
+                // slice's words are v[kb .. kb + 16].
+                uint32_t v[20];
 #pragma unroll
-                for (int i = 0; i < 17; ++i) w[i] = lds32(src_row + kb * 68 + 4 * i);
+                for (int i = 0; i < 5; ++i) {
+                    const uint4 q4 = lds128(src_row + kb * 64 + 16 * i);
+                    v[4 * i] = q4.x; v[4 * i + 1] = q4.y; v[4 * i + 2] = q4.z; v[4 * i + 3] = q4.w;
+                }
+                const uint32_t* w = v + kb;
                 const uint32_t a_dst = stage_addr + s * stage_bytes + a_row_off;
                 const __half2 off = __half2half2(__ushort_as_half(uint16_t(0x6480)));  // 1152
 #pragma unroll
@@ -335,7 +371,8 @@ __global__ void __launch_bounds__(gemm_threads(NG), 1) k_gemm_q8_tcgen05(const _
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t m = m0 + col + j;
                         if (m < m_end) {
-                            yout[uint64_t(m) * p.n_rows + n] = __uint_as_float(r[j]);
+                            const float sc = p.col_scale ? p.col_scale[m] : 1.0f;
+                            yout[uint64_t(m) * p.n_rows + n] = __fmul_rn(__uint_as_float(r[j]), sc);
                         }
                     }
                 }
@@ -356,6 +393,73 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
+
+// Grouped form for the routed experts: every group of size class `cls` (17 or more routes of one expert,
+// consecutive rows of the fp16 activation array x16 [n_slots x K]) against its expert's slab of w0 (and
+// of w1 for blockIdx.z == 1): out[slot][row] = col_scale[slot] * sum_k x16[slot][k] * W[expert][row][k].
+// `group_bound` is an upper bound of the class's group count (the grid's y extent); tn = the class's
+// largest group, 32 to 256 tokens per tile.
+int32_t bhd_launch_gemm_q8_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
+                                   const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* x16, uint32_t n_slots,
+                                   float* out0, float* out1, const float* col_scale, cudaStream_t s) {
+    if (group_bound == 0) return BHD_OK;
+    const uint32_t K = uint32_t(w0->cols), N = uint32_t(w0->rows);
+    const uint32_t tn = 4u << cls;  // classes 3..6 -> 32, 64, 128, 256
+    if (cls < 3 || cls > 6) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "grouped matmul: size class %u has no tensor-core form", cls);
+    // Two stages leave room for two CTAs per SM at the narrow tiles, where the kernel is bound by weight traffic
+    // and a second CTA covers the first one's start-up and drain; the wide tiles keep deeper rings.
+    const uint32_t stages = tn == 256 ? 3u : (tn <= 32 ? 2u : 4u);
+    const size_t dyn = 1024 + 2 * size_t(PACK_BYTES) + size_t(stages) * (A_BYTES + tn * 128u);
+    EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode);
+    CUtensorMap map_w[2], map_x;
+    for (int i = 0; i < 2; ++i) {
+        const bhd_weight* w = (i == 1 && w1) ? w1 : w0;
+        const cuuint64_t dims[2] = {w->row_bytes / 2, w->rows * w->slabs};
+        const cuuint64_t strides[1] = {w->row_bytes};
+        const cuuint32_t box[2] = {PACK_ROW / 2, TILE_N};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->dev, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the expert tensor map", bhd_device_name());
+    }
+    {
+        const cuuint64_t dims[2] = {K, n_slots};
+        const cuuint64_t strides[1] = {uint64_t(K) * 2};
+        const cuuint32_t box[2] = {SLICE_K, tn};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return bhd_fail(ctx, BHD_ERR_BACKEND, "%s backend error: cannot encode the activation tensor map", bhd_device_name());
+    }
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_tcgen05<PLAIN_NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
+                 "raising the shared memory limit");
+        once.mark(ctx);
+    }
+    GemmParams p = {};
+    p.y = out0;
+    p.y1 = out1;
+    p.status = ctx->status_dev;
+    p.n_rows = N;
+    p.k = K;
+    p.tn = tn;
+    p.stages = stages;
+    p.hdr = static_cast<const MoeHeader*>(hdr);
+    p.groups = static_cast<const MoeGroup*>(groups);
+    p.glist = glist;
+    p.cls = cls;
+    p.col_scale = col_scale;
+    k_gemm_q8_tcgen05<PLAIN_NG><<<dim3((N + TILE_N - 1) / TILE_N, group_bound, w1 ? 2 : 1), gemm_threads(PLAIN_NG), dyn, s>>>(
+        map_w[0], map_w[1], map_x, p);
+    BHD_LAUNCHED(ctx, "tcgen05 grouped expert kernel");
+    return BHD_OK;
+}
+
+bool bhd_gemm_q8_grouped_usable(const bhd_ctx* ctx, const bhd_weight* w) {
+    return ctx->tmap_encode && w->kind == BHD_TYPE_Q8_0 && w->row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(w->dev) & 15) == 0 &&
+           w->cols % 32 == 0 && w->cols != 0 && w->rows * w->slabs <= 0x7fffffffull;
+}
 
 // Tensor-core path of bhd_matmul: Q8_0 weights, M >= 64 tokens. Sets *handled = false when the
 // shape does not qualify (the caller then uses the batched matvec kernels).
@@ -405,7 +509,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
                  "raising the shared memory limit");
         once.mark(ctx);
     }
-    GemmParams p;
+    GemmParams p = {};
     p.y = y;
     p.status = ctx->status_dev;
     p.n_rows = N;
@@ -414,7 +518,7 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     p.k = K;
     p.tn = tn;
     p.stages = stages;
-    k_gemm_q8_tcgen05<PLAIN_NG><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), gemm_threads(PLAIN_NG), dyn, s>>>(map_w, map_x, p);
+    k_gemm_q8_tcgen05<PLAIN_NG><<<dim3((N + TILE_N - 1) / TILE_N, (M + tn - 1) / tn), gemm_threads(PLAIN_NG), dyn, s>>>(map_w, map_w, map_x, p);
     BHD_LAUNCHED(ctx, "tcgen05 matmul kernel");
     *handled = true;
     return BHD_OK;

@@ -8,11 +8,11 @@
 //     conversion to a floating-point bit pattern and no constant offset to undo, and one
 //     instruction covers 32 columns instead of 16 -- about half the issue slots per byte of
 //     the fp16 variant, which was issue-bound.
-//   * Activations are block floating point: per scale group (32 columns, 16 for Q6_K) a power
-//     of two 2^e and a 15-bit integer X = round(x * 2^(14 - e)) split into two signed bytes,
+//   * Activations are block-scaled integers: per scale group (32 columns, 16 for Q6_K) a factor
+//     s = max|x| / 32639 and a 16-bit integer X = round(x / s) split into two signed bytes,
 //     X = 256 * d0 + d1. The two digits sit in adjacent MMA columns; the s32 accumulators are
-//     combined exactly (256 * c0 + c1) and scaled by 2^(e - 14) and the block scale in f32.
-//     Relative error 2^-15 of the largest activation of the group; any finite f32 is accepted.
+//     combined exactly (256 * c0 + c1) and scaled by s and the block scale in f32.
+//     Relative error 2^-16 of the largest activation of the group; any finite f32 is accepted.
 //
 // Reference semantics: crates/beholdd-backend/src/cpu.rs:398-507; block formats:
 // crates/beholdd-kernel/src/kquant.rs:29-241.
@@ -40,7 +40,7 @@ __host__ __device__ constexpr int cluster_of(uint32_t kind, int nb) { return (ki
 __host__ __device__ constexpr int igroups(uint32_t kind) { return kind == BHD_TYPE_Q6_K ? 16 : 8; }
 
 // Packed activations of one chunk: [group][vector][digit][t] 8-byte B fragments (b0, b1), then
-// [group][vector] f32 pairs (2^(e-14), sum of the dequantised activations of the group).
+// [group][vector] f32 pairs (the group's factor s, sum of the dequantised activations of the group).
 __host__ __device__ constexpr int iblob_frag_bytes(uint32_t kind, int nb) { return igroups(kind) * nb * 64; }
 __host__ __device__ constexpr int iblob_bytes(uint32_t kind, int nb) {
     return (iblob_frag_bytes(kind, nb) + igroups(kind) * nb * 8 + 127) / 128 * 128;
@@ -207,18 +207,18 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
         if (bad) atomicOr(status, BHD_DEV_ACTIVATION_RANGE);
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        // mx = m * 2^ex with m in [0.5, 1): ex = biased exponent - 126. Groups whose largest
-        // magnitude is below 2^-100 (denormals included) pack as zero.
-        const int eb = int(__float_as_uint(mx) >> 23);
-        const bool tiny = eb < 27;
-        const float up = tiny ? 0.f : __uint_as_float(uint32_t(267 - eb) << 23);    // 2^(14 - ex)
-        const float down = tiny ? 0.f : __uint_as_float(uint32_t(eb - 13) << 23);   // 2^(ex - 14)
+        // The group's largest magnitude maps to 32639 = 127 * 256 + 127, the largest integer whose two balanced
+        // digits both fit a signed byte, so the full 16-bit range is used whatever the magnitude. Groups whose
+        // largest magnitude is below 2^-100 (denormals included) pack as zero.
+        const bool tiny = (__float_as_uint(mx) >> 23) < 27u;
+        const float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
+        const float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
         uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};  // digit 0 / digit 1 words for b0, b1
         int sumX = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const int X = __float2int_rn(val[i] * up);          // |X| <= 2^14
-            const int d0 = (X + 128) >> 8, d1 = X - d0 * 256;   // X = 256 * d0 + d1, both in [-128, 127]
+            const int X = __float2int_rn(val[i] * up);          // |X| <= 32639
+            const int d0 = (X + 128) >> 8, d1 = X - d0 * 256;   // X = 256 * d0 + d1, d0 in [-127, 127], d1 in [-128, 127]
             w0[i >> 2] |= (uint32_t(d0) & 0xffu) << (8 * (i & 3));
             w1[i >> 2] |= (uint32_t(d1) & 0xffu) << (8 * (i & 3));
             sumX += X;
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
 
     // The lane's share of a chunk's packed activations, from the shared memory of the CTA that
     // packed it: the B fragments of the TILES groups its MMA column stands for, and
-    // (2^(e-14), sum) of the TILES groups its accumulator columns stand for. Loaded one chunk ahead.
+    // (factor, sum) of the TILES groups its accumulator columns stand for. Loaded one chunk ahead.
     uint2 bq[TILES], bq_next[TILES];
     float2 mq[TILES], mq_next[TILES];
     const uint32_t xs32 = smem_u32(xs);

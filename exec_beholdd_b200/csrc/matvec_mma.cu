@@ -527,144 +527,10 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
 }
 
 // ---- grouped experts (qwen3moe routed block) ---------------------------------------------------
-// Routes are sorted by expert; every expert's routes are cut into groups of up to 32 and each
-// (group, row tile) of an expert matrix is one CTA of the integer grouped kernel
-// (moe_grouped_i8.cu) streaming all columns. The size class of a group (up to 4 / 8 / 16 / 32
-// routes) picks the kernel instance.
-
-__host__ __device__ constexpr int moe_cls(int nb) { return nb <= 4 ? 0 : (nb <= 8 ? 1 : (nb <= 16 ? 2 : 3)); }
-
-// One CTA. Sorts the local routes by (expert, route index) -- a stable counting sort through a
-// route bitmap per expert, so the order is deterministic -- and lists the groups.
-__global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ experts, const float* __restrict__ weights,
-                                                   uint32_t n_routes, uint32_t first_expert, uint32_t n_local,
-                                                   uint32_t n_total, MoeHeader* hdr,
-                                                   uint32_t* counts, uint32_t* offsets, int32_t* route_slot,
-                                                   int32_t* slot_route, float* slot_weight, MoeGroup* groups,
-                                                   int32_t* glist, uint32_t gmax, uint32_t* bitmap, uint32_t* prefix,
-                                                   uint32_t* status, int use_smem) {
-    __shared__ uint32_t s_counts[1024], s_offsets[1025];
-    extern __shared__ uint32_t s_dyn[];
-    const uint32_t words = (n_routes + 31) / 32;
-    if (use_smem) {  // small problems keep the bitmap and its prefix on chip
-        bitmap = s_dyn;
-        prefix = s_dyn + n_local * words;
-    }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    for (uint32_t i = threadIdx.x; i < n_local * words; i += blockDim.x) bitmap[i] = 0u;
-    __syncthreads();
-    for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
-        const int32_t e = experts[r];
-        if (e < 0 || uint32_t(e) >= n_total) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);  // ids of other ranks are skipped, ids of no rank reported
-        if (e >= int32_t(first_expert) && uint32_t(e) < first_expert + n_local)
-            atomicOr(&bitmap[(uint32_t(e) - first_expert) * words + (r >> 5)], 1u << (r & 31));
-        else
-            route_slot[r] = -1;
-    }
-    __syncthreads();
-    // One warp per expert: exclusive prefix of the set bits over the expert's bitmap words.
-    for (uint32_t e = warp; e < n_local; e += n_warps) {
-        uint32_t run = 0;
-        for (uint32_t w0 = 0; w0 < words; w0 += 32) {
-            const uint32_t w = w0 + lane;
-            const uint32_t c = w < words ? __popc(bitmap[e * words + w]) : 0u;
-            uint32_t incl = c;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const uint32_t o = __shfl_up_sync(0xffffffffu, incl, d);
-                if (lane >= d) incl += o;
-            }
-            if (w < words) prefix[e * words + w] = run + incl - c;
-            run += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (lane == 0) s_counts[e] = run;
-    }
-    __syncthreads();
-    // Groups of up to 32 routes per expert, in expert order. Thread e describes expert e's groups
-    // (n / 32 full ones and a remainder); a block-wide exclusive scan of six per-expert totals
-    // (routes, groups, groups per size class) gives every expert its first slot, first group
-    // index and first index in each class list,
-    // so the lists come out exactly as a sequential walk over the experts would write them.
-    // Requires n_local <= blockDim.x.
-    {
-        __shared__ uint32_t s_warp[32][6];
-        const uint32_t e = threadIdx.x;
-        // An expert with more than 32 routes is cut into ceil(n / 32) groups of equal size (+-1),
-        // `big` of them one route larger: equal sizes fall into the same size class, so the
-        // groups of one expert run in the same launch, next to each other, and share its weights
-        // through L2 instead of reading them from HBM once per launch.
-        const uint32_t n = e < n_local ? s_counts[e] : 0u;
-        const uint32_t parts = (n + 31) / 32, small_nb = parts ? n / parts : 0u, big = parts ? n % parts : 0u;
-        const int cls_small = small_nb ? moe_cls(int(small_nb)) : 0, cls_big = moe_cls(int(small_nb + 1));
-        uint32_t v[6];
-        v[0] = n;
-        v[1] = parts;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) v[2 + c] = (cls_big == c ? big : 0u) + ((small_nb && cls_small == c) ? parts - big : 0u);
-        uint32_t incl[6];
-#pragma unroll
-        for (int q = 0; q < 6; ++q) {
-            incl[q] = v[q];
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const uint32_t o = __shfl_up_sync(0xffffffffu, incl[q], d);
-                if (lane >= d) incl[q] += o;
-            }
-            if (lane == 31) s_warp[warp][q] = incl[q];
-        }
-        __syncthreads();
-        uint32_t base[6], total[6];
-#pragma unroll
-        for (int q = 0; q < 6; ++q) {
-            base[q] = 0;
-            total[q] = 0;
-            for (int w = 0; w < n_warps; ++w) {
-                const uint32_t t = s_warp[w][q];
-                if (w < warp) base[q] += t;
-                total[q] += t;
-            }
-            base[q] += incl[q] - v[q];  // exclusive prefix of this expert
-        }
-        if (e < n_local) {
-            s_offsets[e] = base[0];
-            uint32_t s0 = base[0], ng = base[1];
-            uint32_t gc[4] = {base[2], base[3], base[4], base[5]};
-            for (uint32_t part = 0; part < parts && ng < gmax; ++part) {
-                const uint32_t nb = small_nb + (part < big ? 1u : 0u);
-                const int cls = moe_cls(int(nb));
-                MoeGroup g;
-                g.expert_local = int32_t(e); g.slot0 = int32_t(s0); g.nb = int32_t(nb); g.cls = cls;
-                g.pad0 = g.pad1 = g.pad2 = g.pad3 = 0;
-                glist[cls * gmax + gc[cls]++] = int32_t(ng);
-                groups[ng++] = g;
-                s0 += nb;
-            }
-        }
-        if (threadIdx.x == 0) {
-            s_offsets[n_local] = total[0];
-            // gmax = n_local + n_routes / 32 + 1 bounds the number of groups, so none is cut off
-            for (int c = 0; c < 4; ++c) hdr->gcount[c] = total[2 + c];
-            hdr->total_groups = total[1];
-            hdr->local_routes = total[0];
-        }
-    }
-    __syncthreads();
-    for (uint32_t e = threadIdx.x; e <= n_local; e += blockDim.x) {
-        offsets[e] = s_offsets[e];
-        if (e < n_local) counts[e] = s_counts[e];
-    }
-    for (uint32_t r = threadIdx.x; r < n_routes; r += blockDim.x) {
-        const int32_t e = experts[r];
-        if (e >= int32_t(first_expert) && uint32_t(e) < first_expert + n_local) {
-            const uint32_t el = uint32_t(e) - first_expert, w = r >> 5;
-            const uint32_t rank = prefix[el * words + w] + __popc(bitmap[el * words + w] & ((1u << (r & 31)) - 1u));
-            const uint32_t slot = s_offsets[el] + rank;
-            route_slot[r] = int32_t(slot);
-            slot_route[slot] = int32_t(r);
-            slot_weight[slot] = weights[r];
-        }
-    }
-}
+// Routes are sorted by expert (moe_plan.cu); every expert's routes are cut into groups and each
+// (group, row tile) of an expert matrix is one CTA of a grouped kernel streaming all columns: the
+// integer kernel (moe_grouped_i8.cu) for groups of few routes, the tensor-core kernel
+// (gemm_q8_tcgen05.cu) for groups of many. The size class of a group picks the kernel instance.
 
 // y[t] (+)= ((0 + d[slot(t,0)]) + d[slot(t,1)]) + ...: the reference's accumulation order
 // (crates/beholdd-model/src/qwen3moe/forward.rs:1385-1398); routes of other ranks are skipped.
@@ -841,19 +707,26 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
 
 namespace {
 
-// One launch of the integer grouped kernel per size class that can occur: a class only exists
-// when there are enough routes for its smallest group (5 / 9 / 17).
-int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
-                           const int32_t* glist, uint32_t gmax, uint32_t n_routes, uint32_t n_local, const void* xq, float* out0,
-                           float* out1, const float* slot_weight, cudaStream_t s) {
+// One launch per size class that can occur (a class only exists when there are enough routes for its
+// smallest group): the integer kernel below `tc_min`, the tensor-core kernel from there on.
+int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const MoePlanBuffers& pb, uint32_t n_routes,
+                           uint32_t n_local, uint32_t cap, uint32_t tc_min, const void* xq, const void* x16, float* out0, float* out1,
+                           const float* i8_scale, const float* tc_scale, cudaStream_t s) {
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
-    const uint32_t least[4] = {1, 5, 9, 17};
-    for (uint32_t cls = 0; cls < 4; ++cls) {
-        if (n_routes < least[cls]) break;
-        const uint32_t by_size = n_routes / least[cls];
-        const uint32_t bound = cls == 3 ? by_size : (small < by_size ? small : by_size);
-        const int32_t st = bhd_launch_moe_grouped_i8(ctx, w0, w1, hdr, groups, glist + cls * gmax, cls, bound, xq, n_routes, out0, out1,
-                                                     slot_weight, s);
+    for (uint32_t cls = 0; cls < uint32_t(BHD_MOE_CLASSES); ++cls) {
+        const uint32_t least = bhd_moe_cls_least(int(cls));
+        if (n_routes < least || least > cap) break;
+        // An expert cut into several groups only yields groups of more than cap / 2 routes, so the classes below hold
+        // at most one group per expert; every class holds at most routes / (its smallest group) groups.
+        const uint32_t by_size = n_routes / least;
+        const uint32_t bound = (2 * (4u << cls) >= cap) ? by_size : (small < by_size ? small : by_size);
+        int32_t st;
+        if (cls < tc_min)
+            st = bhd_launch_moe_grouped_i8(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, xq, n_routes, out0,
+                                           out1, i8_scale, s);
+        else
+            st = bhd_launch_gemm_q8_grouped(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, x16, n_routes,
+                                            out0, out1, tc_scale, s);
         if (st != BHD_OK) return st;
     }
     return BHD_OK;
@@ -862,9 +735,10 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
 }  // namespace
 
 // Fast path of bhd_moe_experts: plan (sort routes by expert, cut into groups), token gather +
-// block-floating packing, grouped gate/up, SiLU gating fused into the packing of the down
-// input, grouped down scaled by the route weight, combine in route order. Sets *handled = false
-// when the tensors do not meet the rules of the TMA path (Q8_0, 16-byte aligned rows).
+// packing of the activations (block-floating bytes for the integer kernel, row-scaled fp16 for the
+// tensor-core kernel), grouped gate/up, SiLU gating fused into the packing of the down input,
+// grouped down scaled by the route weight, combine in route order. Sets *handled = false when the
+// tensors do not meet the rules of the TMA path (Q8_0, 16-byte aligned rows).
 int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
                              const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
                              uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y, int accumulate,
@@ -875,55 +749,65 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const uint64_t ff = gate->rows, dim = gate->cols;
     if (dim % 8 != 0 || ff % 8 != 0) return BHD_OK;
     const uint64_t R64 = T * top_k;
-    // 2^20 routes keep every grid dimension of the grouped kernels (at most routes / 17 groups of the
-    // largest class on grid.y) within 65535; more routes take the general kernels.
+    // 2^20 routes keep every grid dimension of the grouped kernels (at most routes / 5 groups of a
+    // class on grid.y would not fit, but a class of groups that small holds at most one group per
+    // expert) within 65535; more routes take the general kernels.
     if (R64 > (1u << 20) || n_local > 1024) return BHD_OK;
     const uint32_t R = uint32_t(R64), E = n_local;
-    const uint32_t words = (R + 31) / 32;
+    // Groups of many routes go to the tensor-core kernel (from 17 routes by default: above about a dozen routes
+    // converting a weight tile once costs fewer instructions than post-processing integer sums per route).
+    const bool tc_ok = bhd_gemm_q8_grouped_usable(ctx, gate) && bhd_gemm_q8_grouped_usable(ctx, up) && bhd_gemm_q8_grouped_usable(ctx, down);
+    uint32_t tc_min = ctx->moe_tc_min_cls ? ctx->moe_tc_min_cls : 3u;
+    if (tc_min < 2) tc_min = 2;
+    if (tc_min > 4) tc_min = 4;
+    const uint32_t cap = tc_ok ? 256u : 32u;
+    if (!tc_ok) tc_min = uint32_t(BHD_MOE_CLASSES);
     const uint32_t gmax = E + R / 32 + 1;
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 256); return o; };
     const size_t o_hdr = take(sizeof(MoeHeader)), o_counts = take(4 * size_t(E)), o_offsets = take(4 * size_t(E + 1));
-    const size_t o_rslot = take(4 * size_t(R)), o_sroute = take(4 * size_t(R)), o_sweight = take(4 * size_t(R));
-    const size_t o_groups = take(sizeof(MoeGroup) * size_t(gmax)), o_glist = take(4 * 4 * size_t(gmax));
-    const size_t o_bitmap = take(4 * size_t(E) * words), o_prefix = take(4 * size_t(E) * words);
+    const size_t o_rslot = take(4 * size_t(R)), o_sroute = take(4 * size_t(R)), o_sweight = take(4 * size_t(R)), o_scls = take(size_t(R));
+    const size_t o_groups = take(sizeof(MoeGroup) * size_t(gmax)), o_glist = take(4 * size_t(BHD_MOE_CLASSES) * size_t(gmax));
+    const size_t o_whist = take(4 * bhd_moe_plan_scratch_words(R, E));
     const size_t o_g = take(4 * size_t(R) * ff), o_u = take(4 * size_t(R) * ff), o_d = take(4 * size_t(R) * dim);
     const size_t o_xq = take(bhd_moe_slots_i8_bytes(uint32_t(dim), R)), o_aq = take(bhd_moe_slots_i8_bytes(uint32_t(ff), R));
+    const size_t o_x16 = take(tc_ok ? 2 * size_t(R) * dim : 0), o_a16 = take(tc_ok ? 2 * size_t(R) * ff : 0);
+    const size_t o_xs = take(4 * size_t(R)), o_as = take(4 * size_t(R));
     int32_t st = bhd_ensure_workspace(ctx, off, s);
     if (st != BHD_OK) return st;
     uint8_t* ws = ctx->workspace;
-    MoeHeader* hdr = reinterpret_cast<MoeHeader*>(ws + o_hdr);
-    MoeGroup* groups = reinterpret_cast<MoeGroup*>(ws + o_groups);
-    int32_t* glist = reinterpret_cast<int32_t*>(ws + o_glist);
-    int32_t* route_slot = reinterpret_cast<int32_t*>(ws + o_rslot);
-    int32_t* slot_route = reinterpret_cast<int32_t*>(ws + o_sroute);
-    float* slot_weight = reinterpret_cast<float*>(ws + o_sweight);
+    MoePlanBuffers pb;
+    pb.hdr = reinterpret_cast<MoeHeader*>(ws + o_hdr);
+    pb.counts = reinterpret_cast<uint32_t*>(ws + o_counts);
+    pb.offsets = reinterpret_cast<uint32_t*>(ws + o_offsets);
+    pb.route_slot = reinterpret_cast<int32_t*>(ws + o_rslot);
+    pb.slot_route = reinterpret_cast<int32_t*>(ws + o_sroute);
+    pb.slot_weight = reinterpret_cast<float*>(ws + o_sweight);
+    pb.slot_cls = ws + o_scls;
+    pb.groups = reinterpret_cast<MoeGroup*>(ws + o_groups);
+    pb.glist = reinterpret_cast<int32_t*>(ws + o_glist);
+    pb.whist = reinterpret_cast<uint32_t*>(ws + o_whist);
+    pb.gmax = gmax;
     float* gbuf = reinterpret_cast<float*>(ws + o_g);
     float* ubuf = reinterpret_cast<float*>(ws + o_u);
     float* dbuf = reinterpret_cast<float*>(ws + o_d);
+    float* xscale = reinterpret_cast<float*>(ws + o_xs);
+    float* ascale = reinterpret_cast<float*>(ws + o_as);
+    const bool tc_possible = tc_ok && R >= bhd_moe_cls_least(int(tc_min));
 
-    const size_t plan_smem = size_t(E) * words * 8;
-    const int plan_on_chip = plan_smem <= 160 * 1024;
-    static bhd_once_per_device plan_once;
-    if (plan_once.pending(ctx)) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_moe_plan, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), "raising the shared memory limit");
-        plan_once.mark(ctx);
-    }
-    // one thread per local expert in the group-building step
-    k_moe_plan<<<1, (R <= 256 && E <= 256) ? 256 : 1024, plan_on_chip ? plan_smem : 0, s>>>(experts, weights, R, first_expert, E, n_total, hdr,
-                                  reinterpret_cast<uint32_t*>(ws + o_counts), reinterpret_cast<uint32_t*>(ws + o_offsets),
-                                  route_slot, slot_route, slot_weight, groups, glist, gmax,
-                                  reinterpret_cast<uint32_t*>(ws + o_bitmap), reinterpret_cast<uint32_t*>(ws + o_prefix),
-                                  ctx->status_dev, plan_on_chip);
-    BHD_LAUNCHED(ctx, "route planning kernel");
+    if ((st = bhd_launch_moe_plan(ctx, experts, weights, R, first_expert, E, n_total, cap, pb, s)) != BHD_OK) return st;
     // gate and up: [ff x dim] per expert, both matrices in one launch per size class
-    if ((st = bhd_launch_moe_slots_i8(ctx, 0, hdr, slot_route, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
-    if ((st = launch_grouped_all(ctx, gate, up, hdr, groups, glist, gmax, R, E, ws + o_xq, gbuf, ubuf, nullptr, s)) != BHD_OK) return st;
+    if ((st = bhd_launch_moe_slots_i8(ctx, 0, pb.hdr, pb.slot_route, pb.slot_cls, tc_min - 1, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
+    if (tc_possible && (st = bhd_launch_moe_rows_f16(ctx, 0, pb.hdr, pb.slot_route, pb.slot_cls, tc_min, top_k, x, nullptr, uint32_t(dim), R,
+                                                      ws + o_x16, nullptr, xscale, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, gate, up, pb, R, E, cap, tc_min, ws + o_xq, ws + o_x16, gbuf, ubuf, nullptr, xscale, s)) != BHD_OK) return st;
     // down: [dim x ff] per expert, each output row scaled by its route weight
-    if ((st = bhd_launch_moe_slots_i8(ctx, 1, hdr, slot_route, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
-    if ((st = launch_grouped_all(ctx, down, nullptr, hdr, groups, glist, gmax, R, E, ws + o_aq, dbuf, nullptr, slot_weight, s)) != BHD_OK) return st;
+    if ((st = bhd_launch_moe_slots_i8(ctx, 1, pb.hdr, pb.slot_route, pb.slot_cls, tc_min - 1, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
+    if (tc_possible && (st = bhd_launch_moe_rows_f16(ctx, 1, pb.hdr, pb.slot_route, pb.slot_cls, tc_min, top_k, gbuf, ubuf, uint32_t(ff), R,
+                                                      ws + o_a16, pb.slot_weight, ascale, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, down, nullptr, pb, R, E, cap, tc_min, ws + o_aq, ws + o_a16, dbuf, nullptr, pb.slot_weight, ascale, s)) != BHD_OK) return st;
     const uint64_t n = T * dim;
-    k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, route_slot, y, n, uint32_t(dim), top_k, accumulate);
+    k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, pb.route_slot, y, n, uint32_t(dim), top_k, accumulate);
     BHD_LAUNCHED(ctx, "route combine kernel");
     *handled = true;
     return BHD_OK;

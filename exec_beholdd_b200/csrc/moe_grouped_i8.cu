@@ -6,12 +6,12 @@
 // weight byte as possible.
 //   * Q8_0 quants go to mma.sync m16n8k32 (s8 x s8 -> s32) exactly as they lie in memory; no
 //     conversion. One MMA covers one 32-column block of 16 rows for four routes.
-//   * Activations are block floating point per (route, 256-column chunk): X = round(x * 2^(14-e))
+//   * Activations are block-scaled integers per (route, 256-column chunk): X = round(x * 32639 / max|x|)
 //     split into two signed bytes, X = 256 * d0 + d1. The two digits of a route sit in adjacent
 //     MMA columns (column = 2 * route + digit), so the lane that owns accumulator columns
 //     (2t, 2t+1) combines them without any exchange: v = 256 * c0 + c1, exact in s32.
 //   * Per block the lane adds d_block(row) * v into a per-chunk f32 sum; per chunk it folds in
-//     the route's 2^(e-14). Relative error 2^-15 of the largest activation of the chunk.
+//     the route's chunk factor max|x| / 32639. Relative error 2^-16 of the largest activation of the chunk.
 //   * Four or eight consumer warps (16 rows each) share the staged activations; one producer
 //     warp keeps a 2-3 stage ring full: one tiled TMA copy per 64 x 272-byte weight box, one bulk
 //     copy for the group's packed activations (contiguous, because slots are sorted by expert).
@@ -30,7 +30,7 @@ constexpr int CHUNK_K = 256;
 constexpr int BOX = 272;        // packed bytes per row per chunk
 constexpr int BOX_ROWS = 64;    // rows of the weight tensor map's box
 // Packed activations of one (slot, chunk): 8 blocks x 2 digits x 32 bytes in fragment order,
-// then 2^(e-14) as f32; padded to 576 bytes so that the eight routes a warp reads at once fall
+// then the chunk factor as f32; padded to 576 bytes so that the eight routes a warp reads at once fall
 // into different shared-memory banks (144 words = 16 mod 32).
 constexpr int SLOT_BYTES = 576, SLOT_SCALE_OFF = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
@@ -99,12 +99,14 @@ __device__ __forceinline__ void imma_s8(int (&c)[4], const uint32_t (&a)[4], uin
 // One warp per (slot, chunk); lane l holds columns 8l..8l+7 of the chunk (block l / 4).
 // out[(chunk * n_slots + slot) * SLOT_BYTES ...]: per block 32 bytes of digit 0 then 32 of digit
 // 1, byte order [t][half][i] for k-slot 16 * half + 4 * t + i (what lane-in-quad t loads as one
-// 8-byte B fragment), then the chunk's 2^(e-14).
-__global__ void k_moe_slots_i8(int mode, const MoeHeader* __restrict__ hdr, const int32_t* __restrict__ slot_route, uint32_t top_k,
+// 8-byte B fragment), then the chunk's factor max|x| / 32639.
+__global__ void k_moe_slots_i8(int mode, const MoeHeader* __restrict__ hdr, const int32_t* __restrict__ slot_route,
+                               const uint8_t* __restrict__ slot_cls, uint32_t max_cls, uint32_t top_k,
                                const float* __restrict__ src, const float* __restrict__ src2, uint32_t K, uint32_t n_slots,
                                uint8_t* __restrict__ out, uint32_t* __restrict__ status) {
     const uint32_t chunk = blockIdx.y, slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (slot >= hdr->local_routes || slot >= n_slots) return;  // whole warps
+    if (slot_cls[slot] > max_cls) return;                       // a group the tensor-core kernel takes (fp16 rows)
     const uint32_t k0 = chunk * CHUNK_K + 8 * lane;
     const uint64_t row = mode == 0 ? uint64_t(uint32_t(slot_route[slot]) / top_k) : uint64_t(slot);
     float v[8];
@@ -137,16 +139,16 @@ __global__ void k_moe_slots_i8(int mode, const MoeHeader* __restrict__ hdr, cons
     if (bad) atomicOr(status, BHD_DEV_ACTIVATION_RANGE);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    // mx = m * 2^ex, m in [0.5, 1): ex = biased exponent - 126; chunks below 2^-100 pack as zero
-    const int eb = int(__float_as_uint(mx) >> 23);
-    const bool tiny = eb < 27;
-    const float up = tiny ? 0.f : __uint_as_float(uint32_t(267 - eb) << 23);   // 2^(14 - ex)
-    const float down = tiny ? 0.f : __uint_as_float(uint32_t(eb - 13) << 23);  // 2^(ex - 14)
+    // The chunk's largest magnitude maps to 32639 = 127 * 256 + 127, the largest integer whose two balanced digits
+    // both fit a signed byte; chunks below 2^-100 pack as zero.
+    const bool tiny = (__float_as_uint(mx) >> 23) < 27u;
+    const float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
+    const float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
     uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int X = __float2int_rn(v[i] * up);           // |X| <= 2^14
-        const int d0 = (X + 128) >> 8, d1 = X - d0 * 256;  // X = 256 * d0 + d1, both in [-128, 127]
+        const int X = __float2int_rn(v[i] * up);           // |X| <= 32639
+        const int d0 = (X + 128) >> 8, d1 = X - d0 * 256;  // X = 256 * d0 + d1, d0 in [-127, 127], d1 in [-128, 127]
         w0[i >> 2] |= (uint32_t(d0) & 0xffu) << (8 * (i & 3));
         w1[i >> 2] |= (uint32_t(d1) & 0xffu) << (8 * (i & 3));
     }
@@ -335,10 +337,11 @@ size_t bhd_moe_slots_i8_bytes(uint32_t K, uint32_t n_slots) {
     return size_t((K + CHUNK_K - 1) / CHUNK_K) * n_slots * SLOT_BYTES;
 }
 
-int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, uint32_t top_k,
-                                const float* src, const float* src2, uint32_t K, uint32_t n_slots, void* out, cudaStream_t s) {
+int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, const uint8_t* slot_cls,
+                                uint32_t max_cls, uint32_t top_k, const float* src, const float* src2, uint32_t K, uint32_t n_slots,
+                                void* out, cudaStream_t s) {
     if (n_slots == 0) return BHD_OK;
-    k_moe_slots_i8<<<dim3((n_slots + 3) / 4, (K + CHUNK_K - 1) / CHUNK_K), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, top_k,
+    k_moe_slots_i8<<<dim3((n_slots + 3) / 4, (K + CHUNK_K - 1) / CHUNK_K), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, slot_cls, max_cls, top_k,
                                                                                          src, src2, K, n_slots, static_cast<uint8_t*>(out),
                                                                                          ctx->status_dev);
     BHD_LAUNCHED(ctx, mode ? "expert gating kernel" : "token gather kernel");

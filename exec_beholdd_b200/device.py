@@ -28,7 +28,7 @@ EXPORTS = [
     "bhd_error_text", "bhd_last_error_message", "bhd_device_name", "bhd_ctx_create", "bhd_ctx_destroy", "bhd_supports",
     "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_noalloc", "bhd_matvec_host", "bhd_matvec_host_async", "bhd_sync",
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
-    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf",
+    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option",
 ]
 
 
@@ -94,6 +94,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_check_status.argtypes = [vp, vp]
     lib.bhd_debug_wait_test.argtypes = [vp, u32, u32]
     lib.bhd_debug_expf.argtypes = [vp, vp, vp, u64, vp]
+    lib.bhd_debug_option.argtypes = [vp, u32, u32]
     lib.bhd_launch_count.restype = u64
     lib.bhd_launch_count.argtypes = [vp]
     return lib

@@ -228,6 +228,13 @@ int32_t bhd_check_status(bhd_ctx* ctx, void* stream);
  * stays usable. bhd_check_status reports BHD_ERR_DEVICE_STATUS once. */
 int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one_copy);
 
+/* Tuning hook, no counterpart in the reference. Keys:
+ *   BHD_OPTION_MOE_TC_MIN_CLASS  smallest expert-group size class the tensor-core grouped kernel takes in
+ *                                bhd_moe_experts / bhd_moe_layer: 2 = groups of 9+ routes, 3 = 17+ (default),
+ *                                4 = 33+; smaller groups run on the integer kernel. 0 restores the default. */
+#define BHD_OPTION_MOE_TC_MIN_CLASS 1u
+int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value);
+
 /* Test hook, no counterpart in the reference: out[i] = the library's expf(in[i]), the function the
  * router softmax uses on the device. The reference calls the host libm (Rust f32::exp,
  * crates/beholdd-kernel/src/vecops.rs:70-87); expert selection is the CPU's only if both give
