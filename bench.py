@@ -671,7 +671,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline workload only")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--moe-tokens", default="1,16,64,512", help="token counts of the routed-layer detail runs")
-    ap.add_argument("--exchanges", default="alltoall,gather", help="expert-parallel exchanges to run with several ranks")
+    ap.add_argument("--exchanges", default="peer,alltoall,gather", help="expert-parallel exchanges to run with several ranks")
     ap.add_argument("--sections", default="detail,prefill,moe,rowsplit", help="which detail runs follow the headline workload")
     ap.add_argument("--prefill-shapes", default="128x12288,128x4096,512x12288,512x4096,2048x12288,2048x4096",
                     help="MxN cases of the Q8_0 K=4096 prefill matmul detail run")

@@ -40,6 +40,8 @@ struct bhd_ctx {
     uint32_t spin_limit;    // polls a bounded wait makes before it gives up (0: the kernel's default)
     uint32_t debug_drop;    // test hook: the next decode matvec leaves this many copies unrequested
     uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)
+    uint32_t moe_tc_plain;   // 1: the tensor-core grouped kernel with singly rounded fp16 operands in shared memory
+    uint32_t gemm_impl;      // prefill matmul: 0 default, 1 shared-memory weight operand, 2 tensor-memory weight operand
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
 };
@@ -225,6 +227,11 @@ struct MoeHeader {
     uint32_t total_groups, local_routes, pad0, pad1;
 };
 
+extern "C" int32_t bhd_peer_alloc(bhd_ctx* ctx, uint64_t n_bytes, void** out_dev, uint8_t* handle64);
+extern "C" int32_t bhd_peer_open(bhd_ctx* ctx, const uint8_t* handle64, void** out_dev);
+extern "C" int32_t bhd_peer_close(bhd_ctx* ctx, void* dev);
+extern "C" int32_t bhd_peer_free(bhd_ctx* ctx, void* dev);
+
 // ---- kernel launchers implemented across the .cu files --------------------------------
 int32_t bhd_launch_dequantize(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, float* out, cudaStream_t s);
 int32_t bhd_launch_matvec_strict(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
@@ -233,13 +240,20 @@ int32_t bhd_launch_matvec_general(bhd_ctx* ctx, const bhd_weight* w, uint64_t sl
                                   uint64_t batch, float scale, int accumulate, cudaStream_t s);
 int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
                                   const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* xq, uint32_t n_slots,
-                                  float* out0, float* out1, const float* slot_weight, cudaStream_t s);
+                                  float* out0, float* out1, float* const* slot_dst, const float* slot_weight, cudaStream_t s);
+
 int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, const uint8_t* slot_cls,
                                 uint32_t max_cls, uint32_t top_k, const float* src, const float* src2, uint32_t K, uint32_t n_slots,
                                 void* out, cudaStream_t s);
 int32_t bhd_launch_moe_rows_f16(bhd_ctx* ctx, int mode, const void* hdr, const int32_t* slot_route, const uint8_t* slot_cls,
                                 uint32_t min_cls, uint32_t top_k, const float* src, const float* src2, uint32_t K, uint32_t n_slots,
-                                void* out16, const float* slot_weight, float* scale_out, cudaStream_t s);
+                                void* out16, void* out16_lo, const float* slot_weight, float* scale_out, cudaStream_t s);
+int32_t bhd_launch_gemm_q8_ts_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
+                                      const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* x_hi, const void* x_lo,
+                                      uint32_t n_slots, float* out0, float* out1, float* const* row_dst, const float* col_scale,
+                                      cudaStream_t s);
+int32_t bhd_launch_gemm_q8_ts_dense(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, cudaStream_t s);
+bool bhd_gemm_q8_ts_usable(const bhd_ctx* ctx, const bhd_weight* w);
 int32_t bhd_launch_gemm_q8_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
                                    const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* x16, uint32_t n_slots,
                                    float* out0, float* out1, const float* col_scale, cudaStream_t s);
@@ -258,7 +272,21 @@ struct MoePlanBuffers {
     int32_t* glist;                 // [BHD_MOE_CLASSES][gmax]: group indices per class, in expert order
     uint32_t* whist;                // [route blocks * 8][n_local] scratch
     uint32_t gmax;
+    // Expert parallel: where the weighted output row of each slot goes. Route r = (p * top_k + j) of global
+    // position p belongs to rank p / t_per_rank, whose buffer of returned rows [top_k][t_per_rank][dim] starts at
+    // peer_rows[that rank] (as mapped in this process). Null peer_rows: rows stay in the local scratch.
+    float** slot_dst;               // [routes]
+    float* const* peer_rows;
+    uint32_t t_per_rank, dim, top_k;
 };
+struct MoePeerOut {                 // argument of the fast expert path when it runs as one rank of an expert-parallel group
+    float* const* peer_rows;
+    uint32_t t_per_rank;
+};
+int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
+                             const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
+                             uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y, int accumulate,
+                             cudaStream_t s, bool* handled, const MoePeerOut* peer);
 size_t bhd_moe_plan_scratch_words(uint32_t n_routes, uint32_t n_local);
 int32_t bhd_launch_moe_plan(bhd_ctx* ctx, const int32_t* experts, const float* weights, uint32_t n_routes, uint32_t first_expert,
                             uint32_t n_local, uint32_t n_total, uint32_t cap, const MoePlanBuffers& b, cudaStream_t s);

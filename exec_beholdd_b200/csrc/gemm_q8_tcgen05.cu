@@ -404,8 +404,8 @@ int32_t bhd_launch_gemm_q8_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd
                                    float* out0, float* out1, const float* col_scale, cudaStream_t s) {
     if (group_bound == 0) return BHD_OK;
     const uint32_t K = uint32_t(w0->cols), N = uint32_t(w0->rows);
-    const uint32_t tn = 4u << cls;  // classes 3..6 -> 32, 64, 128, 256
-    if (cls < 3 || cls > 6) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "grouped matmul: size class %u has no tensor-core form", cls);
+    const uint32_t tn = 4u << cls;  // classes 2..6 -> 16, 32, 64, 128, 256
+    if (cls < 2 || cls > 6) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "grouped matmul: size class %u has no tensor-core form", cls);
     // Two stages leave room for two CTAs per SM at the narrow tiles, where the kernel is bound by weight traffic
     // and a second CTA covers the first one's start-up and drain; the wide tiles keep deeper rings.
     const uint32_t stages = tn == 256 ? 3u : (tn <= 32 ? 2u : 4u);
@@ -482,6 +482,11 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     const uint64_t n_elems = uint64_t(M) * K;
     k_f32_to_f16<<<unsigned((n_elems / 4 + 255) / 256), 256, 0, s>>>(x, x16, n_elems, ctx->status_dev);
     BHD_LAUNCHED(ctx, "activation fp16 conversion kernel");
+    if (ctx->gemm_impl == 2) {  // weight operand in tensor memory
+        st = bhd_launch_gemm_q8_ts_dense(ctx, w, slab, x16, y, M, s);
+        *handled = st == BHD_OK;
+        return st;
+    }
 
     EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode);
     CUtensorMap map_w, map_x;

@@ -210,9 +210,26 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
         // The group's largest magnitude maps to 32639 = 127 * 256 + 127, the largest integer whose two balanced
         // digits both fit a signed byte, so the full 16-bit range is used whatever the magnitude. Groups whose
         // largest magnitude is below 2^-100 (denormals included) pack as zero.
-        const bool tiny = (__float_as_uint(mx) >> 23) < 27u;
-        const float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
-        const float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
+        // When a power-of-two factor already makes every value of the group an integer within that range
+        // (small integers, dyadic fractions), it is used instead: such inputs then pass through exactly.
+        const uint32_t eb = __float_as_uint(mx) >> 23;
+        const bool tiny = eb < 27u;
+        float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
+        float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
+        {
+            const float up2 = tiny ? 0.f : __uint_as_float((268u - eb) << 23);  // 2^(14 - (eb - 127)): |x * up2| < 2^15
+            bool lossless = !tiny;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float t = val[i] * up2;
+                lossless = lossless && t == rintf(t) && fabsf(t) <= 32639.0f;
+            }
+            // every lane of the quad (the group) must agree
+            if ((__ballot_sync(0xffffffffu, !lossless) & (0xFu << (threadIdx.x & 28u))) == 0u) {
+                up = up2;
+                down = __uint_as_float((eb - 14u) << 23);
+            }
+        }
         uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};  // digit 0 / digit 1 words for b0, b1
         int sumX = 0;
 #pragma unroll

@@ -710,8 +710,8 @@ namespace {
 // One launch per size class that can occur (a class only exists when there are enough routes for its
 // smallest group): the integer kernel below `tc_min`, the tensor-core kernel from there on.
 int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const MoePlanBuffers& pb, uint32_t n_routes,
-                           uint32_t n_local, uint32_t cap, uint32_t tc_min, const void* xq, const void* x16, float* out0, float* out1,
-                           const float* i8_scale, const float* tc_scale, cudaStream_t s) {
+                           uint32_t n_local, uint32_t cap, uint32_t tc_min, const void* xq, const void* x16, const void* x16_lo, float* out0,
+                           float* out1, float* const* slot_dst, const float* i8_scale, const float* tc_scale, cudaStream_t s) {
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
     for (uint32_t cls = 0; cls < uint32_t(BHD_MOE_CLASSES); ++cls) {
         const uint32_t least = bhd_moe_cls_least(int(cls));
@@ -723,10 +723,13 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
         int32_t st;
         if (cls < tc_min)
             st = bhd_launch_moe_grouped_i8(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, xq, n_routes, out0,
-                                           out1, i8_scale, s);
-        else
+                                           out1, slot_dst, i8_scale, s);
+        else if (ctx->moe_tc_plain && !slot_dst)
             st = bhd_launch_gemm_q8_grouped(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, x16, n_routes,
                                             out0, out1, tc_scale, s);
+        else
+            st = bhd_launch_gemm_q8_ts_grouped(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, x16, x16_lo,
+                                               n_routes, out0, out1, slot_dst, tc_scale, s);
         if (st != BHD_OK) return st;
     }
     return BHD_OK;
@@ -742,7 +745,7 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
 int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
                              const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
                              uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y, int accumulate,
-                             cudaStream_t s, bool* handled) {
+                             cudaStream_t s, bool* handled, const MoePeerOut* peer) {
     *handled = false;
     if (!bhd_moe_i8_usable(gate) || !bhd_moe_i8_usable(up) || !bhd_moe_i8_usable(down)) return BHD_OK;
     if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return BHD_OK;
@@ -756,11 +759,12 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const uint32_t R = uint32_t(R64), E = n_local;
     // Groups of many routes go to the tensor-core kernel (from 17 routes by default: above about a dozen routes
     // converting a weight tile once costs fewer instructions than post-processing integer sums per route).
-    const bool tc_ok = bhd_gemm_q8_grouped_usable(ctx, gate) && bhd_gemm_q8_grouped_usable(ctx, up) && bhd_gemm_q8_grouped_usable(ctx, down);
+    const bool tc_ok = ctx->moe_tc_min_cls < uint32_t(BHD_MOE_CLASSES) && bhd_gemm_q8_grouped_usable(ctx, gate) &&
+                       bhd_gemm_q8_grouped_usable(ctx, up) && bhd_gemm_q8_grouped_usable(ctx, down);
     uint32_t tc_min = ctx->moe_tc_min_cls ? ctx->moe_tc_min_cls : 3u;
     if (tc_min < 2) tc_min = 2;
     if (tc_min > 4) tc_min = 4;
-    const uint32_t cap = tc_ok ? 256u : 32u;
+    const uint32_t cap = tc_ok ? ((ctx->moe_tc_plain && !peer) ? 256u : 128u) : 32u;  // the exact form holds hi and lo rows: 128 routes per tile
     if (!tc_ok) tc_min = uint32_t(BHD_MOE_CLASSES);
     const uint32_t gmax = E + R / 32 + 1;
     size_t off = 0;
@@ -772,7 +776,8 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     const size_t o_g = take(4 * size_t(R) * ff), o_u = take(4 * size_t(R) * ff), o_d = take(4 * size_t(R) * dim);
     const size_t o_xq = take(bhd_moe_slots_i8_bytes(uint32_t(dim), R)), o_aq = take(bhd_moe_slots_i8_bytes(uint32_t(ff), R));
     const size_t o_x16 = take(tc_ok ? 2 * size_t(R) * dim : 0), o_a16 = take(tc_ok ? 2 * size_t(R) * ff : 0);
-    const size_t o_xs = take(4 * size_t(R)), o_as = take(4 * size_t(R));
+    const size_t o_x16l = take(tc_ok ? 2 * size_t(R) * dim : 0), o_a16l = take(tc_ok ? 2 * size_t(R) * ff : 0);
+    const size_t o_xs = take(4 * size_t(R)), o_as = take(4 * size_t(R)), o_sdst = take(peer ? sizeof(float*) * size_t(R) : 0);
     int32_t st = bhd_ensure_workspace(ctx, off, s);
     if (st != BHD_OK) return st;
     uint8_t* ws = ctx->workspace;
@@ -788,6 +793,11 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     pb.glist = reinterpret_cast<int32_t*>(ws + o_glist);
     pb.whist = reinterpret_cast<uint32_t*>(ws + o_whist);
     pb.gmax = gmax;
+    pb.slot_dst = peer ? reinterpret_cast<float**>(ws + o_sdst) : nullptr;
+    pb.peer_rows = peer ? peer->peer_rows : nullptr;
+    pb.t_per_rank = peer ? peer->t_per_rank : 0u;
+    pb.dim = uint32_t(dim);
+    pb.top_k = top_k;
     float* gbuf = reinterpret_cast<float*>(ws + o_g);
     float* ubuf = reinterpret_cast<float*>(ws + o_u);
     float* dbuf = reinterpret_cast<float*>(ws + o_d);
@@ -799,13 +809,17 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     // gate and up: [ff x dim] per expert, both matrices in one launch per size class
     if ((st = bhd_launch_moe_slots_i8(ctx, 0, pb.hdr, pb.slot_route, pb.slot_cls, tc_min - 1, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
     if (tc_possible && (st = bhd_launch_moe_rows_f16(ctx, 0, pb.hdr, pb.slot_route, pb.slot_cls, tc_min, top_k, x, nullptr, uint32_t(dim), R,
-                                                      ws + o_x16, nullptr, xscale, s)) != BHD_OK) return st;
-    if ((st = launch_grouped_all(ctx, gate, up, pb, R, E, cap, tc_min, ws + o_xq, ws + o_x16, gbuf, ubuf, nullptr, xscale, s)) != BHD_OK) return st;
+                                                      ws + o_x16, ws + o_x16l, nullptr, xscale, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, gate, up, pb, R, E, cap, tc_min, ws + o_xq, ws + o_x16, ws + o_x16l, gbuf, ubuf, nullptr, nullptr, xscale, s)) != BHD_OK) return st;
     // down: [dim x ff] per expert, each output row scaled by its route weight
     if ((st = bhd_launch_moe_slots_i8(ctx, 1, pb.hdr, pb.slot_route, pb.slot_cls, tc_min - 1, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
     if (tc_possible && (st = bhd_launch_moe_rows_f16(ctx, 1, pb.hdr, pb.slot_route, pb.slot_cls, tc_min, top_k, gbuf, ubuf, uint32_t(ff), R,
-                                                      ws + o_a16, pb.slot_weight, ascale, s)) != BHD_OK) return st;
-    if ((st = launch_grouped_all(ctx, down, nullptr, pb, R, E, cap, tc_min, ws + o_aq, ws + o_a16, dbuf, nullptr, pb.slot_weight, ascale, s)) != BHD_OK) return st;
+                                                      ws + o_a16, ws + o_a16l, pb.slot_weight, ascale, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, down, nullptr, pb, R, E, cap, tc_min, ws + o_aq, ws + o_a16, ws + o_a16l, dbuf, nullptr, pb.slot_dst, pb.slot_weight, ascale, s)) != BHD_OK) return st;
+    if (peer) {  // the rows went to their owners; the caller signals them and combines what it received
+        *handled = true;
+        return BHD_OK;
+    }
     const uint64_t n = T * dim;
     k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, pb.route_slot, y, n, uint32_t(dim), top_k, accumulate);
     BHD_LAUNCHED(ctx, "route combine kernel");

@@ -412,11 +412,6 @@ extern "C" int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const f
     return BHD_OK;
 }
 
-int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_weight* up, const bhd_weight* down,
-                             const float* x, uint64_t T, uint32_t top_k, const int32_t* experts, const float* weights,
-                             uint32_t first_expert, uint32_t n_local, uint32_t n_total, float* y, int accumulate,
-                             cudaStream_t s, bool* handled);
-
 namespace {
 
 // Everything bhd_moe_experts checks before it touches an output; bhd_moe_layer runs the same
@@ -459,7 +454,7 @@ int32_t run_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight*
     const uint64_t ff = gate_exps->rows, dim = gate_exps->cols;
     bool handled = false;
     int32_t st = bhd_moe_experts_fast(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev,
-                                      weights_dev, first_expert, n_local, n_total, y_dev, accumulate, s, &handled);
+                                      weights_dev, first_expert, n_local, n_total, y_dev, accumulate, s, &handled, nullptr);
     if (st != BHD_OK || handled) return st;
 
     // General kernels: one warp per (route, row). Grids put the large dimension on x.
@@ -502,6 +497,12 @@ extern "C" int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, co
     // ids that belong to another rank.
     return run_experts(ctx, gate_exps, up_exps, down_exps, x_dev, n_positions, top_k, experts_dev, weights_dev,
                        first_expert, n_local, n_experts ? n_experts : 0x7fffffffu, y_dev, accumulate, cudaStream_t(stream));
+}
+
+// bhd_moe_route for callers inside the library (validated arguments, no probabilities or near misses).
+int32_t bhd_moe_route_internal(bhd_ctx* ctx, const bhd_weight* router, const float* x_dev, uint64_t n_positions, uint32_t top_k,
+                               int32_t* experts_dev, float* weights_dev, int32_t* counts_dev, cudaStream_t s) {
+    return bhd_moe_route(ctx, router, x_dev, n_positions, top_k, experts_dev, weights_dev, counts_dev, nullptr, nullptr, s);
 }
 
 extern "C" int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, float* y_dev, uint64_t n_positions,

@@ -141,9 +141,25 @@ __global__ void k_moe_slots_i8(int mode, const MoeHeader* __restrict__ hdr, cons
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     // The chunk's largest magnitude maps to 32639 = 127 * 256 + 127, the largest integer whose two balanced digits
     // both fit a signed byte; chunks below 2^-100 pack as zero.
-    const bool tiny = (__float_as_uint(mx) >> 23) < 27u;
-    const float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
-    const float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
+    // When a power-of-two factor already makes every value of the chunk an integer within that range (small
+    // integers, dyadic fractions), it is used instead: such inputs then pass through exactly.
+    const uint32_t eb = __float_as_uint(mx) >> 23;
+    const bool tiny = eb < 27u;
+    float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
+    float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
+    {
+        const float up2 = tiny ? 0.f : __uint_as_float((268u - eb) << 23);  // |x * up2| < 2^15
+        bool lossless = !tiny;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float t = v[i] * up2;
+            lossless = lossless && t == rintf(t) && fabsf(t) <= 32639.0f;
+        }
+        if (__all_sync(0xffffffffu, lossless)) {
+            up = up2;
+            down = __uint_as_float((eb - 14u) << 23);
+        }
+    }
     uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -170,6 +186,7 @@ struct GroupedI8Params {
     const uint8_t* xq;         // [chunk][slot][SLOT_BYTES]
     float* out0;               // [slot][rows] of matrix 0 (gate, or down)
     float* out1;               // [slot][rows] of matrix 1 (up)
+    float* const* slot_dst;    // optional: where the output row of a slot starts (instead of out0 + slot * rows)
     const float* slot_weight;  // down only: route weight per slot
     uint32_t* status;
     uint32_t rows, chunks, n_slots, cls, ring;
@@ -301,8 +318,9 @@ __global__ void __launch_bounds__((CW + 1) * 32) k_moe_grouped_i8(const __grid_c
         if (route >= nb) continue;  // columns beyond the group hold whatever was in shared memory
         const uint32_t slot = slot0 + route;
         const float sc = p.slot_weight ? p.slot_weight[slot] : 1.0f;
-        if (row_a < p.rows) out[uint64_t(slot) * p.rows + row_a] = __fmul_rn(acc[j][0], sc);
-        if (row_b < p.rows) out[uint64_t(slot) * p.rows + row_b] = __fmul_rn(acc[j][1], sc);
+        float* dst = p.slot_dst ? p.slot_dst[slot] : out + uint64_t(slot) * p.rows;
+        if (row_a < p.rows) dst[row_a] = __fmul_rn(acc[j][0], sc);
+        if (row_b < p.rows) dst[row_b] = __fmul_rn(acc[j][1], sc);
     }
 }
 
@@ -351,8 +369,9 @@ int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const i
 // Groups of one size class (cls 0..3: up to 4, 8, 16, 32 routes): one CTA per (group, 64-row tile[, gate|up]).
 int32_t bhd_launch_moe_grouped_i8(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,
                                   const int32_t* glist, uint32_t cls, uint32_t group_bound, const void* xq, uint32_t n_slots,
-                                  float* out0, float* out1, const float* slot_weight, cudaStream_t s) {
+                                  float* out0, float* out1, float* const* slot_dst, const float* slot_weight, cudaStream_t s) {
     GroupedI8Params p;
+    p.slot_dst = slot_dst;
     p.hdr = static_cast<const MoeHeader*>(hdr);
     p.groups = static_cast<const MoeGroup*>(groups);
     p.glist = glist;

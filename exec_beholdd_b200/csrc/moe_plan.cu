@@ -195,6 +195,10 @@ __global__ void __launch_bounds__(PLAN_THREADS) k_moe_scatter(const int32_t* __r
             b.slot_route[slot] = int32_t(r);
             b.slot_weight[slot] = weights[r];
             b.slot_cls[slot] = uint8_t(bhd_moe_cls(int(nb)));
+            if (b.peer_rows) {
+                const uint32_t pos = r / b.top_k, j = r - pos * b.top_k, owner = pos / b.t_per_rank, t = pos - owner * b.t_per_rank;
+                b.slot_dst[slot] = b.peer_rows[owner] + (uint64_t(j) * b.t_per_rank + t) * b.dim;
+            }
         } else if (r < n_routes) {
             b.route_slot[r] = -1;
         }

@@ -28,7 +28,8 @@ EXPORTS = [
     "bhd_error_text", "bhd_last_error_message", "bhd_device_name", "bhd_ctx_create", "bhd_ctx_destroy", "bhd_supports",
     "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_noalloc", "bhd_matvec_host", "bhd_matvec_host_async", "bhd_sync",
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
-    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option",
+    "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option", "bhd_peer_alloc", "bhd_peer_open", "bhd_peer_close", "bhd_peer_free",
+    "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy",
 ]
 
 
@@ -95,6 +96,14 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_debug_wait_test.argtypes = [vp, u32, u32]
     lib.bhd_debug_expf.argtypes = [vp, vp, vp, u64, vp]
     lib.bhd_debug_option.argtypes = [vp, u32, u32]
+    lib.bhd_peer_alloc.argtypes = [vp, u64, C.POINTER(vp), vp]
+    lib.bhd_peer_open.argtypes = [vp, vp, C.POINTER(vp)]
+    lib.bhd_peer_close.argtypes = [vp, vp]
+    lib.bhd_peer_free.argtypes = [vp, vp]
+    lib.bhd_ep_create.argtypes = [vp, u32, u32, u32, u32, u32, u32, C.POINTER(vp), vp]
+    lib.bhd_ep_connect.argtypes = [vp, vp]
+    lib.bhd_ep_layer.argtypes = [vp, vp, vp, vp, vp, vp, vp, u64, vp, vp, vp, i32, vp]
+    lib.bhd_ep_destroy.argtypes = [vp]
     lib.bhd_launch_count.restype = u64
     lib.bhd_launch_count.argtypes = [vp]
     return lib

@@ -46,20 +46,56 @@ class ExpertParallelLayer:
         self.rank, self.world, self.group = rank, world, group
         self.per = n_experts // world
         assert n_experts % world == 0
-        assert exchange in ("gather", "alltoall")
+        assert exchange in ("gather", "alltoall", "peer")
         self.exchange = exchange
+        self._ep = None        # the library's exchange object ("peer")
+        self._ep_max_t = 0
         self.last_counts = None
         self._marks = None  # (name, event) pairs of an instrumented forward
 
     #: whether forward() can be captured into a CUDA graph (the NCCL exchanges here read split sizes on the host)
     @property
     def capturable(self) -> bool:
-        return self.world == 1
+        return self.world == 1 or self.exchange == "peer"
 
     #: whether the result equals the single-GPU layer over the same global batch to the bit
     @property
     def bit_identical(self) -> bool:
-        return self.world == 1 or self.exchange == "alltoall"
+        return self.world == 1 or self.exchange in ("alltoall", "peer")
+
+    def _peer_exchange(self, T: int):
+        """The library's peer-memory exchange (bhd_ep_*), created on first use for T positions per rank; the
+        64-byte handles of the ranks' blocks travel through the process group."""
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+
+        if self._ep is not None and T <= self._ep_max_t:
+            return self._ep
+        self._free_peer_exchange()
+        lib, ctx = self.dev.lib, self.dev.ctx
+        handle = (C.c_uint8 * 64)()
+        ep = C.c_void_p()
+        self.dev._check(lib.bhd_ep_create(ctx, self.rank, self.world, self.n_experts, self.dim, self.top_k, T, C.byref(ep), handle))
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda" if dist.get_backend(self.group) == "nccl" else "cpu")
+        everyone = torch.empty((self.world, 64), dtype=torch.uint8, device=mine.device)
+        dist.all_gather_into_tensor(everyone.view(-1), mine, group=self.group)
+        blob = bytes(everyone.cpu().numpy().reshape(-1).tolist())
+        self.dev._check(lib.bhd_ep_connect(ep, C.c_char_p(blob)))
+        dist.barrier(group=self.group)  # every rank has mapped every block before anyone writes
+        self._ep, self._ep_max_t = ep, T
+        return ep
+
+    def _free_peer_exchange(self):
+        if self._ep is not None:
+            import torch
+            import torch.distributed as dist
+
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)  # nobody still writes into a block that is about to go
+            self.dev.lib.bhd_ep_destroy(self._ep)
+            self._ep = None
 
     def _mark(self, name):
         if self._marks is not None:
@@ -111,6 +147,7 @@ class ExpertParallelLayer:
                    n_experts, dim, ff, top_k, rank, world, group, exchange)
 
     def free(self):
+        self._free_peer_exchange()
         for w in (self.router, self.gate, self.up, self.down):
             w.free()
 
@@ -148,6 +185,15 @@ class ExpertParallelLayer:
             return experts, weights
 
         import torch.distributed as dist
+
+        if self.exchange == "peer":
+            ep = self._peer_exchange(T)
+            self.dev._check(self.dev.lib.bhd_ep_layer(ep, self.router.handle, self.gate.handle, self.up.handle, self.down.handle,
+                                                      x.data_ptr(), y.data_ptr(), T, experts.data_ptr(), weights.data_ptr(),
+                                                      counts.data_ptr(), 1 if accumulate else 0, self.dev._stream()))
+            self.last_counts = counts
+            self._mark("layer")
+            return experts, weights
 
         self._route(x, experts, weights, counts)
         self.last_counts = counts

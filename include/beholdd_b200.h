@@ -198,6 +198,40 @@ int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_wei
 int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, float* y_dev, uint64_t n_positions, uint32_t top_k,
                         uint64_t dim, int32_t accumulate, void* stream);
 
+/* ---- several GPUs of one node (one process per GPU); the reference is single-process and has no counterpart ----
+ *
+ * Peer-visible buffers: allocated (and zeroed) by their owner, exported as 64 opaque bytes, opened by the
+ * other ranks' processes, which then address them with ordinary loads and stores over NVLink. How the 64
+ * bytes travel between the processes is the host's business. Close every opened mapping before its owner
+ * frees the buffer. */
+int32_t bhd_peer_alloc(bhd_ctx* ctx, uint64_t n_bytes, void** out_dev, uint8_t* handle64);
+int32_t bhd_peer_open(bhd_ctx* ctx, const uint8_t* handle64, void** out_dev);
+int32_t bhd_peer_close(bhd_ctx* ctx, void* dev);
+int32_t bhd_peer_free(bhd_ctx* ctx, void* dev);
+
+/* The routed layer with the experts split over `world` ranks (at most 8): rank r holds experts
+ * [r * n_experts / world, (r + 1) * n_experts / world) as the slabs of its gate/up/down weights, the router is
+ * replicated, and every rank owns `n_positions` positions per call (the same number on every rank). The ranks
+ * exchange rows through peer memory inside the kernels (dispatch: every position to every rank; return: each
+ * route's weighted output row straight from the down-projection epilogue into the owner's buffer), flags with a
+ * bounded wait order the steps, and the owner adds the returned rows in selection order
+ * (forward.rs:1385-1398): the result equals bhd_moe_layer over all world * n_positions positions on one GPU,
+ * bit for bit. No host synchronisation, no collective library; the call can be captured into a CUDA graph.
+ *   bhd_ep_create   allocates this rank's exchange block for at most `max_positions` positions per rank and
+ *                   returns its 64-byte handle;
+ *   bhd_ep_connect  takes the handles of all ranks in rank order (world * 64 bytes; the own entry is ignored);
+ *   bhd_ep_layer    one layer; all ranks must call it the same number of times with the same n_positions. A
+ *                   rank that never arrives makes the others' waits run out (about a second), which they
+ *                   report through BHD_ERR_DEVICE_STATUS at the next bhd_check_status. */
+typedef struct bhd_ep bhd_ep;
+int32_t bhd_ep_create(bhd_ctx* ctx, uint32_t rank, uint32_t world, uint32_t n_experts, uint32_t dim, uint32_t top_k,
+                      uint32_t max_positions, bhd_ep** out_ep, uint8_t* handle64);
+int32_t bhd_ep_connect(bhd_ep* ep, const uint8_t* handles);
+int32_t bhd_ep_layer(bhd_ep* ep, const bhd_weight* router, const bhd_weight* gate_exps, const bhd_weight* up_exps,
+                     const bhd_weight* down_exps, const float* x_dev, float* y_dev, uint64_t n_positions,
+                     int32_t* experts_dev, float* weights_dev, int32_t* counts_dev, int32_t accumulate, void* stream);
+int32_t bhd_ep_destroy(bhd_ep* ep);
+
 /* The whole routed feed-forward of one layer (forward.rs:1299-1407): bhd_moe_route then
  * bhd_moe_experts over all experts. The operator shape follows the reference's only
  * resident routed-MoE entry point, VulkanDevice::routed_moe_bf16 / RoutedMoeProgram::
@@ -231,8 +265,15 @@ int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one
 /* Tuning hook, no counterpart in the reference. Keys:
  *   BHD_OPTION_MOE_TC_MIN_CLASS  smallest expert-group size class the tensor-core grouped kernel takes in
  *                                bhd_moe_experts / bhd_moe_layer: 2 = groups of 9+ routes, 3 = 17+ (default),
- *                                4 = 33+; smaller groups run on the integer kernel. 0 restores the default. */
+ *                                4 = 33+; smaller groups run on the integer kernel; 7 = integer kernels only
+ *                                (experts are then cut into groups of at most 32 routes). 0 restores the default.
+ *   BHD_OPTION_MOE_TC_PLAIN      1: those groups run with singly rounded fp16 operands staged in shared memory
+ *                                (faster, about 1e-3 less accurate); 0: exact hi + lo operands (default).
+ *   BHD_OPTION_GEMM_IMPL         prefill matmul: 1 = weight operand staged in shared memory, 2 = in tensor
+ *                                memory, 0 = the library's choice. */
 #define BHD_OPTION_MOE_TC_MIN_CLASS 1u
+#define BHD_OPTION_MOE_TC_PLAIN 2u
+#define BHD_OPTION_GEMM_IMPL 3u
 int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value);
 
 /* Test hook, no counterpart in the reference: out[i] = the library's expf(in[i]), the function the

@@ -54,7 +54,7 @@ def main():
             single.forward(x_all, y_all)
             want_single = y_all[:T].clone()
             want_oracle, experts_o, _, _ = orc.moe_layer(host[0], host[1], host[2], host[3], ff, x_np, k)
-        for exchange in [v for v in os.environ.get("BHD_TEST_EXCHANGES", "alltoall,gather").split(",") if v]:
+        for exchange in [v for v in os.environ.get("BHD_TEST_EXCHANGES", "peer,alltoall,gather").split(",") if v]:
             layer = ExpertParallelLayer.from_synthetic(dev, seed, ne, dim, ff, k, rank, world, exchange=exchange)
             y = torch.full((T, dim), float("nan"), device="cuda")
             for _ in range(2):  # twice: buffers and flags of the first call are reused by the second
