@@ -491,43 +491,48 @@ def bench_row_split(dev, torch, dist, kind, batch, steps, warmup, rank, world, b
 
     copies = 4  # distinct shards per step so that the weights come from HBM, not L2
     hosts = [synth.matrix(kind, SEED + i, ROWS, COLS) for i in range(copies)]
-    lins = [RowSplitLinear.from_host(dev, h, kind, ROWS, COLS, rank, world) for h in hosts]
     x = torch.from_numpy(synth.activations(SEED + 1, (batch, COLS))).cuda()
     y = torch.empty((batch, ROWS), device="cuda")
-
-    def step():
-        for lin in lins:
-            lin.forward(x, y)
-
-    graph = all(lin.capturable for lin in lins)
-    secs = max_over_ranks(torch, dist, time_region(torch, step, steps, warmup, barrier, graph=graph))
-    y.fill_(float("nan"))
-    lins[-1].forward(x, y)
-    torch.cuda.synchronize()
-    status_error = None
-    try:
-        dev.check_status()
-    except Exception as e:
-        status_error = repr(e)
-    us = secs / steps / copies * 1e6
-    out = {"us_per_matvec": round(us, 2), "gbs_whole_weight": round(algorithmic_bytes(kind, ROWS, COLS, batch) / us / 1e3, 1),
-           "rows_per_gpu": ROWS // world, "exchange": lins[0].exchange, "launch": "cuda graph" if graph else "eager"}
-    bad = False
+    y1 = n1_us = whole = None
     if rank == 0:
         whole = dev.upload_weight(Weight(hosts[-1], kind, ROWS, COLS))
         y1 = torch.empty((batch, ROWS), device="cuda")
-        dev.matvec_resident(whole, x, y1)
         n1_secs = time_region(torch, lambda: dev.matvec_resident(whole, x, y1), max(steps, 20), warmup)
-        err = max_rel_err(y.cpu().numpy(), y1.cpu().numpy())
-        out["parity"] = {"against": "the whole weight on rank 0", "max_rel_err": err, "ok": bool(err <= TOL)}
-        out["n1_same_run_us_warm_l2"] = n1_secs / max(steps, 20) * 1e6
-        bad = not out["parity"]["ok"]
+        n1_us = n1_secs / max(steps, 20) * 1e6
+    out = {"rows_per_gpu": ROWS // world, "n1_same_run_us_warm_l2": n1_us}
+    for exchange in ("peer", "all_gather"):
+        lins = [RowSplitLinear.from_host(dev, h, kind, ROWS, COLS, rank, world, exchange=exchange) for h in hosts]
+
+        def step():
+            for lin in lins:
+                lin.forward(x, y)
+
+        graph = all(lin.capturable for lin in lins)
+        secs = max_over_ranks(torch, dist, time_region(torch, step, steps, warmup, barrier, graph=graph))
+        y.fill_(float("nan"))
+        lins[-1].forward(x, y)
+        torch.cuda.synchronize()
+        status_error = None
+        try:
+            dev.check_status()
+        except Exception as e:
+            status_error = repr(e)
+        us = secs / steps / copies * 1e6
+        entry = {"us_per_matvec": round(us, 2), "gbs_whole_weight": round(algorithmic_bytes(kind, ROWS, COLS, batch) / us / 1e3, 1),
+                 "launch": "cuda graph" if graph else "eager"}
+        bad = False
+        if rank == 0:
+            err = max_rel_err(y.cpu().numpy(), y1.cpu().numpy())
+            entry["parity"] = {"against": "the whole weight on rank 0", "max_rel_err": err, "ok": bool(err <= TOL)}
+            bad = not entry["parity"]["ok"]
+        if status_error:
+            entry["status_error"] = status_error
+        entry["failed_on_some_rank"] = agree(torch, dist, bad or status_error is not None)
+        out[exchange] = entry
+        for lin in lins:
+            lin.free()
+    if whole is not None:
         whole.free()
-    if status_error:
-        out["status_error"] = status_error
-    out["failed_on_some_rank"] = agree(torch, dist, bad or status_error is not None)
-    for lin in lins:
-        lin.free()
     return out
 
 

@@ -41,6 +41,7 @@ struct bhd_ctx {
     uint32_t debug_drop;    // test hook: the next decode matvec leaves this many copies unrequested
     uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)
     uint32_t moe_tc_plain;   // 1: the tensor-core grouped kernel with singly rounded fp16 operands in shared memory
+    uint32_t decode_i8_nb4;  // 1: three and four activation vectors also take the integer decode kernel
     uint32_t gemm_impl;      // prefill matmul: 0 default, 1 shared-memory weight operand, 2 tensor-memory weight operand
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation

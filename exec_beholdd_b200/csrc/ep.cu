@@ -272,3 +272,168 @@ extern "C" int32_t bhd_ep_layer(bhd_ep* ep, const bhd_weight* router, const bhd_
     BHD_LAUNCHED(ctx, "route combine kernel");
     return BHD_OK;
 }
+
+// ---- a large projection with its rows split over the ranks -----------------------------------------
+// Rank r holds rows [r * N / W, (r + 1) * N / W) of the packed weight (whole packed rows, so no sum
+// crosses a GPU and the order of every row's summation is the single-GPU order), computes its slice
+// of y with the ordinary matvec kernels, and one more kernel stores the slice into every rank's copy
+// of y over peer memory, raises this rank's flag everywhere, waits (bounded) for the other ranks'
+// flags and hands the assembled y to the caller. Two buffers alternate between calls: a rank that
+// runs ahead writes the next call's slice into the other buffer while a slower rank still reads
+// this call's. The reference's counterpart is a plain Device::matvec (crates/beholdd-backend/src/lib.rs:182-198).
+
+#define BHD_RS_MAGIC 0x62686452u  // "bhdR"
+
+struct RsLayout {
+    size_t y[2], flags, total;
+};
+
+struct bhd_rowsplit {
+    uint32_t magic;
+    bhd_ctx* ctx;
+    uint32_t rank, world, rows, max_batch;
+    RsLayout lay;
+    uint8_t* local;
+    EpPeers peers;
+    float* slice;  // [max_batch x rows / world] local scratch
+    bool connected;
+};
+
+namespace {
+
+constexpr int RS_FLAG = 0, RS_EPOCH = 16;
+
+// One CTA. slice [batch x per] -> rows [rank * per, +per) of y in every rank's block; flags; wait; y -> out.
+__global__ void __launch_bounds__(1024) k_rs_exchange(const float* __restrict__ slice, uint32_t batch, uint32_t per, uint32_t rows,
+                                                      uint32_t rank, uint32_t world, EpPeers peers, RsLayout lay, float* __restrict__ out,
+                                                      uint32_t* status) {
+    uint32_t* flags = reinterpret_cast<uint32_t*>(peers.base[rank] + lay.flags);
+    const uint32_t e = flags[RS_EPOCH] + 1u;
+    const size_t yoff = lay.y[e & 1u];
+    const uint32_t n = batch * per;
+    if ((per & 3u) == 0) {
+        const uint32_t per4 = per / 4;
+        for (uint32_t i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const uint32_t b = i / per4, c = i - b * per4;
+            const float4 v = reinterpret_cast<const float4*>(slice)[i];
+            for (uint32_t r = 0; r < world; ++r)
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(peers.base[r] + yoff) + size_t(b) * rows + size_t(rank) * per + 4 * c) = v;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+            const uint32_t b = i / per, c = i - b * per;
+            const float v = slice[i];
+            for (uint32_t r = 0; r < world; ++r) reinterpret_cast<float*>(peers.base[r] + yoff)[size_t(b) * rows + size_t(rank) * per + c] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+        st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + lay.flags) + RS_FLAG + rank, e);
+        bool ok = false;
+        for (uint32_t spin = 0; spin < EP_SPIN_LIMIT; ++spin) {
+            if (int32_t(ld_acquire_sys(flags + RS_FLAG + threadIdx.x) - e) >= 0) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (!ok) atomicOr(status, BHD_DEV_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) flags[RS_EPOCH] = e;
+    const float* y = reinterpret_cast<const float*>(peers.base[rank] + yoff);
+    for (uint32_t i = threadIdx.x; i < batch * rows; i += blockDim.x) out[i] = __ldcg(y + i);  // written by peers: not through L1
+}
+
+bool rs_ok(const bhd_rowsplit* rs) { return rs && rs->magic == BHD_RS_MAGIC && rs->ctx && rs->ctx->magic == BHD_CTX_MAGIC; }
+
+}  // namespace
+
+extern "C" int32_t bhd_rowsplit_create(bhd_ctx* ctx, uint32_t rank, uint32_t world, uint32_t rows, uint32_t max_batch,
+                                       bhd_rowsplit** out_rs, uint8_t* handle64) {
+    if (!ctx || ctx->magic != BHD_CTX_MAGIC) return BHD_ERR_INVALID_ARGUMENT;
+    if (!out_rs || !handle64) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rowsplit_create: null output");
+    *out_rs = nullptr;
+    if (world < 1 || world > EP_MAX_WORLD || rank >= world || rows == 0 || rows % world != 0 || max_batch == 0)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: %u rows do not split over %u ranks (at most %d), rank %u", rows, world,
+                        EP_MAX_WORLD, rank);
+    bhd_rowsplit* rs = new (std::nothrow) bhd_rowsplit();
+    if (!rs) return bhd_fail(ctx, BHD_ERR_ALLOCATION, "%s could not allocate host memory for an exchange handle", bhd_device_name());
+    memset(rs, 0, sizeof(*rs));
+    rs->ctx = ctx;
+    rs->rank = rank; rs->world = world; rs->rows = rows; rs->max_batch = max_batch;
+    const size_t ybytes = (size_t(max_batch) * rows * 4 + 255) / 256 * 256;
+    rs->lay.y[0] = 0; rs->lay.y[1] = ybytes; rs->lay.flags = 2 * ybytes; rs->lay.total = 2 * ybytes + 256;
+    void* p = nullptr;
+    int32_t st = bhd_peer_alloc(ctx, rs->lay.total, &p, handle64);
+    if (st != BHD_OK) { delete rs; return st; }
+    rs->local = static_cast<uint8_t*>(p);
+    rs->peers.base[rank] = rs->local;
+    bhd_device_guard guard(ctx);
+    if (cudaMalloc(reinterpret_cast<void**>(&rs->slice), size_t(max_batch) * (rows / world) * 4) != cudaSuccess) {
+        cudaGetLastError();
+        bhd_peer_free(ctx, p);
+        delete rs;
+        return bhd_fail(ctx, BHD_ERR_ALLOCATION, "%s could not allocate %zu bytes for %s", bhd_device_name(),
+                        size_t(max_batch) * (rows / world) * 4, "a row-split slice");
+    }
+    rs->magic = BHD_RS_MAGIC;
+    rs->connected = world == 1;
+    *out_rs = rs;
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_rowsplit_connect(bhd_rowsplit* rs, const uint8_t* handles) {
+    if (!rs_ok(rs)) return BHD_ERR_INVALID_ARGUMENT;
+    bhd_ctx* ctx = rs->ctx;
+    if (!handles) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rowsplit_connect: null handles");
+    bhd_device_guard guard(ctx);
+    for (uint32_t r = 0; r < rs->world; ++r) {
+        if (r == rs->rank || rs->peers.base[r]) continue;
+        void* p = nullptr;
+        const int32_t st = bhd_peer_open(ctx, handles + 64 * size_t(r), &p);
+        if (st != BHD_OK) return st;
+        rs->peers.base[r] = static_cast<uint8_t*>(p);
+    }
+    rs->connected = true;
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_rowsplit_destroy(bhd_rowsplit* rs) {
+    if (!rs_ok(rs)) return BHD_ERR_INVALID_ARGUMENT;
+    bhd_ctx* ctx = rs->ctx;
+    {
+        bhd_device_guard guard(ctx);
+        cudaDeviceSynchronize();
+        for (uint32_t r = 0; r < rs->world; ++r)
+            if (r != rs->rank && rs->peers.base[r]) cudaIpcCloseMemHandle(rs->peers.base[r]);
+        if (rs->slice) cudaFree(rs->slice);
+        if (rs->local) cudaFree(rs->local);
+        cudaGetLastError();
+    }
+    rs->magic = 0;
+    delete rs;
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_rowsplit_matvec(bhd_rowsplit* rs, const bhd_weight* shard, uint64_t slab, const float* x_dev, float* y_dev,
+                                       uint32_t batch, float scale, void* stream) {
+    if (!rs_ok(rs)) return BHD_ERR_INVALID_ARGUMENT;
+    bhd_ctx* ctx = rs->ctx;
+    if (!rs->connected) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rowsplit_matvec: the group is not connected yet");
+    if (!shard || shard->magic != BHD_WEIGHT_MAGIC || shard->ctx != ctx)
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rowsplit_matvec: not a weight of this context");
+    const uint32_t per = rs->rows / rs->world;
+    if (shard->rows != per)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: the shard has %llu rows, a rank of this group holds %u", (unsigned long long)shard->rows, per);
+    if (batch == 0) return BHD_OK;
+    if (batch > rs->max_batch)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: %u activation vectors, the exchange was created for at most %u", batch, rs->max_batch);
+    if (!x_dev || !y_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rowsplit_matvec: null buffer");
+    bhd_device_guard guard(ctx);
+    int32_t st = batch <= 8 ? bhd_matvec(ctx, shard, slab, x_dev, rs->slice, batch, scale, 0, stream)
+                            : bhd_matmul(ctx, shard, slab, x_dev, rs->slice, batch, stream);
+    if (st != BHD_OK) return st;
+    k_rs_exchange<<<1, 1024, 0, cudaStream_t(stream)>>>(rs->slice, batch, per, rs->rows, rs->rank, rs->world, rs->peers, rs->lay, y_dev,
+                                                         ctx->status_dev);
+    BHD_LAUNCHED(ctx, "row-split exchange kernel");
+    return BHD_OK;
+}

@@ -166,37 +166,52 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
     static_assert(ITEMS % 8 == 0, "whole warps must run the same number of passes (full-mask shuffles below)");
     const int quad = threadIdx.x >> 2, t = threadIdx.x & 3, nquads = blockDim.x >> 2;
     const bool vec_ok = (K & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
-    for (uint32_t it = quad; it < n_local * ITEMS; it += nquads) {
-        // local chunk lc -> chunk: runs of `run` consecutive chunks, `chunk_stride` apart
+    // The loads of up to PASSES items are issued before any of them is processed: the packing sits on the critical
+    // path right after the dependency wait, and one L2 round trip is all it should cost.
+    constexpr int PASSES = 4;
+    const uint32_t total = n_local * ITEMS;
+    for (uint32_t it0 = quad; it0 < total; it0 += PASSES * nquads) {
+    float vals[PASSES][8];
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) {
+        const uint32_t it = it0 + ps * nquads;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vals[ps][i] = 0.f;
+        if (it >= total) continue;
         const uint32_t lc = it / ITEMS, item = it % ITEMS, chunk = chunk0 + (lc / run) * chunk_stride + lc % run;
         const int grp = int(item) / NB, v = int(item) % NB;
-        // columns (within the chunk) behind b0 and b1 of this lane
         int c0, c1;
         if (KIND == BHD_TYPE_Q8_0) { c0 = 32 * grp + 4 * t; c1 = c0 + 16; }
         else if (KIND == BHD_TYPE_Q4_K) { c0 = 64 * (grp >> 1) + 32 * (grp & 1) + 8 * t; c1 = c0 + 4; }
-        else { c0 = 16 * grp + 4 * t; c1 = -1; }  // Q6_K: the other half of the k range is the neighbouring group
-        float val[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) val[i] = 0.f;
+        else { c0 = 16 * grp + 4 * t; c1 = -1; }
         const uint32_t k0 = chunk * CHUNK_K + uint32_t(c0), k1 = chunk * CHUNK_K + uint32_t(c1);
         const bool live = chunk < chunks && uint32_t(v) < nvec;
         const float* xr = x + uint64_t(v) * K;
         if (live && k0 + 3 < K && vec_ok) {
             const float4 f = *reinterpret_cast<const float4*>(xr + k0);
-            val[0] = f.x; val[1] = f.y; val[2] = f.z; val[3] = f.w;
+            vals[ps][0] = f.x; vals[ps][1] = f.y; vals[ps][2] = f.z; vals[ps][3] = f.w;
         } else if (live) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) if (k0 + i < K) val[i] = xr[k0 + i];
+            for (int i = 0; i < 4; ++i) if (k0 + i < K) vals[ps][i] = xr[k0 + i];
         }
         if (c1 >= 0) {
             if (live && k1 + 3 < K && vec_ok) {
                 const float4 f = *reinterpret_cast<const float4*>(xr + k1);
-                val[4] = f.x; val[5] = f.y; val[6] = f.z; val[7] = f.w;
+                vals[ps][4] = f.x; vals[ps][5] = f.y; vals[ps][6] = f.z; vals[ps][7] = f.w;
             } else if (live) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) if (k1 + i < K) val[4 + i] = xr[k1 + i];
+                for (int i = 0; i < 4; ++i) if (k1 + i < K) vals[ps][4 + i] = xr[k1 + i];
             }
         }
+    }
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) {
+        const uint32_t it = it0 + ps * nquads;
+        if (it >= total) continue;  // whole warps: total and the first item of a warp are multiples of 8
+        // local chunk lc -> chunk: runs of `run` consecutive chunks, `chunk_stride` apart
+        const uint32_t lc = it / ITEMS, item = it % ITEMS;
+        const int grp = int(item) / NB, v = int(item) % NB;
+        float (&val)[8] = vals[ps];
         float mx = 0.f;
         bool bad = false;
 #pragma unroll
@@ -252,6 +267,7 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
             frag[4 + t] = make_uint2(w1[0], w1[1]);
         }
         if (t == 0) reinterpret_cast<float2*>(cb + FRAG)[grp * NB + v] = make_float2(down, float(sumX) * down);
+    }
     }
 }
 
@@ -443,7 +459,6 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 f[3] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
             };
             uint32_t f0[4], f1[4];
-            const float nib = (gl & 1) ? 0.0625f : 1.0f;  // j = tl * GPT + gl is odd exactly when gl is (GPT is even)
             fields(h0, f0);
             fields(h1, f1);
 #pragma unroll
@@ -454,7 +469,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_matvec_decode_i8(const __grid_co
                 const float sc0 = u2f((f0[2 * hi4] >> sh) & 0xffu), mn0 = u2f((f0[2 * hi4 + 1] >> sh) & 0xffu);
                 const float sc1 = u2f((f1[2 * hi4] >> sh) & 0xffu), mn1 = u2f((f1[2 * hi4 + 1] >> sh) & 0xffu);
                 const float2 m = mq[tl];
-                const float mx = m.x * nib;  // odd sub-blocks were fed as 16 * q
+                const float mx = (j & 1) ? m.x * 0.0625f : m.x;  // odd sub-blocks were fed as 16 * q
                 tot0 += fmaf(d0 * sc0 * mx, float(acc[tl][0] * 256 + acc[tl][1]), -(m0 * mn0) * m.y);
                 tot1 += fmaf(d1 * sc1 * mx, float(acc[tl][2] * 256 + acc[tl][3]), -(m1 * mn1) * m.y);
             }
@@ -589,11 +604,13 @@ int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cu
 int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                     uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled) {
     *handled = false;
-    if (!w->tmap16_ok || batch == 0 || batch > 2 || w->cols == 0 || w->rows > 0x7fffffffull) return BHD_OK;
+    const uint32_t max_batch = ctx->decode_i8_nb4 ? 4u : 2u;
+    if (!w->tmap16_ok || batch == 0 || batch > max_batch || w->cols == 0 || w->rows > 0x7fffffffull) return BHD_OK;
     if (w->kind != BHD_TYPE_Q8_0 && w->kind != BHD_TYPE_Q4_K && w->kind != BHD_TYPE_Q6_K) return BHD_OK;
     const uint32_t chunks = uint32_t((w->cols + CHUNK_K - 1) / CHUNK_K);
     const uint32_t tiles = uint32_t((w->rows + ROWS - 1) / ROWS);
-    const int nb = int(batch);
+    const int nb = batch == 3 ? 4 : int(batch);
+    if (nb == 4 && w->kind == BHD_TYPE_Q6_K) return BHD_OK;  // its 16-column groups need two groups per accumulator tile
     // Where this kernel wins, by measurement on B200 against the fp16 decode kernel: one vector
     // of Q4_K or Q8_0 at every shape tried; one vector of Q6_K, or two of Q4_K, only for tall
     // matrices of up to 4096 columns (rows are not split over CTAs here, so wide rows leave
@@ -601,6 +618,7 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     const bool tall = w->rows >= 8192 && w->cols <= 4096;
     if (nb == 1 && w->kind == BHD_TYPE_Q6_K && !tall) return BHD_OK;
     if (nb == 2 && !(w->kind == BHD_TYPE_Q4_K && tall)) return BHD_OK;
+    if (nb == 4 && !tall) return BHD_OK;
     // Few row tiles and long rows (a down projection, [4096 x 12288]): four CTAs per tile, each a
     // quarter of the columns, so that the grid still fills the GPU.
     // Measured: Q4_K 4096x12288 12.8 -> 11.7 us, 4096x4096 7.1 -> 6.2 us; Q8_0 gains only below
@@ -627,10 +645,11 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     p.drop_copy = ctx->debug_drop;
     ctx->debug_drop = 0;  // one launch only
     int32_t st = BHD_OK;
-#define BHD_CASE(K)                                          \
-    case K:                                                  \
-        if (nb == 1) st = launch_i8<K, 1, 1>(ctx, w, p, s);  \
-        else st = launch_i8<K, 2, 1>(ctx, w, p, s);          \
+#define BHD_CASE(K)                                               \
+    case K:                                                       \
+        if (nb == 1) st = launch_i8<K, 1, 1>(ctx, w, p, s);       \
+        else if (nb == 2) st = launch_i8<K, 2, 1>(ctx, w, p, s);  \
+        else st = launch_i8<K == BHD_TYPE_Q6_K ? BHD_TYPE_Q8_0 : K, 4, 1>(ctx, w, p, s); \
         break;
     if (ksplit && w->kind == BHD_TYPE_Q4_K) st = launch_i8<BHD_TYPE_Q4_K, 1, 4>(ctx, w, p, s);
     else if (ksplit) st = launch_i8<BHD_TYPE_Q8_0, 1, 4>(ctx, w, p, s);

@@ -757,11 +757,13 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     // expert) within 65535; more routes take the general kernels.
     if (R64 > (1u << 20) || n_local > 1024) return BHD_OK;
     const uint32_t R = uint32_t(R64), E = n_local;
-    // Groups of many routes go to the tensor-core kernel (from 17 routes by default: above about a dozen routes
-    // converting a weight tile once costs fewer instructions than post-processing integer sums per route).
-    const bool tc_ok = ctx->moe_tc_min_cls < uint32_t(BHD_MOE_CLASSES) && bhd_gemm_q8_grouped_usable(ctx, gate) &&
+    // Groups of many routes can go to the tensor-core kernel (BHD_OPTION_MOE_TC_MIN_CLASS). It is not the default:
+    // measured on B200, its per-slice pipeline latency makes it slower than the integer kernel at every group size
+    // met so far (17 to 160 routes per expert).
+    const uint32_t opt = ctx->moe_tc_min_cls;
+    const bool tc_ok = opt != 0 && opt < uint32_t(BHD_MOE_CLASSES) && bhd_gemm_q8_grouped_usable(ctx, gate) &&
                        bhd_gemm_q8_grouped_usable(ctx, up) && bhd_gemm_q8_grouped_usable(ctx, down);
-    uint32_t tc_min = ctx->moe_tc_min_cls ? ctx->moe_tc_min_cls : 3u;
+    uint32_t tc_min = opt;
     if (tc_min < 2) tc_min = 2;
     if (tc_min > 4) tc_min = 4;
     const uint32_t cap = tc_ok ? ((ctx->moe_tc_plain && !peer) ? 256u : 128u) : 32u;  // the exact form holds hi and lo rows: 128 routes per tile

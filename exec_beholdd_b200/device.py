@@ -29,7 +29,8 @@ EXPORTS = [
     "bhd_weight_upload", "bhd_weight_wrap_device", "bhd_weight_free", "bhd_dequantize", "bhd_matvec", "bhd_matvec_noalloc", "bhd_matvec_host", "bhd_matvec_host_async", "bhd_sync",
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
     "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option", "bhd_peer_alloc", "bhd_peer_open", "bhd_peer_close", "bhd_peer_free",
-    "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy",
+    "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy", "bhd_rowsplit_create", "bhd_rowsplit_connect",
+    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy",
 ]
 
 
@@ -104,6 +105,10 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_ep_connect.argtypes = [vp, vp]
     lib.bhd_ep_layer.argtypes = [vp, vp, vp, vp, vp, vp, vp, u64, vp, vp, vp, i32, vp]
     lib.bhd_ep_destroy.argtypes = [vp]
+    lib.bhd_rowsplit_create.argtypes = [vp, u32, u32, u32, u32, C.POINTER(vp), vp]
+    lib.bhd_rowsplit_connect.argtypes = [vp, vp]
+    lib.bhd_rowsplit_matvec.argtypes = [vp, vp, u64, vp, vp, u32, f32, vp]
+    lib.bhd_rowsplit_destroy.argtypes = [vp]
     lib.bhd_launch_count.restype = u64
     lib.bhd_launch_count.argtypes = [vp]
     return lib

@@ -232,6 +232,20 @@ int32_t bhd_ep_layer(bhd_ep* ep, const bhd_weight* router, const bhd_weight* gat
                      int32_t* experts_dev, float* weights_dev, int32_t* counts_dev, int32_t accumulate, void* stream);
 int32_t bhd_ep_destroy(bhd_ep* ep);
 
+/* One large projection with its rows split over `world` ranks: rank r holds whole packed rows
+ * [r * rows / world, (r + 1) * rows / world) as `shard`; every rank has the full x and ends with the full
+ * y [batch x rows] in y_dev. The slices travel through peer memory inside one kernel after the matvec (stores
+ * into every rank's copy, flags, bounded wait); no row's summation crosses a GPU, so y does not depend on
+ * `world` beyond the kernel the shard's shape selects. Capturable into a CUDA graph. All ranks must make the
+ * same sequence of calls. Device::matvec is the reference's form (crates/beholdd-backend/src/lib.rs:182-198). */
+typedef struct bhd_rowsplit bhd_rowsplit;
+int32_t bhd_rowsplit_create(bhd_ctx* ctx, uint32_t rank, uint32_t world, uint32_t rows, uint32_t max_batch,
+                            bhd_rowsplit** out_rs, uint8_t* handle64);
+int32_t bhd_rowsplit_connect(bhd_rowsplit* rs, const uint8_t* handles);
+int32_t bhd_rowsplit_matvec(bhd_rowsplit* rs, const bhd_weight* shard, uint64_t slab, const float* x_dev, float* y_dev,
+                            uint32_t batch, float scale, void* stream);
+int32_t bhd_rowsplit_destroy(bhd_rowsplit* rs);
+
 /* The whole routed feed-forward of one layer (forward.rs:1299-1407): bhd_moe_route then
  * bhd_moe_experts over all experts. The operator shape follows the reference's only
  * resident routed-MoE entry point, VulkanDevice::routed_moe_bf16 / RoutedMoeProgram::
@@ -263,17 +277,20 @@ int32_t bhd_check_status(bhd_ctx* ctx, void* stream);
 int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one_copy);
 
 /* Tuning hook, no counterpart in the reference. Keys:
- *   BHD_OPTION_MOE_TC_MIN_CLASS  smallest expert-group size class the tensor-core grouped kernel takes in
- *                                bhd_moe_experts / bhd_moe_layer: 2 = groups of 9+ routes, 3 = 17+ (default),
- *                                4 = 33+; smaller groups run on the integer kernel; 7 = integer kernels only
- *                                (experts are then cut into groups of at most 32 routes). 0 restores the default.
+ *   BHD_OPTION_MOE_TC_MIN_CLASS  smallest expert-group size class the tensor-core (tcgen05) grouped kernel takes
+ *                                in bhd_moe_experts / bhd_moe_layer / bhd_ep_layer: 2 = groups of 9+ routes,
+ *                                3 = 17+, 4 = 33+; smaller groups run on the integer kernel. 0 (default): integer
+ *                                kernels only (experts are then cut into groups of at most 32 routes).
  *   BHD_OPTION_MOE_TC_PLAIN      1: those groups run with singly rounded fp16 operands staged in shared memory
  *                                (faster, about 1e-3 less accurate); 0: exact hi + lo operands (default).
  *   BHD_OPTION_GEMM_IMPL         prefill matmul: 1 = weight operand staged in shared memory, 2 = in tensor
- *                                memory, 0 = the library's choice. */
+ *                                memory, 0 = the library's choice.
+ *   BHD_OPTION_DECODE_I8_FOUR    1: bhd_matvec sends three and four activation vectors of Q8_0 / Q4_K through the
+ *                                integer decode kernel as well (tall matrices); 0: through the fp16 decode kernel. */
 #define BHD_OPTION_MOE_TC_MIN_CLASS 1u
 #define BHD_OPTION_MOE_TC_PLAIN 2u
 #define BHD_OPTION_GEMM_IMPL 3u
+#define BHD_OPTION_DECODE_I8_FOUR 4u
 int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value);
 
 /* Test hook, no counterpart in the reference: out[i] = the library's expf(in[i]), the function the

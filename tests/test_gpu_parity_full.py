@@ -160,6 +160,47 @@ def test_routed_layer_at_benchmark_shapes_against_oracle(dev, oracle, T, tails):
         h.free()
 
 
+@pytest.mark.parametrize("min_cls,T", [(3, 512), (2, 512), (4, 2048), (2, 40)])
+def test_tensor_core_grouped_expert_kernel_against_oracle(dev, oracle, min_cls, T):
+    """The tcgen05 grouped kernel (weights in tensor memory, exact hi + lo operands) is an option of the routed
+    layer (groups of 9+ / 17+ / 33+ routes per expert; the default runs every group on the integer kernel). At the
+    benchmark shapes against the oracle (T = 2048: against the default path, to keep the CPU time in bounds)."""
+    import torch
+    from exec_beholdd_b200 import Weight
+
+    ne, dim, ff, k = 128, 2048, 768, 8
+    if T == 40:
+        ne = 8  # few experts: 40 routes per expert
+    router, gate, up, down, x = moe_inputs(900 + T, ne, dim, ff, T, tails=True)
+    rw = dev.upload_weight(Weight(router.view(np.uint8).reshape(-1), 0, ne, dim))
+    gw = dev.upload_weight(Weight(gate, 8, ff, dim), slabs=ne)
+    uw = dev.upload_weight(Weight(up, 8, ff, dim), slabs=ne)
+    dw = dev.upload_weight(Weight(down, 8, dim, ff), slabs=ne)
+    xd = cuda(x)
+    e = torch.zeros((T, k), dtype=torch.int32, device="cuda")
+    w = torch.zeros((T, k), device="cuda")
+    c = torch.zeros((ne,), dtype=torch.int32, device="cuda")
+    if T <= 512:
+        want, experts, _, _ = oracle.moe_layer(router, gate, up, down, ff, x, k)
+    else:
+        yd = torch.empty((T, dim), device="cuda")
+        dev.moe_layer(rw, gw, uw, dw, xd, yd, k, e, w, c)
+        want, experts = yd.cpu().numpy(), e.cpu().numpy()
+    try:
+        assert dev.lib.bhd_debug_option(dev.ctx, 1, min_cls) == 0
+        y = torch.full((T, dim), float("nan"), device="cuda")
+        dev.moe_layer(rw, gw, uw, dw, xd, y, k, e, w, c)
+        dev.check_status()
+    finally:
+        dev.lib.bhd_debug_option(dev.ctx, 1, 0)
+    assert np.array_equal(e.cpu().numpy(), experts)
+    err = max_rel_err(y.cpu().numpy(), want)
+    print(f"tensor-core grouped kernel, groups of class {min_cls}+, T={T}: max-rel-err {err:.2e}, busiest expert {int(c.max())} routes")
+    assert err <= TOL
+    for h in (rw, gw, uw, dw):
+        h.free()
+
+
 def test_route_margin_is_reported(dev, oracle):
     """The smallest gap between the last selected and the first rejected probability: the
     distance of the selection from a tie that a one-ulp difference in expf could flip

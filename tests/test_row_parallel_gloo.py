@@ -40,7 +40,7 @@ def _worker(rank, world, port, kind, rows, cols, batch, out_dir):
         def _local(self, x, y_local):
             y_local.copy_(torch.from_numpy(orc.matvec_batch(mine, kind, rows // world, cols, x.numpy())))
 
-    lin = OracleLinear(None, None, rows, cols, rank, world)
+    lin = OracleLinear(None, None, rows, cols, rank, world, exchange="all_gather")
     x = synth.activations(5, (batch, cols))          # the same activations on every rank
     y = torch.full((batch, rows), float("nan"))
     lin.forward(torch.from_numpy(x), y)
