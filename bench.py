@@ -406,6 +406,57 @@ def bench_moe_single(dev, torch, T, steps, warmup):
     return out
 
 
+def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128):
+    """The full-forward configuration: a random-init 48-layer Qwen3-30B-A3B-architecture model in Q8_0, a 512-token
+    prefill of uniform random token ids and 128 greedy decode steps with a KV cache; with several ranks every rank
+    runs its own sequence and the experts are split over the ranks. Device-timed; eager launches from the host."""
+    from exec_beholdd_b200 import synth
+    from exec_beholdd_b200.qwen3moe import Qwen3MoeConfig, Qwen3MoeModel
+
+    cfg = Qwen3MoeConfig()
+    t0 = time.perf_counter()
+    model = Qwen3MoeModel.random_init(dev, cfg, SEED, rank, world)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    ids = torch.from_numpy((synth.u64(SEED + 50 + rank, 3, prompt_len) % np.uint64(cfg.vocab)).astype(np.int32)).cuda()
+    model.forward(ids[:64], start=0)                      # warm-up: sizes the workspace, loads the kernels
+    model.forward(ids[64:65], start=64)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    ev[0].record()
+    logits = model.forward(ids, start=0)
+    ev[1].record()
+    out = torch.empty(n_new, dtype=torch.int32, device="cuda")
+    for i in range(n_new):
+        out[i] = torch.argmax(logits).to(torch.int32)
+        if i + 1 < n_new:
+            logits = model.forward(out[i:i + 1])
+    ev[2].record()
+    torch.cuda.synchronize()
+    prefill_s, decode_s = ev[0].elapsed_time(ev[1]) / 1e3, ev[1].elapsed_time(ev[2]) / 1e3
+    status_error = None
+    try:
+        dev.check_status()
+    except Exception as e:
+        status_error = repr(e)
+    finite = bool(torch.isfinite(logits).all())
+    if world > 1:
+        prefill_s, decode_s = max_over_ranks(torch, dist, prefill_s), max_over_ranks(torch, dist, decode_s)
+    res = {"model": "Qwen3-30B-A3B architecture, random init, Q8_0 (separate Q8_0 LM head, f32 embeddings)", "layers": cfg.n_layers,
+           "prefill_tokens_per_gpu": prompt_len, "decode_steps": n_new, "prefill_ms": prefill_s * 1e3,
+           "prefill_tokens_per_s": world * prompt_len / prefill_s, "decode_ms_per_token": decode_s / (n_new - 1) * 1e3,
+           "decode_tokens_per_s": world * (n_new - 1) / decode_s, "weights_generated_in_s": build_s, "logits_finite": finite,
+           "generated_ids_head": out[:8].cpu().tolist(), "launch": "eager, host-paced"}
+    if status_error:
+        res["status_error"] = status_error
+    if world > 1:
+        res["failed_on_some_rank"] = agree(torch, dist, status_error is not None or not finite)
+    model.free()
+    return res
+
+
 # ---- several ranks ---------------------------------------------------------------------------
 
 def agree(torch, dist, flag: bool) -> bool:
@@ -625,6 +676,10 @@ def run_gpu_arm(args):
             row_split = {f"b{b}": bench_row_split(dev, torch, dist, HEAD_KIND, b, max(dsteps, 50), 3, rank, world, barrier)
                          for b in (1, 4)}
 
+        full = None
+        if not args.quick and "forward" in sections:
+            full = leg("full_forward", lambda: bench_full_forward(dev, torch, dist, rank, world))
+
         e2e = leg("e2e", lambda: bench_matvec_e2e(dev, torch, HEAD_KIND, steps, 3, head["copies"], max(1, passes // 4)))
         if world > 1:  # whole-job figure: the replicas' rates add up
             e2e = dict(e2e, value=_sum_over_ranks(torch, dist, e2e["value"]))
@@ -649,7 +704,7 @@ def run_gpu_arm(args):
                          "kernel": "k_matvec_decode_i8 (the only kernel of the step)", "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
             "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "moe_layer": moe,
-            "row_split_projection": row_split,
+            "row_split_projection": row_split, "full_forward": full,
         }
         if errors:
             line["errors"] = errors
@@ -677,7 +732,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--moe-tokens", default="1,16,64,512", help="token counts of the routed-layer detail runs")
     ap.add_argument("--exchanges", default="peer,alltoall,gather", help="expert-parallel exchanges to run with several ranks")
-    ap.add_argument("--sections", default="detail,prefill,moe,rowsplit", help="which detail runs follow the headline workload")
+    ap.add_argument("--sections", default="detail,prefill,moe,rowsplit,forward", help="which detail runs follow the headline workload")
     ap.add_argument("--prefill-shapes", default="128x12288,128x4096,512x12288,512x4096,2048x12288,2048x4096",
                     help="MxN cases of the Q8_0 K=4096 prefill matmul detail run")
     args = ap.parse_args()

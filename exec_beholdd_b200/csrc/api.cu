@@ -47,6 +47,7 @@ const char* bhd_kind_name(uint32_t kind) {
         case BHD_TYPE_Q4_K: return "Q4_K";
         case BHD_TYPE_Q5_K: return "Q5_K";
         case BHD_TYPE_Q6_K: return "Q6_K";
+        case BHD_TYPE_BF16: return "BF16";
         default: return "unknown";
     }
 }
@@ -60,6 +61,7 @@ bool bhd_block_geometry(uint32_t kind, uint64_t* elems, uint64_t* bytes) {
         case BHD_TYPE_Q4_K: *elems = 256; *bytes = 144; return true;
         case BHD_TYPE_Q5_K: *elems = 256; *bytes = 176; return true;
         case BHD_TYPE_Q6_K: *elems = 256; *bytes = 210; return true;
+        case BHD_TYPE_BF16: *elems = 1; *bytes = 2; return true;
         default: return false;
     }
 }
@@ -515,7 +517,7 @@ int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value) {
         case BHD_OPTION_MOE_TC_MIN_CLASS: ctx->moe_tc_min_cls = value; return BHD_OK;
         case BHD_OPTION_MOE_TC_PLAIN: ctx->moe_tc_plain = value; return BHD_OK;
         case BHD_OPTION_GEMM_IMPL: ctx->gemm_impl = value; return BHD_OK;
-        case BHD_OPTION_DECODE_I8_FOUR: ctx->decode_i8_nb4 = value; return BHD_OK;
+        case BHD_OPTION_ROUTER_TILING: ctx->router_variant = value; return BHD_OK;
         default: return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "debug_option: unknown key %u", key);
     }
 }

@@ -41,7 +41,7 @@ struct bhd_ctx {
     uint32_t debug_drop;    // test hook: the next decode matvec leaves this many copies unrequested
     uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)
     uint32_t moe_tc_plain;   // 1: the tensor-core grouped kernel with singly rounded fp16 operands in shared memory
-    uint32_t decode_i8_nb4;  // 1: three and four activation vectors also take the integer decode kernel
+    uint32_t router_variant; // tiling of the router-logits kernel for more than 64 positions (0: default)
     uint32_t gemm_impl;      // prefill matmul: 0 default, 1 shared-memory weight operand, 2 tensor-memory weight operand
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
@@ -156,6 +156,12 @@ __device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_F16>(const uint8_t* ro
 }
 
 template <>
+__device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_BF16>(const uint8_t* row, uint64_t k) {
+    // the upper half of an f32 (crates/beholdd-core/src/quant.rs bf16_to_f32; cpu.rs:113-122)
+    return __uint_as_float(uint32_t(bhd_ld_u16(row + 2 * k)) << 16);
+}
+
+template <>
 __device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q8_0>(const uint8_t* row, uint64_t k) {
     const uint8_t* blk = row + (k >> 5) * 34;
     const float d = bhd_f16_bits_to_f32(bhd_ld_u16(blk));
@@ -208,6 +214,7 @@ __device__ __forceinline__ float bhd_decode_elem<BHD_TYPE_Q6_K>(const uint8_t* r
         case BHD_TYPE_Q4_K: MACRO(BHD_TYPE_Q4_K); break; \
         case BHD_TYPE_Q5_K: MACRO(BHD_TYPE_Q5_K); break; \
         case BHD_TYPE_Q6_K: MACRO(BHD_TYPE_Q6_K); break; \
+        case BHD_TYPE_BF16: MACRO(BHD_TYPE_BF16); break; \
         default: break;                                  \
     }
 

@@ -1,0 +1,208 @@
+// The operators of a transformer layer around the quantised projections and the routed experts:
+// RMSNorm (also the per-head QK-norm), rotary embedding in both pair layouts, causal /
+// incremental attention over an f32 key-value cache, and embedding-row decoding.
+//
+// Each follows the reference's CPU arithmetic step by step, in the same order and at the same
+// widths, so the results are the CPU's bits (up to the order of one f64 sum in RMSNorm):
+//   RMSNorm    crates/beholdd-kernel/src/vecops.rs:54-64   f64 sum of squares, one f32 factor
+//   rope       vecops.rs:163-197                           a*c - b*s, a*s + b*c, each product and sum rounded to f32
+//   attention  crates/beholdd-backend/src/cpu.rs:585-837   f64 dot products, f32 softmax (host expf), f64 value sums
+//   embedding  crates/beholdd-model/src/qwen3moe/forward.rs:954-972  Device::dequantize of one row
+// These are HBM- or latency-bound helpers, not hot kernels: one CTA per row / per (position, head).
+#include "common.cuh"
+#include "expf_exact.h"
+
+namespace {
+
+bool ctx_ok(const bhd_ctx* c) { return c && c->magic == BHD_CTX_MAGIC; }
+
+__global__ void __launch_bounds__(256) k_rmsnorm(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, uint64_t n,
+                                                 float eps) {
+    __shared__ double s_part[8];
+    __shared__ float s_inv;
+    const float* xr = x + blockIdx.x * n;
+    float* yr = y + blockIdx.x * n;
+    double ss = 0.0;
+    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const double v = double(xr[i]);
+        ss = __dadd_rn(ss, __dmul_rn(v, v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (unsigned i = 0; i < (blockDim.x >> 5); ++i) t += s_part[i];
+        s_inv = float(1.0 / sqrt(t / double(n) + double(eps)));
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = __fmul_rn(xr[i], inv);
+        yr[i] = w ? __fmul_rn(v, w[i]) : v;
+    }
+}
+
+// x [n_positions][vectors_per_position][2 * n_pairs]; cos / sin [n_positions][n_pairs].
+__global__ void k_rope(float* __restrict__ x, const float* __restrict__ cos, const float* __restrict__ sin, uint64_t n_vectors,
+                       uint32_t vectors_per_position, uint32_t n_pairs, int layout, int inverse) {
+    const uint64_t idx = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (idx >= n_vectors * n_pairs) return;
+    const uint64_t vec = idx / n_pairs, i = idx - vec * n_pairs, pos = vec / vectors_per_position;
+    float* xv = x + vec * 2 * n_pairs;
+    const uint64_t ia = layout == 0 ? 2 * i : i, ib = layout == 0 ? 2 * i + 1 : i + n_pairs;
+    const float a = xv[ia], b = xv[ib];
+    const float c = cos[pos * n_pairs + i], s = inverse ? -sin[pos * n_pairs + i] : sin[pos * n_pairs + i];
+    xv[ia] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    xv[ib] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+}
+
+// One CTA per (query position, head). scores in shared memory (f32, one per visible key position).
+__global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                   const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_heads,
+                                                   uint32_t n_kv_heads, uint32_t head_dim, float scale) {
+    extern __shared__ float scores[];
+    __shared__ float s_max, s_inv;
+    const uint32_t qp = blockIdx.x, head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
+    const uint32_t visible = query_start + qp + 1;
+    const float* query = q + (uint64_t(qp) * n_heads + head) * head_dim;
+    // scores: f64 dot product in element order, scaled in f64, rounded to f32
+    for (uint32_t kp = threadIdx.x; kp < visible; kp += blockDim.x) {
+        const float* key = k_cache + (uint64_t(kp) * n_kv_heads + kv_head) * head_dim;
+        double dot = 0.0;
+        for (uint32_t d = 0; d < head_dim; ++d) dot = __dadd_rn(dot, __dmul_rn(double(query[d]), double(key[d])));
+        scores[kp] = float(__dmul_rn(dot, double(scale)));
+    }
+    __syncthreads();
+    // softmax as vecops::softmax: max, exp(v - max) (0 for -inf), sequential f32 sum, multiply by 1 / sum
+    if (threadIdx.x < 32) {
+        float m = -INFINITY;
+        for (uint32_t i = threadIdx.x; i < visible; i += 32) m = fmaxf(m, scores[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x == 0) s_max = m;
+    }
+    __syncthreads();
+    const float m = s_max;
+    const bool all_masked = !isfinite(m);
+    for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) {
+        const float v = scores[i];
+        scores[i] = all_masked ? 0.0f : (isfinite(v) ? bhd_expf_exact(__fsub_rn(v, m)) : 0.0f);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.0f;
+        for (uint32_t i = 0; i < visible; ++i) sum = __fadd_rn(sum, scores[i]);
+        s_inv = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    if (!all_masked) {
+        const float inv = s_inv;
+        for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) scores[i] = __fmul_rn(scores[i], inv);
+    }
+    __syncthreads();
+    // values: per output dimension an f64 sum over the visible positions, in position order
+    float* o = out + (uint64_t(qp) * n_heads + head) * head_dim;
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        double sum = 0.0;
+        for (uint32_t vp = 0; vp < visible; ++vp)
+            sum = __dadd_rn(sum, __dmul_rn(double(scores[vp]), double(v_cache[(uint64_t(vp) * n_kv_heads + kv_head) * head_dim + d])));
+        o[d] = float(sum);
+    }
+}
+
+template <uint32_t KIND>
+__global__ void k_embedding_rows(const uint8_t* __restrict__ w, uint64_t row_bytes, uint64_t rows, uint64_t cols, const int32_t* __restrict__ ids,
+                                 float* __restrict__ out, uint32_t* __restrict__ status) {
+    const int32_t id = ids[blockIdx.x];
+    if (id < 0 || uint64_t(id) >= rows) {
+        if (threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+        return;
+    }
+    const uint8_t* row = w + uint64_t(id) * row_bytes;
+    for (uint64_t k = threadIdx.x; k < cols; k += blockDim.x) out[blockIdx.x * cols + k] = bhd_decode_elem<KIND>(row, k);
+}
+
+}  // namespace
+
+extern "C" int32_t bhd_rmsnorm(bhd_ctx* ctx, float* y_dev, const float* x_dev, const float* weight_dev, uint64_t n_rows, uint64_t n, float eps,
+                               void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (n == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: RMSNorm input cannot be empty");
+    if (!isfinite(eps) || eps < 0.0f) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: RMSNorm epsilon must be finite and non-negative, got %g", double(eps));
+    if (n_rows == 0) return BHD_OK;
+    if (n_rows > 0x7fffffffull) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: too many RMSNorm rows");
+    if (!y_dev || !x_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rmsnorm: null buffer");
+    bhd_device_guard guard(ctx);
+    k_rmsnorm<<<unsigned(n_rows), 256, 0, cudaStream_t(stream)>>>(y_dev, x_dev, weight_dev, n, eps);
+    BHD_LAUNCHED(ctx, "RMSNorm kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_rope(bhd_ctx* ctx, float* x_dev, const float* cos_dev, const float* sin_dev, uint64_t n_positions,
+                            uint32_t vectors_per_position, uint32_t n_pairs, int32_t layout, int32_t inverse, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (layout != 0 && layout != 1) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: layout must be 0 (interleaved) or 1 (split half)");
+    const uint64_t n_vectors = n_positions * vectors_per_position;
+    if (n_vectors == 0 || n_pairs == 0) return BHD_OK;
+    if (!x_dev || !cos_dev || !sin_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: null buffer");
+    bhd_device_guard guard(ctx);
+    const uint64_t n = n_vectors * n_pairs;
+    k_rope<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(x_dev, cos_dev, sin_dev, n_vectors, vectors_per_position, n_pairs, layout,
+                                                                         inverse);
+    BHD_LAUNCHED(ctx, "rotary embedding kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                                             uint64_t n_query_positions, uint64_t query_start, uint64_t n_kv_positions, uint32_t n_heads,
+                                             uint32_t n_kv_heads, uint32_t head_dim, float scale, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (n_query_positions == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention requires at least one query position");
+    if (n_kv_positions == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention requires at least one cached position");
+    if (n_heads == 0 || n_kv_heads == 0 || head_dim == 0)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention dimensions must be non-zero, got heads=%u kv_heads=%u head_dim=%u",
+                        n_heads, n_kv_heads, head_dim);
+    if (n_heads % n_kv_heads != 0)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention needs query heads divisible by kv heads, got %u and %u",
+                        n_heads, n_kv_heads);
+    if (!isfinite(scale) || scale <= 0.0f)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention scale must be positive and finite, got %g", double(scale));
+    if (query_start + n_query_positions > n_kv_positions)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention query range %llu..%llu exceeds %llu cached positions",
+                        (unsigned long long)query_start, (unsigned long long)(query_start + n_query_positions), (unsigned long long)n_kv_positions);
+    if (n_query_positions > 0x7fffffffull || n_heads > 65535u || n_kv_positions > (200u * 1024u) / 4u)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: attention over %llu positions and %u heads is beyond this kernel",
+                        (unsigned long long)n_kv_positions, n_heads);
+    if (!out_dev || !q_dev || !k_cache_dev || !v_cache_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "attention: null buffer");
+    bhd_device_guard guard(ctx);
+    const size_t smem = size_t(query_start + n_query_positions) * sizeof(float);
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+        once.mark(ctx);
+    }
+    k_attention<<<dim3(unsigned(n_query_positions), n_heads), 128, smem, cudaStream_t(stream)>>>(out_dev, q_dev, k_cache_dev, v_cache_dev,
+                                                                                                  uint32_t(query_start), n_heads, n_kv_heads,
+                                                                                                  head_dim, scale);
+    BHD_LAUNCHED(ctx, "attention kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, const int32_t* ids_dev, uint64_t n_ids, float* out_dev,
+                                      void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (!table || table->magic != BHD_WEIGHT_MAGIC || table->ctx != ctx) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "embedding_rows: not a weight of this context");
+    if (n_ids == 0 || table->cols == 0) return BHD_OK;
+    if (n_ids > 0x7fffffffull) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: too many embedding rows");
+    if (!ids_dev || !out_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "embedding_rows: null buffer");
+    bhd_device_guard guard(ctx);
+    cudaStream_t s = cudaStream_t(stream);
+#define LAUNCH(K) \
+    k_embedding_rows<K><<<unsigned(n_ids), 256, 0, s>>>(table->dev, table->row_bytes, table->rows * table->slabs, table->cols, ids_dev, out_dev, ctx->status_dev)
+    BHD_DISPATCH_KIND(table->kind, LAUNCH)
+#undef LAUNCH
+    BHD_LAUNCHED(ctx, "embedding row kernel");
+    return BHD_OK;
+}

@@ -8,11 +8,11 @@
 //     conversion to a floating-point bit pattern and no constant offset to undo, and one
 //     instruction covers 32 columns instead of 16 -- about half the issue slots per byte of
 //     the fp16 variant, which was issue-bound.
-//   * Activations are block-scaled integers: per scale group (32 columns, 16 for Q6_K) a factor
-//     s = max|x| / 32639 and a 16-bit integer X = round(x / s) split into two signed bytes,
-//     X = 256 * d0 + d1. The two digits sit in adjacent MMA columns; the s32 accumulators are
-//     combined exactly (256 * c0 + c1) and scaled by s and the block scale in f32.
-//     Relative error 2^-16 of the largest activation of the group; any finite f32 is accepted.
+//   * Activations are block floating point: per scale group (32 columns, 16 for Q6_K) a power
+//     of two s and a 15- to 16-bit integer X = round(x / s), |X| <= 32639, split into two signed
+//     bytes, X = 256 * d0 + d1. The two digits sit in adjacent MMA columns; the s32 accumulators
+//     are combined exactly (256 * c0 + c1) and scaled by s and the block scale in f32. Relative
+//     error at most 2^-15 of the largest activation of the group; any finite f32 is accepted.
 //
 // Reference semantics: crates/beholdd-backend/src/cpu.rs:398-507; block formats:
 // crates/beholdd-kernel/src/kquant.rs:29-241.
@@ -166,52 +166,37 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
     static_assert(ITEMS % 8 == 0, "whole warps must run the same number of passes (full-mask shuffles below)");
     const int quad = threadIdx.x >> 2, t = threadIdx.x & 3, nquads = blockDim.x >> 2;
     const bool vec_ok = (K & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
-    // The loads of up to PASSES items are issued before any of them is processed: the packing sits on the critical
-    // path right after the dependency wait, and one L2 round trip is all it should cost.
-    constexpr int PASSES = 4;
-    const uint32_t total = n_local * ITEMS;
-    for (uint32_t it0 = quad; it0 < total; it0 += PASSES * nquads) {
-    float vals[PASSES][8];
-#pragma unroll
-    for (int ps = 0; ps < PASSES; ++ps) {
-        const uint32_t it = it0 + ps * nquads;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) vals[ps][i] = 0.f;
-        if (it >= total) continue;
+    for (uint32_t it = quad; it < n_local * ITEMS; it += nquads) {
+        // local chunk lc -> chunk: runs of `run` consecutive chunks, `chunk_stride` apart
         const uint32_t lc = it / ITEMS, item = it % ITEMS, chunk = chunk0 + (lc / run) * chunk_stride + lc % run;
         const int grp = int(item) / NB, v = int(item) % NB;
+        // columns (within the chunk) behind b0 and b1 of this lane
         int c0, c1;
         if (KIND == BHD_TYPE_Q8_0) { c0 = 32 * grp + 4 * t; c1 = c0 + 16; }
         else if (KIND == BHD_TYPE_Q4_K) { c0 = 64 * (grp >> 1) + 32 * (grp & 1) + 8 * t; c1 = c0 + 4; }
-        else { c0 = 16 * grp + 4 * t; c1 = -1; }
+        else { c0 = 16 * grp + 4 * t; c1 = -1; }  // Q6_K: the other half of the k range is the neighbouring group
+        float val[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) val[i] = 0.f;
         const uint32_t k0 = chunk * CHUNK_K + uint32_t(c0), k1 = chunk * CHUNK_K + uint32_t(c1);
         const bool live = chunk < chunks && uint32_t(v) < nvec;
         const float* xr = x + uint64_t(v) * K;
         if (live && k0 + 3 < K && vec_ok) {
             const float4 f = *reinterpret_cast<const float4*>(xr + k0);
-            vals[ps][0] = f.x; vals[ps][1] = f.y; vals[ps][2] = f.z; vals[ps][3] = f.w;
+            val[0] = f.x; val[1] = f.y; val[2] = f.z; val[3] = f.w;
         } else if (live) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) if (k0 + i < K) vals[ps][i] = xr[k0 + i];
+            for (int i = 0; i < 4; ++i) if (k0 + i < K) val[i] = xr[k0 + i];
         }
         if (c1 >= 0) {
             if (live && k1 + 3 < K && vec_ok) {
                 const float4 f = *reinterpret_cast<const float4*>(xr + k1);
-                vals[ps][4] = f.x; vals[ps][5] = f.y; vals[ps][6] = f.z; vals[ps][7] = f.w;
+                val[4] = f.x; val[5] = f.y; val[6] = f.z; val[7] = f.w;
             } else if (live) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) if (k1 + i < K) vals[ps][4 + i] = xr[k1 + i];
+                for (int i = 0; i < 4; ++i) if (k1 + i < K) val[4 + i] = xr[k1 + i];
             }
         }
-    }
-#pragma unroll
-    for (int ps = 0; ps < PASSES; ++ps) {
-        const uint32_t it = it0 + ps * nquads;
-        if (it >= total) continue;  // whole warps: total and the first item of a warp are multiples of 8
-        // local chunk lc -> chunk: runs of `run` consecutive chunks, `chunk_stride` apart
-        const uint32_t lc = it / ITEMS, item = it % ITEMS;
-        const int grp = int(item) / NB, v = int(item) % NB;
-        float (&val)[8] = vals[ps];
         float mx = 0.f;
         bool bad = false;
 #pragma unroll
@@ -222,29 +207,16 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
         if (bad) atomicOr(status, BHD_DEV_ACTIVATION_RANGE);
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        // The group's largest magnitude maps to 32639 = 127 * 256 + 127, the largest integer whose two balanced
-        // digits both fit a signed byte, so the full 16-bit range is used whatever the magnitude. Groups whose
-        // largest magnitude is below 2^-100 (denormals included) pack as zero.
-        // When a power-of-two factor already makes every value of the group an integer within that range
-        // (small integers, dyadic fractions), it is used instead: such inputs then pass through exactly.
-        const uint32_t eb = __float_as_uint(mx) >> 23;
-        const bool tiny = eb < 27u;
-        float up = tiny ? 0.f : __fdiv_rn(32639.0f, mx);
-        float down = tiny ? 0.f : __fdiv_rn(mx, 32639.0f);
-        {
-            const float up2 = tiny ? 0.f : __uint_as_float((268u - eb) << 23);  // 2^(14 - (eb - 127)): |x * up2| < 2^15
-            bool lossless = !tiny;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float t = val[i] * up2;
-                lossless = lossless && t == rintf(t) && fabsf(t) <= 32639.0f;
-            }
-            // every lane of the quad (the group) must agree
-            if ((__ballot_sync(0xffffffffu, !lossless) & (0xFu << (threadIdx.x & 28u))) == 0u) {
-                up = up2;
-                down = __uint_as_float((eb - 14u) << 23);
-            }
-        }
+        // mx = m * 2^ex with m in [0.5, 1): ex = biased exponent - 126. The factor is the power of two that brings the
+        // group's largest magnitude just below 2^15, or below 2^14 when that would pass 32639 = 127 * 256 + 127, the
+        // largest integer whose two balanced digits both fit a signed byte. A power of two keeps small integers and
+        // dyadic fractions exact. Groups whose largest magnitude is below 2^-100 (denormals included) pack as zero.
+        const int eb = int(__float_as_uint(mx) >> 23);
+        const bool tiny = eb < 27;
+        const float up16 = __uint_as_float(uint32_t(268 - eb) << 23);               // 2^(15 - ex)
+        const bool wide = !tiny && mx * up16 <= 32639.0f;
+        const float up = tiny ? 0.f : (wide ? up16 : __uint_as_float(uint32_t(267 - eb) << 23));
+        const float down = tiny ? 0.f : __uint_as_float(uint32_t(wide ? eb - 14 : eb - 13) << 23);
         uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};  // digit 0 / digit 1 words for b0, b1
         int sumX = 0;
 #pragma unroll
@@ -267,7 +239,6 @@ __device__ __forceinline__ void pack_chunks(const float* __restrict__ x, uint32_
             frag[4 + t] = make_uint2(w1[0], w1[1]);
         }
         if (t == 0) reinterpret_cast<float2*>(cb + FRAG)[grp * NB + v] = make_float2(down, float(sumX) * down);
-    }
     }
 }
 
@@ -604,21 +575,19 @@ int32_t launch_i8(bhd_ctx* ctx, const bhd_weight* w, const DecodeI8Params& p, cu
 int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y,
                                     uint32_t batch, float scale, int accumulate, cudaStream_t s, bool* handled) {
     *handled = false;
-    const uint32_t max_batch = ctx->decode_i8_nb4 ? 4u : 2u;
-    if (!w->tmap16_ok || batch == 0 || batch > max_batch || w->cols == 0 || w->rows > 0x7fffffffull) return BHD_OK;
+    if (!w->tmap16_ok || batch == 0 || batch > 2 || w->cols == 0 || w->rows > 0x7fffffffull) return BHD_OK;
     if (w->kind != BHD_TYPE_Q8_0 && w->kind != BHD_TYPE_Q4_K && w->kind != BHD_TYPE_Q6_K) return BHD_OK;
     const uint32_t chunks = uint32_t((w->cols + CHUNK_K - 1) / CHUNK_K);
     const uint32_t tiles = uint32_t((w->rows + ROWS - 1) / ROWS);
-    const int nb = batch == 3 ? 4 : int(batch);
-    if (nb == 4 && w->kind == BHD_TYPE_Q6_K) return BHD_OK;  // its 16-column groups need two groups per accumulator tile
-    // Where this kernel wins, by measurement on B200 against the fp16 decode kernel: one vector
+    const int nb = int(batch);
+    // Three and four vectors (one 8-column MMA per block, measured): 19 us against the fp16 decode kernel's 13 us
+    // per 12288x4096 matvec, so they stay there. Where this kernel wins, by measurement on B200: one vector
     // of Q4_K or Q8_0 at every shape tried; one vector of Q6_K, or two of Q4_K, only for tall
     // matrices of up to 4096 columns (rows are not split over CTAs here, so wide rows leave
     // too few CTAs, and the wider operand sets of those variants cost occupancy).
     const bool tall = w->rows >= 8192 && w->cols <= 4096;
     if (nb == 1 && w->kind == BHD_TYPE_Q6_K && !tall) return BHD_OK;
     if (nb == 2 && !(w->kind == BHD_TYPE_Q4_K && tall)) return BHD_OK;
-    if (nb == 4 && !tall) return BHD_OK;
     // Few row tiles and long rows (a down projection, [4096 x 12288]): four CTAs per tile, each a
     // quarter of the columns, so that the grid still fills the GPU.
     // Measured: Q4_K 4096x12288 12.8 -> 11.7 us, 4096x4096 7.1 -> 6.2 us; Q8_0 gains only below
@@ -645,11 +614,10 @@ int32_t bhd_launch_matvec_decode_i8(bhd_ctx* ctx, const bhd_weight* w, uint64_t 
     p.drop_copy = ctx->debug_drop;
     ctx->debug_drop = 0;  // one launch only
     int32_t st = BHD_OK;
-#define BHD_CASE(K)                                               \
-    case K:                                                       \
-        if (nb == 1) st = launch_i8<K, 1, 1>(ctx, w, p, s);       \
-        else if (nb == 2) st = launch_i8<K, 2, 1>(ctx, w, p, s);  \
-        else st = launch_i8<K == BHD_TYPE_Q6_K ? BHD_TYPE_Q8_0 : K, 4, 1>(ctx, w, p, s); \
+#define BHD_CASE(K)                                          \
+    case K:                                                  \
+        if (nb == 1) st = launch_i8<K, 1, 1>(ctx, w, p, s);  \
+        else st = launch_i8<K, 2, 1>(ctx, w, p, s);          \
         break;
     if (ksplit && w->kind == BHD_TYPE_Q4_K) st = launch_i8<BHD_TYPE_Q4_K, 1, 4>(ctx, w, p, s);
     else if (ksplit) st = launch_i8<BHD_TYPE_Q8_0, 1, 4>(ctx, w, p, s);

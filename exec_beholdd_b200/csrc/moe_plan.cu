@@ -13,7 +13,8 @@
 //                 exclusive prefixes over (block, warp) per expert, expert offsets, and the
 //                 group records and per-class group lists (in expert order).
 //   k_moe_scatter the same walk again: slot = expert offset + prefix of (block, warp) + rank
-//                 inside the warp's range, by warp-wide matching of equal experts.
+//                 inside the warp's range, by warp-wide matching of equal experts. With a single
+//                 route block (up to 2048 routes) the first launch does this step as well.
 // All integer work; ids outside [0, n_total) are reported through the status word, ids of other
 // ranks' experts are skipped.
 #include "common.cuh"
@@ -52,9 +53,49 @@ __device__ __forceinline__ Parts cut(uint32_t n, uint32_t cap) {
     return p;
 }
 
-__global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __restrict__ experts, uint32_t n_routes, uint32_t first,
-                                                           uint32_t n_local, uint32_t n_total, uint32_t cap, MoePlanBuffers b,
-                                                           uint32_t* ticket, uint32_t* status) {
+// The second walk over the routes of block `block`: slot = expert offset + prefix of (block, warp) + rank inside
+// the warp's range. `run` [PLAN_WARPS][n_local] is shared-memory scratch.
+__device__ __forceinline__ void scatter_block(const int32_t* __restrict__ experts, const float* __restrict__ weights, uint32_t n_routes,
+                                              uint32_t first, uint32_t n_local, uint32_t n_total, uint32_t cap, const MoePlanBuffers& b,
+                                              uint32_t block, uint32_t* run) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = threadIdx.x; i < PLAN_WARPS * n_local; i += PLAN_THREADS) run[i] = 0u;
+    __syncthreads();
+    const uint32_t r0 = block * BLOCK_ROUTES + warp * WARP_ROUTES;
+    const uint32_t* prefix = b.whist + (uint64_t(block) * PLAN_WARPS + warp) * n_local;
+    for (int it = 0; it < WARP_ROUTES / 32; ++it) {
+        const uint32_t r = r0 + it * 32 + lane;
+        const int32_t el = local_expert(experts, r, n_routes, first, n_local, n_total, nullptr);
+        const uint32_t mask = __match_any_sync(0xffffffffu, el >= 0 ? uint32_t(el) : 0x80000000u + lane);
+        uint32_t seen = 0;
+        if (el >= 0) seen = run[warp * n_local + el];
+        __syncwarp();
+        if (el >= 0) {
+            const uint32_t in_expert = __ldcg(prefix + el) + seen + __popc(mask & lanemask_lt());  // rank among the expert's routes
+            const uint32_t slot = __ldcg(b.offsets + el) + in_expert;
+            if ((mask & lanemask_lt()) == 0) run[warp * n_local + el] = seen + __popc(mask);
+            // size class of the group this slot falls into (the cut of the histogram step, recomputed)
+            const Parts pt = cut(__ldcg(b.counts + el), cap);
+            const uint32_t in_big = pt.big * (pt.small_nb + 1);
+            const uint32_t nb = in_expert < in_big ? pt.small_nb + 1 : pt.small_nb;
+            b.route_slot[r] = int32_t(slot);
+            b.slot_route[slot] = int32_t(r);
+            b.slot_weight[slot] = weights[r];
+            b.slot_cls[slot] = uint8_t(bhd_moe_cls(int(nb)));
+            if (b.peer_rows) {
+                const uint32_t pos = r / b.top_k, j = r - pos * b.top_k, owner = pos / b.t_per_rank, t = pos - owner * b.t_per_rank;
+                b.slot_dst[slot] = b.peer_rows[owner] + (uint64_t(j) * b.t_per_rank + t) * b.dim;
+            }
+        } else if (r < n_routes) {
+            b.route_slot[r] = -1;
+        }
+        __syncwarp();
+    }
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __restrict__ experts, const float* __restrict__ weights,
+                                                           uint32_t n_routes, uint32_t first, uint32_t n_local, uint32_t n_total,
+                                                           uint32_t cap, MoePlanBuffers b, uint32_t* ticket, uint32_t* status) {
     extern __shared__ uint32_t hist[];  // [PLAN_WARPS][n_local], later the per-expert totals
     __shared__ uint32_t s_warp[PLAN_WARPS][NQ], s_carry[NQ];
     __shared__ bool s_last;
@@ -165,45 +206,19 @@ __global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __rest
         b.hdr->pad0 = b.hdr->pad1 = 0;
         *ticket = 0u;  // ready for the next launch
     }
+    // A single route block needs no second launch: this CTA has everything the scatter step reads.
+    if (n_blocks == 1) {
+        __threadfence();
+        __syncthreads();
+        scatter_block(experts, weights, n_routes, first, n_local, n_total, cap, b, 0, hist);
+    }
 }
 
 __global__ void __launch_bounds__(PLAN_THREADS) k_moe_scatter(const int32_t* __restrict__ experts, const float* __restrict__ weights,
                                                               uint32_t n_routes, uint32_t first, uint32_t n_local, uint32_t n_total,
                                                               uint32_t cap, MoePlanBuffers b) {
     extern __shared__ uint32_t run[];  // [PLAN_WARPS][n_local]: routes of the expert already seen by this warp
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (uint32_t i = threadIdx.x; i < PLAN_WARPS * n_local; i += PLAN_THREADS) run[i] = 0u;
-    __syncthreads();
-    const uint32_t r0 = blockIdx.x * BLOCK_ROUTES + warp * WARP_ROUTES;
-    const uint32_t* prefix = b.whist + (uint64_t(blockIdx.x) * PLAN_WARPS + warp) * n_local;
-    for (int it = 0; it < WARP_ROUTES / 32; ++it) {
-        const uint32_t r = r0 + it * 32 + lane;
-        const int32_t el = local_expert(experts, r, n_routes, first, n_local, n_total, nullptr);
-        const uint32_t mask = __match_any_sync(0xffffffffu, el >= 0 ? uint32_t(el) : 0x80000000u + lane);
-        uint32_t seen = 0;
-        if (el >= 0) seen = run[warp * n_local + el];
-        __syncwarp();
-        if (el >= 0) {
-            const uint32_t in_expert = prefix[el] + seen + __popc(mask & lanemask_lt());  // rank among the expert's routes
-            const uint32_t slot = b.offsets[el] + in_expert;
-            if ((mask & lanemask_lt()) == 0) run[warp * n_local + el] = seen + __popc(mask);
-            // size class of the group this slot falls into (the cut of k_moe_hist, recomputed)
-            const Parts pt = cut(b.counts[el], cap);
-            const uint32_t in_big = pt.big * (pt.small_nb + 1);
-            const uint32_t nb = in_expert < in_big ? pt.small_nb + 1 : pt.small_nb;
-            b.route_slot[r] = int32_t(slot);
-            b.slot_route[slot] = int32_t(r);
-            b.slot_weight[slot] = weights[r];
-            b.slot_cls[slot] = uint8_t(bhd_moe_cls(int(nb)));
-            if (b.peer_rows) {
-                const uint32_t pos = r / b.top_k, j = r - pos * b.top_k, owner = pos / b.t_per_rank, t = pos - owner * b.t_per_rank;
-                b.slot_dst[slot] = b.peer_rows[owner] + (uint64_t(j) * b.t_per_rank + t) * b.dim;
-            }
-        } else if (r < n_routes) {
-            b.route_slot[r] = -1;
-        }
-        __syncwarp();
-    }
+    scatter_block(experts, weights, n_routes, first, n_local, n_total, cap, b, blockIdx.x, run);
 }
 
 }  // namespace
@@ -219,9 +234,11 @@ int32_t bhd_launch_moe_plan(bhd_ctx* ctx, const int32_t* experts, const float* w
     const unsigned blocks = unsigned((n_routes + BLOCK_ROUTES - 1) / BLOCK_ROUTES);
     const size_t smem = size_t(PLAN_WARPS) * n_local * sizeof(uint32_t);  // at most 32 KB
     uint32_t* ticket = ctx->status_dev + 1;  // a spare word next to the status word; zero between launches
-    k_moe_hist<<<blocks, PLAN_THREADS, smem, s>>>(experts, n_routes, first_expert, n_local, n_total, cap, b, ticket, ctx->status_dev);
+    k_moe_hist<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, b, ticket, ctx->status_dev);
     BHD_LAUNCHED(ctx, "route histogram kernel");
-    k_moe_scatter<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, b);
-    BHD_LAUNCHED(ctx, "route scatter kernel");
+    if (blocks > 1) {  // a single block scatters inside the first launch
+        k_moe_scatter<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, b);
+        BHD_LAUNCHED(ctx, "route scatter kernel");
+    }
     return BHD_OK;
 }

@@ -30,7 +30,7 @@ EXPORTS = [
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
     "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option", "bhd_peer_alloc", "bhd_peer_open", "bhd_peer_close", "bhd_peer_free",
     "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy", "bhd_rowsplit_create", "bhd_rowsplit_connect",
-    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy",
+    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal",
 ]
 
 
@@ -109,6 +109,12 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_rowsplit_connect.argtypes = [vp, vp]
     lib.bhd_rowsplit_matvec.argtypes = [vp, vp, u64, vp, vp, u32, f32, vp]
     lib.bhd_rowsplit_destroy.argtypes = [vp]
+    lib.bhd_rmsnorm.argtypes = [vp, vp, vp, vp, u64, u64, f32, vp]
+    lib.bhd_rope.argtypes = [vp, vp, vp, vp, u64, u32, u32, i32, i32, vp]
+    lib.bhd_incremental_attention.argtypes = [vp, vp, vp, vp, vp, u64, u64, u64, u32, u32, u32, f32, vp]
+    lib.bhd_embedding_rows.argtypes = [vp, vp, vp, u64, vp, vp]
+    lib.bhd_debug_fill_q8_0.argtypes = [vp, vp, u64, u64, u64, u64, u64, vp]
+    lib.bhd_debug_fill_normal.argtypes = [vp, vp, u64, u64, u64, f32, vp]
     lib.bhd_launch_count.restype = u64
     lib.bhd_launch_count.argtypes = [vp]
     return lib
@@ -331,6 +337,28 @@ class CudaDevice:
         if x.numel() != m * w.cols or y.numel() != m * w.rows:
             raise ShapeError(ERR_SHAPE, f"shape mismatch: weight is {w.rows}x{w.cols}, got x={tuple(x.shape)} y={tuple(y.shape)}")
         self._check(self.lib.bhd_matmul(self.ctx, w.handle, slab, _ptr(x), _ptr(y), m, self._stream()))
+
+    def rmsnorm_resident(self, y, x, weight=None, eps: float = 1e-6) -> None:
+        """Rows of x [n_rows x n] (or one vector) normalised into y (Command::RmsNorm, execution.rs:415-457)."""
+        n = x.shape[-1]
+        self._check(self.lib.bhd_rmsnorm(self.ctx, _ptr(y), _ptr(x), _ptr(weight), x.numel() // n, n, eps, self._stream()))
+
+    def rope_resident(self, x, cos, sin, split_half: bool = True, inverse: bool = False) -> None:
+        """x [n_positions x heads x head_dim] rotated in place with cos/sin [n_positions x head_dim / 2] (Command::Rope)."""
+        n_pos, heads, hd = x.shape
+        self._check(self.lib.bhd_rope(self.ctx, _ptr(x), _ptr(cos), _ptr(sin), n_pos, heads, hd // 2, 1 if split_half else 0,
+                                      1 if inverse else 0, self._stream()))
+
+    def attention_resident(self, out, q, k_cache, v_cache, query_start: int, n_kv_positions: int, scale: float) -> None:
+        """q [n_query x n_heads x head_dim] against caches [>= n_kv_positions x n_kv_heads x head_dim]
+        (Command::IncrementalCausalAttention)."""
+        n_q, n_heads, hd = q.shape
+        self._check(self.lib.bhd_incremental_attention(self.ctx, _ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), n_q, query_start,
+                                                       n_kv_positions, n_heads, k_cache.shape[1], hd, scale, self._stream()))
+
+    def embedding_rows_resident(self, table: ResidentWeight, ids, out) -> None:
+        """out[i] = decoded row ids[i] of the table (Command::EmbeddingRow)."""
+        self._check(self.lib.bhd_embedding_rows(self.ctx, table.handle, _ptr(ids), ids.numel(), _ptr(out), self._stream()))
 
     def moe_route(self, router: ResidentWeight, x, top_k: int, experts, weights, counts=None, near=None, probs=None) -> None:
         T = x.shape[0]

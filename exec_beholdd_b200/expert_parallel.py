@@ -40,7 +40,9 @@ class ExpertParallelLayer:
     """One routed-expert layer with experts split across `world` ranks."""
 
     def __init__(self, dev, router, gate, up, down, n_experts, dim, ff, top_k, rank=0, world=1, group=None,
-                 exchange="gather"):
+                 exchange="gather", exchange_owner=None):
+        """`exchange_owner`: another layer of the same shape whose peer-memory exchange this one uses (the layers of
+        a model run one after the other, so one exchange block serves them all)."""
         self.dev, self.router, self.gate, self.up, self.down = dev, router, gate, up, down
         self.n_experts, self.dim, self.ff, self.top_k = n_experts, dim, ff, top_k
         self.rank, self.world, self.group = rank, world, group
@@ -50,6 +52,7 @@ class ExpertParallelLayer:
         self.exchange = exchange
         self._ep = None        # the library's exchange object ("peer")
         self._ep_max_t = 0
+        self._ep_owner = exchange_owner
         self.last_counts = None
         self._marks = None  # (name, event) pairs of an instrumented forward
 
@@ -71,6 +74,8 @@ class ExpertParallelLayer:
         import torch
         import torch.distributed as dist
 
+        if self._ep_owner is not None:
+            return self._ep_owner._peer_exchange(T)
         if self._ep is not None and T <= self._ep_max_t:
             return self._ep
         self._free_peer_exchange()

@@ -45,6 +45,7 @@ extern "C" {
 #define BHD_TYPE_Q4_K 12u
 #define BHD_TYPE_Q5_K 13u
 #define BHD_TYPE_Q6_K 14u
+#define BHD_TYPE_BF16 30u
 
 typedef struct bhd_ctx bhd_ctx;       /* one per GPU; owns the stream-ordered workspace */
 /* Device and workspace rules of a context:
@@ -198,6 +199,34 @@ int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_wei
 int32_t bhd_moe_combine(bhd_ctx* ctx, const float* per_route_dev, float* y_dev, uint64_t n_positions, uint32_t top_k,
                         uint64_t dim, int32_t accumulate, void* stream);
 
+/* ---- the rest of a transformer layer (what config "full forward" needs around the projections and the experts) ----
+ *
+ * Device::rmsnorm (lib.rs:200-206; cpu.rs:537-570; vecops.rs:54-64) over n_rows rows of n floats:
+ * y = x / sqrt(mean(x^2) + eps) * w with an f64 sum of squares; weight_dev may be NULL. With n = head_dim and
+ * one row per (position, head) this is the per-head QK-norm (forward.rs:1131-1160). */
+int32_t bhd_rmsnorm(bhd_ctx* ctx, float* y_dev, const float* x_dev, const float* weight_dev, uint64_t n_rows, uint64_t n,
+                    float eps, void* stream);
+
+/* Device::rope (lib.rs:260-272; cpu.rs:870-905; vecops.rs:163-197) in place on n_positions * vectors_per_position
+ * vectors of 2 * n_pairs floats; cos/sin are [n_positions][n_pairs] (vecops::rope_at per position, computed by the
+ * host in f64). layout 0 = interleaved pairs, 1 = split half (Qwen); inverse != 0 negates the sine. */
+int32_t bhd_rope(bhd_ctx* ctx, float* x_dev, const float* cos_dev, const float* sin_dev, uint64_t n_positions,
+                 uint32_t vectors_per_position, uint32_t n_pairs, int32_t layout, int32_t inverse, void* stream);
+
+/* Device::incremental_causal_attention (lib.rs:228-253; cpu.rs:693-837): q [n_query][n_heads][head_dim] at absolute
+ * positions query_start.., caches [n_kv_positions][n_kv_heads][head_dim] f32; position p attends to cache entries
+ * 0..p. Device::causal_attention (cpu.rs:585-691) is query_start = 0 with the sequence itself as the cache. f64 dot
+ * products and value sums, f32 softmax, as the CPU computes them. */
+int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev,
+                                  const float* v_cache_dev, uint64_t n_query_positions, uint64_t query_start,
+                                  uint64_t n_kv_positions, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                  float scale, void* stream);
+
+/* Embedding lookup (forward.rs:954-972): rows ids[i] of `table` decoded to f32, out [n_ids][cols]; an id outside the
+ * table is reported through the status word. */
+int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, const int32_t* ids_dev, uint64_t n_ids, float* out_dev,
+                           void* stream);
+
 /* ---- several GPUs of one node (one process per GPU); the reference is single-process and has no counterpart ----
  *
  * Peer-visible buffers: allocated (and zeroed) by their owner, exported as 64 opaque bytes, opened by the
@@ -285,12 +314,12 @@ int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one
  *                                (faster, about 1e-3 less accurate); 0: exact hi + lo operands (default).
  *   BHD_OPTION_GEMM_IMPL         prefill matmul: 1 = weight operand staged in shared memory, 2 = in tensor
  *                                memory, 0 = the library's choice.
- *   BHD_OPTION_DECODE_I8_FOUR    1: bhd_matvec sends three and four activation vectors of Q8_0 / Q4_K through the
- *                                integer decode kernel as well (tall matrices); 0: through the fp16 decode kernel. */
+ *   BHD_OPTION_ROUTER_TILING     router-logits kernel for more than 64 positions: 0 = 32 positions per CTA and 3
+ *                                tiles in flight, 1 = 32 and 5, 2 = 16 and 6, 3 = 8 and 7 (the small-batch tiling). */
 #define BHD_OPTION_MOE_TC_MIN_CLASS 1u
 #define BHD_OPTION_MOE_TC_PLAIN 2u
 #define BHD_OPTION_GEMM_IMPL 3u
-#define BHD_OPTION_DECODE_I8_FOUR 4u
+#define BHD_OPTION_ROUTER_TILING 5u
 int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value);
 
 /* Test hook, no counterpart in the reference: out[i] = the library's expf(in[i]), the function the
@@ -298,6 +327,15 @@ int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value);
  * crates/beholdd-kernel/src/vecops.rs:70-87); expert selection is the CPU's only if both give
  * the same floats, which a test checks over a sweep of arguments. */
 int32_t bhd_debug_expf(bhd_ctx* ctx, const float* in_dev, float* out_dev, uint64_t n, void* stream);
+
+/* Benchmark helpers, no counterpart in the reference: seeded synthetic tensors generated on the device.
+ * bhd_debug_fill_q8_0 writes n_slabs * blocks_per_slab Q8_0 blocks (34 bytes each; an f16 scale uniform in
+ * [1e-3, 1e-2] and 32 int8 quants uniform in [-127, 127]), byte for byte what the host generator of this
+ * package produces for (seed, stream0 + slab * stream_step); bhd_debug_fill_normal writes f32 N(0, std). */
+int32_t bhd_debug_fill_q8_0(bhd_ctx* ctx, uint8_t* out_dev, uint64_t blocks_per_slab, uint64_t n_slabs, uint64_t seed,
+                            uint64_t stream0, uint64_t stream_step, void* stream);
+int32_t bhd_debug_fill_normal(bhd_ctx* ctx, float* out_dev, uint64_t n, uint64_t seed, uint64_t stream, float std,
+                              void* cuda_stream);
 
 /* How many kernels this library has launched on the context since it was created. */
 uint64_t bhd_launch_count(const bhd_ctx* ctx);

@@ -569,6 +569,83 @@ int32_t orc_moe_layer(const float* router, const uint8_t* gate_exps, const uint8
     return ORC_OK;
 }
 
+// ---- the rest of a transformer layer (rotary embedding, causal attention) ----------------------
+
+// crates/beholdd-kernel/src/vecops.rs:118-150 (rope_freqs with optional YaRN interpolation) and :153-161
+// (rope_at): cos / sin of one position, f64 angle arithmetic rounded to f32 at the end.
+int32_t orc_rope_table(double theta, uint64_t dim, uint64_t orig_seq_len, double factor, double beta_fast, double beta_slow,
+                       uint64_t pos, float* cos_out, float* sin_out) {
+    if (dim == 0 || dim % 2 != 0 || !cos_out || !sin_out) return ORC_SHAPE;
+    const uint64_t half = dim / 2;
+    std::vector<double> freqs(half);
+    for (uint64_t i = 0; i < half; ++i) freqs[i] = 1.0 / std::pow(theta, double(2 * i) / double(dim));
+    if (orig_seq_len > 0) {
+        auto corr = [&](double rot) { return double(dim) * std::log(double(orig_seq_len) / (rot * 2.0 * M_PI)) / (2.0 * std::log(theta)); };
+        double lo = std::floor(corr(beta_fast)), hi = std::ceil(corr(beta_slow));
+        lo = std::max(lo, 0.0);
+        hi = std::min(hi, double(dim) - 1.0);
+        if (lo == hi) hi += 0.001;
+        for (uint64_t i = 0; i < half; ++i) {
+            const double ramp = std::min(1.0, std::max(0.0, (double(i) - lo) / (hi - lo)));
+            freqs[i] = freqs[i] / factor * ramp + freqs[i] * (1.0 - ramp);
+        }
+    }
+    for (uint64_t i = 0; i < half; ++i) {
+        const double a = double(pos) * freqs[i];
+        cos_out[i] = float(std::cos(a));
+        sin_out[i] = float(std::sin(a));
+    }
+    return ORC_OK;
+}
+
+// Device::rope (crates/beholdd-backend/src/cpu.rs:870-905) over vecops::rope_apply (interleaved pairs,
+// vecops.rs:163-178) and rope_apply_split_half (vecops.rs:180-197). layout 0 = interleaved, 1 = split half.
+int32_t orc_rope(float* x, uint64_t x_len, const float* cos, const float* sin, uint64_t n_pairs, int32_t layout, int32_t inverse) {
+    if (x_len != 2 * n_pairs) return ORC_SHAPE;
+    const float sgn = inverse ? -1.0f : 1.0f;
+    for (uint64_t i = 0; i < n_pairs; ++i) {
+        const uint64_t ia = layout == 0 ? 2 * i : i, ib = layout == 0 ? 2 * i + 1 : i + n_pairs;
+        const float a = x[ia], b = x[ib];
+        const float c = cos[i], s = sgn * sin[i];
+        x[ia] = a * c - b * s;
+        x[ib] = a * s + b * c;
+    }
+    return ORC_OK;
+}
+
+// Device::incremental_causal_attention (cpu.rs:693-837); Device::causal_attention (cpu.rs:585-691) is the case
+// query_start = 0, n_kv_positions = n_query_positions. f64 dot products and f64 value sums, f32 softmax.
+int32_t orc_incremental_attention(float* out, const float* q, const float* k_cache, const float* v_cache, uint64_t n_query_positions,
+                                  uint64_t query_start, uint64_t n_kv_positions, uint64_t n_heads, uint64_t n_kv_heads,
+                                  uint64_t head_dim, float scale) {
+    if (n_query_positions == 0 || n_kv_positions == 0 || n_heads == 0 || n_kv_heads == 0 || head_dim == 0) return ORC_SHAPE;
+    if (n_heads % n_kv_heads != 0 || !std::isfinite(scale) || scale <= 0.0f) return ORC_SHAPE;
+    if (query_start + n_query_positions > n_kv_positions) return ORC_SHAPE;
+    const uint64_t group = n_heads / n_kv_heads;
+    std::vector<float> scores(query_start + n_query_positions);
+    for (uint64_t qp = 0; qp < n_query_positions; ++qp) {
+        const uint64_t abs_pos = query_start + qp;
+        for (uint64_t head = 0; head < n_heads; ++head) {
+            const uint64_t kv_head = head / group;
+            const float* query = q + (qp * n_heads + head) * head_dim;
+            for (uint64_t kp = 0; kp <= abs_pos; ++kp) {
+                const float* key = k_cache + (kp * n_kv_heads + kv_head) * head_dim;
+                double dot = 0.0;
+                for (uint64_t d = 0; d < head_dim; ++d) dot += double(query[d]) * double(key[d]);
+                scores[kp] = float(dot * double(scale));
+            }
+            softmax_inplace(scores.data(), abs_pos + 1);
+            float* o = out + (qp * n_heads + head) * head_dim;
+            for (uint64_t d = 0; d < head_dim; ++d) {
+                double sum = 0.0;
+                for (uint64_t vp = 0; vp <= abs_pos; ++vp) sum += double(scores[vp]) * double(v_cache[(vp * n_kv_heads + kv_head) * head_dim + d]);
+                o[d] = float(sum);
+            }
+        }
+    }
+    return ORC_OK;
+}
+
 // The host libm's expf over an array: what the reference's softmax and SiLU call through Rust's
 // f32::exp (crates/beholdd-kernel/src/vecops.rs:70-93). Lets a test compare the device's expf with it.
 void orc_expf_array(const float* in, float* out, uint64_t n) {

@@ -71,6 +71,11 @@ class Oracle:
         L.orc_softmax.argtypes = [C.POINTER(C.c_float), C.c_uint64]
         L.orc_expf_array.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64]
         L.orc_expf_array.restype = None
+        L.orc_rope_table.argtypes = [C.c_double, C.c_uint64, C.c_uint64, C.c_double, C.c_double, C.c_double, C.c_uint64,
+                                     C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        L.orc_rope.argtypes = [C.POINTER(C.c_float), C.c_uint64, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64, C.c_int32,
+                               C.c_int32]
+        L.orc_incremental_attention.argtypes = [C.POINTER(C.c_float)] * 4 + [C.c_uint64] * 6 + [C.c_float]
         L.orc_swiglu.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64, C.c_float]
         L.orc_rmsnorm.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_uint64, C.c_float]
         L.orc_stable_top_k.argtypes = [C.POINTER(C.c_float), C.c_uint64, C.c_uint64, C.POINTER(C.c_int32),
@@ -162,6 +167,43 @@ class Oracle:
         out = np.empty_like(v)
         self.lib.orc_expf_array(_f32(v), _f32(out), v.size)
         return out
+
+    def rope_table(self, theta, dim, pos, orig_seq_len=0, factor=1.0, beta_fast=32.0, beta_slow=1.0):
+        """cos / sin of one position (vecops::rope_freqs + rope_at)."""
+        cos, sin = np.zeros(dim // 2, dtype=np.float32), np.zeros(dim // 2, dtype=np.float32)
+        st = self.lib.orc_rope_table(theta, dim, orig_seq_len, factor, beta_fast, beta_slow, pos, _f32(cos), _f32(sin))
+        if st != OK:
+            raise OracleError(st)
+        return cos, sin
+
+    def rope(self, x, cos, sin, split_half: bool, inverse: bool = False) -> np.ndarray:
+        """Device::rope on one vector; returns the rotated copy."""
+        x = np.array(x, dtype=np.float32)
+        cos, sin = np.ascontiguousarray(cos, dtype=np.float32), np.ascontiguousarray(sin, dtype=np.float32)
+        if sin.size != cos.size:
+            raise OracleError(SHAPE)
+        st = self.lib.orc_rope(_f32(x), x.size, _f32(cos), _f32(sin), cos.size, 1 if split_half else 0, 1 if inverse else 0)
+        if st != OK:
+            raise OracleError(st)
+        return x
+
+    def incremental_attention(self, q, k_cache, v_cache, n_query, query_start, n_kv, n_heads, n_kv_heads, head_dim, scale):
+        """Device::incremental_causal_attention; q [n_query][n_heads][head_dim], caches [n_kv][n_kv_heads][head_dim]."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k = np.ascontiguousarray(k_cache, dtype=np.float32)
+        v = np.ascontiguousarray(v_cache, dtype=np.float32)
+        if q.size != n_query * n_heads * head_dim or k.size != n_kv * n_kv_heads * head_dim or v.size != k.size:
+            raise OracleError(SHAPE)
+        out = np.zeros(q.size, dtype=np.float32)
+        st = self.lib.orc_incremental_attention(_f32(out), _f32(q), _f32(k), _f32(v), n_query, query_start, n_kv, n_heads, n_kv_heads,
+                                                head_dim, scale)
+        if st != OK:
+            raise OracleError(st)
+        return out.reshape(q.shape)
+
+    def causal_attention(self, q, k, v, n_positions, n_heads, n_kv_heads, head_dim, scale):
+        """Device::causal_attention: every position attends to itself and the positions before it."""
+        return self.incremental_attention(q, k, v, n_positions, 0, n_positions, n_heads, n_kv_heads, head_dim, scale)
 
     def swiglu(self, gate, up, limit=0.0) -> np.ndarray:
         g = np.array(gate, dtype=np.float32)

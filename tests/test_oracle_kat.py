@@ -290,3 +290,54 @@ def test_stable_top_k(oracle):
         oracle.stable_top_k([0.5, np.inf], 1)
     with pytest.raises(OracleError):
         oracle.stable_top_k([0.5, -0.5], 1)
+
+
+# ---- the rest of a layer: rotary embedding and causal attention (the reference's own vectors) ----
+
+def test_rope_layouts_follow_the_reference(oracle):
+    # crates/beholdd-backend/src/cpu.rs:1369-1386
+    cos, sin = [0.0, 0.0], [1.0, 1.0]
+    assert oracle.rope([1.0, 2.0, 3.0, 4.0], cos, sin, split_half=False).tolist() == [-2.0, 1.0, -4.0, 3.0]
+    half = oracle.rope([1.0, 2.0, 3.0, 4.0], cos, sin, split_half=True)
+    assert half.tolist() == [-3.0, -4.0, 1.0, 2.0]
+    assert oracle.rope(half, cos, sin, split_half=True, inverse=True).tolist() == [1.0, 2.0, 3.0, 4.0]
+
+
+def test_rope_table_is_theta_to_the_minus_two_i_over_dim(oracle):
+    # crates/beholdd-kernel/src/vecops.rs:118-161 without YaRN
+    cos, sin = oracle.rope_table(1.0e6, 8, 3)
+    for i in range(4):
+        a = 3.0 / (1.0e6 ** (2 * i / 8))
+        assert cos[i] == np.float32(np.cos(a)) and sin[i] == np.float32(np.sin(a))
+    cos0, sin0 = oracle.rope_table(1.0e6, 128, 0)
+    assert np.all(cos0 == 1.0) and np.all(sin0 == 0.0)
+
+
+def test_causal_attention_known_softmax_result(oracle):
+    # crates/beholdd-backend/src/cpu.rs:1389-1411
+    out = oracle.causal_attention([1.0, 0.0, 1.0, 0.0], [0.0, 0.0, np.log(np.float32(3.0)), 0.0], [2.0, 4.0, 6.0, 8.0], 2, 1, 1, 2, 1.0)
+    assert np.abs(out.reshape(-1) - np.array([2.0, 4.0, 5.0, 7.0])).max() < 1e-6
+
+
+def test_causal_attention_masks_the_future_and_maps_gqa_groups(oracle):
+    # crates/beholdd-backend/src/cpu.rs:1414-1440
+    out = oracle.causal_attention(np.zeros(8), np.zeros(4), [1.0, 10.0, 3.0, 30.0], 2, 4, 2, 1, 1.0)
+    assert out.reshape(-1).tolist() == [1.0, 1.0, 10.0, 10.0, 2.0, 2.0, 20.0, 20.0]
+
+
+def test_incremental_attention_equals_the_full_sequence_chunk_bitwise(oracle):
+    # crates/beholdd-backend/src/cpu.rs:1495-1541
+    q = np.sin((np.arange(24, dtype=np.float32) + np.float32(1.0)) * np.float32(0.37)).astype(np.float32)
+    k = np.cos((np.arange(12, dtype=np.float32) + np.float32(2.0)) * np.float32(0.23)).astype(np.float32)
+    v = (np.arange(12, dtype=np.float32) * np.float32(0.5) - np.float32(2.0)).astype(np.float32)
+    full = oracle.causal_attention(q, k, v, 3, 4, 2, 2, 0.5).reshape(-1)
+    inc = oracle.incremental_attention(q[8:], k, v, 2, 1, 3, 4, 2, 2, 0.5).reshape(-1)
+    assert np.array_equal(inc.view(np.uint32), full[8:].view(np.uint32))
+
+
+def test_incremental_attention_uses_the_absolute_position(oracle):
+    # crates/beholdd-backend/src/cpu.rs:1544-1570: the third cache entry is in the query's future
+    out = oracle.incremental_attention([1.0], [0.0, np.log(np.float32(3.0)), 100.0], [2.0, 6.0, 10000.0], 1, 1, 3, 1, 1, 1, 1.0)
+    assert abs(float(out.reshape(-1)[0]) - 5.0) < 1e-6
+    with pytest.raises(Exception):
+        oracle.incremental_attention([1.0], [0.0], [0.0], 1, 1, 1, 1, 1, 1, 1.0)  # query range 1..2 exceeds one cached position
