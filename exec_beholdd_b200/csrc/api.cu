@@ -232,6 +232,7 @@ static int32_t make_weight(bhd_ctx* ctx, const void* src, bool src_is_device, ui
     memset(w, 0, sizeof(*w));
     w->magic = BHD_WEIGHT_MAGIC;
     w->ctx = ctx;
+    w->device = ctx->device;
     w->kind = kind;
     w->rows = rows;
     w->cols = cols;
@@ -284,7 +285,7 @@ int32_t bhd_weight_wrap_device(bhd_ctx* ctx, const void* bytes_dev, uint64_t n_b
 int32_t bhd_weight_free(bhd_weight* w) {
     if (!w || w->magic != BHD_WEIGHT_MAGIC) return BHD_ERR_INVALID_ARGUMENT;
     if (w->owned && w->dev) {
-        bhd_device_guard guard(w->ctx);
+        bhd_device_guard guard(w->device);
         cudaDeviceSynchronize();
         cudaFree(w->dev);
     }

@@ -50,6 +50,7 @@ struct bhd_ctx {
 struct bhd_weight {
     uint32_t magic;
     bhd_ctx* ctx;
+    int device;           // the context's GPU, kept here so that a weight can be freed after its context
     uint8_t* dev;
     bool owned;
     uint32_t kind;
@@ -73,10 +74,11 @@ struct bhd_weight {
 struct bhd_device_guard {
     int prev = -1;
     bool switched = false;
-    explicit bhd_device_guard(const bhd_ctx* ctx) {
+    explicit bhd_device_guard(const bhd_ctx* ctx) : bhd_device_guard(ctx->device) {}
+    explicit bhd_device_guard(int device) {
         if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != ctx->device) {
-            cudaSetDevice(ctx->device);
+        if (prev != device) {
+            cudaSetDevice(device);
             switched = true;
         }
         cudaGetLastError();

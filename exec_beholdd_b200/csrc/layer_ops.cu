@@ -112,6 +112,17 @@ __global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, cons
     }
 }
 
+// Command::SigmoidGate (crates/beholdd-backend/src/execution.rs:1425-1441): out = in * sigmoid(gate), the sigmoid in its
+// overflow-free form.
+__global__ void k_sigmoid_gate(float* __restrict__ out, const float* __restrict__ in, const float* __restrict__ gate, uint64_t n) {
+    const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (i >= n) return;
+    const float g = gate[i];
+    const float tail = bhd_expf_exact(-fabsf(g));
+    const float sig = g >= 0.0f ? __fdiv_rn(1.0f, __fadd_rn(1.0f, tail)) : __fdiv_rn(tail, __fadd_rn(1.0f, tail));
+    out[i] = __fmul_rn(in[i], sig);
+}
+
 template <uint32_t KIND>
 __global__ void k_embedding_rows(const uint8_t* __restrict__ w, uint64_t row_bytes, uint64_t rows, uint64_t cols, const int32_t* __restrict__ ids,
                                  float* __restrict__ out, uint32_t* __restrict__ status) {
@@ -205,4 +216,22 @@ extern "C" int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, con
 #undef LAUNCH
     BHD_LAUNCHED(ctx, "embedding row kernel");
     return BHD_OK;
+}
+
+extern "C" int32_t bhd_sigmoid_gate(bhd_ctx* ctx, float* out_dev, const float* in_dev, const float* gate_dev, uint64_t n, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (n == 0) return BHD_OK;
+    if (!out_dev || !in_dev || !gate_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "sigmoid_gate: null buffer");
+    bhd_device_guard guard(ctx);
+    k_sigmoid_gate<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(out_dev, in_dev, gate_dev, n);
+    BHD_LAUNCHED(ctx, "sigmoid gate kernel");
+    return BHD_OK;
+}
+
+// Grows the context's workspace to at least n_bytes now, so that later calls (a CUDA graph capture in particular, during
+// which nothing may be allocated) find it large enough.
+extern "C" int32_t bhd_workspace_reserve(bhd_ctx* ctx, uint64_t n_bytes) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    bhd_device_guard guard(ctx);
+    return bhd_ensure_workspace(ctx, size_t(n_bytes), nullptr);
 }

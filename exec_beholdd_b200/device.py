@@ -30,7 +30,7 @@ EXPORTS = [
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
     "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option", "bhd_peer_alloc", "bhd_peer_open", "bhd_peer_close", "bhd_peer_free",
     "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy", "bhd_rowsplit_create", "bhd_rowsplit_connect",
-    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal",
+    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal", "bhd_sigmoid_gate", "bhd_workspace_reserve",
 ]
 
 
@@ -115,6 +115,8 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_embedding_rows.argtypes = [vp, vp, vp, u64, vp, vp]
     lib.bhd_debug_fill_q8_0.argtypes = [vp, vp, u64, u64, u64, u64, u64, vp]
     lib.bhd_debug_fill_normal.argtypes = [vp, vp, u64, u64, u64, f32, vp]
+    lib.bhd_sigmoid_gate.argtypes = [vp, vp, vp, vp, u64, vp]
+    lib.bhd_workspace_reserve.argtypes = [vp, u64]
     lib.bhd_launch_count.restype = u64
     lib.bhd_launch_count.argtypes = [vp]
     return lib

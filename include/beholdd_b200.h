@@ -222,6 +222,14 @@ int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const float* q_d
                                   uint64_t n_kv_positions, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
                                   float scale, void* stream);
 
+/* Command::SigmoidGate of the recorded IR (crates/beholdd-backend/src/execution.rs:441-445, 1425-1441):
+ * out[i] = in[i] * sigmoid(gate[i]). */
+int32_t bhd_sigmoid_gate(bhd_ctx* ctx, float* out_dev, const float* in_dev, const float* gate_dev, uint64_t n, void* stream);
+
+/* Grows the context's workspace to at least n_bytes now. Nothing may be allocated while a stream is being captured
+ * into a CUDA graph, so a host that records graphs reserves the largest workspace its commands need first. */
+int32_t bhd_workspace_reserve(bhd_ctx* ctx, uint64_t n_bytes);
+
 /* Embedding lookup (forward.rs:954-972): rows ids[i] of `table` decoded to f32, out [n_ids][cols]; an id outside the
  * table is reported through the status word. */
 int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, const int32_t* ids_dev, uint64_t n_ids, float* out_dev,

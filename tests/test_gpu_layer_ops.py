@@ -273,14 +273,8 @@ def test_device_weight_generator_reproduces_the_host_generator(dev):
     assert abs(float(fn.mean())) < 2e-4 and abs(float(fn.std()) - 0.02) < 2e-4
 
 
-def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
-    """A 2-layer qwen3moe-architecture model, teacher-forced: a 5-token prefill and two decode steps against the same
-    model composed from the oracle's operators (crates/beholdd-model/src/qwen3moe/forward.rs:954-972, 1022-1455).
-    Expert indices of every layer exact, logits within tolerance."""
-    import torch
-    from exec_beholdd_b200 import synth
-    from exec_beholdd_b200.qwen3moe import Qwen3MoeConfig, Qwen3MoeModel
-
+def small_model(synth, Qwen3MoeConfig):
+    """A 2-layer qwen3moe-architecture model with seeded host weights."""
     cfg = Qwen3MoeConfig(n_layers=2, dim=512, n_heads=4, n_kv_heads=2, head_dim=128, n_experts=8, top_k=2, expert_ff=256, vocab=300,
                          rope_theta=1.0e6, eps=1e-6, context=16)
     seed, qw, kvw = 99, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
@@ -296,6 +290,19 @@ def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
                                "gate": synth.expert_slabs(seed + l, cfg.n_experts, cfg.expert_ff, cfg.dim, 21),
                                "up": synth.expert_slabs(seed + l, cfg.n_experts, cfg.expert_ff, cfg.dim, 22),
                                "down": synth.expert_slabs(seed + l, cfg.n_experts, cfg.dim, cfg.expert_ff, 23)})
+    return cfg, host
+
+
+def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
+    """A 2-layer qwen3moe-architecture model, teacher-forced: a 5-token prefill and two decode steps against the same
+    model composed from the oracle's operators (crates/beholdd-model/src/qwen3moe/forward.rs:954-972, 1022-1455).
+    Expert indices of every layer exact, logits within tolerance."""
+    import torch
+    from exec_beholdd_b200 import synth
+    from exec_beholdd_b200.qwen3moe import Qwen3MoeConfig, Qwen3MoeModel
+
+    cfg, host = small_model(synth, Qwen3MoeConfig)
+    qw, kvw = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
     model = Qwen3MoeModel.from_host(dev, cfg, host)
     scale = float(1.0 / np.sqrt(np.float32(cfg.head_dim)))
     kc = [np.zeros((cfg.context, cfg.n_kv_heads, cfg.head_dim), np.float32) for _ in range(cfg.n_layers)]
@@ -343,3 +350,56 @@ def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
     out = model.generate_greedy(cuda(ids[:5]), 3)
     assert out.shape[0] == 3 and int(out.min()) >= 0 and int(out.max()) < cfg.vocab
     model.free()
+
+
+def test_model_read_from_a_gguf_file_equals_the_model_given_as_arrays(dev, tmp_path):
+    """GGUF ingestion end to end: the small model written as a GGUF checkpoint (llama.cpp's qwen3moe tensor names,
+    3-D expert tensors), read back through the memory-mapped reader into HBM, gives the bits of the model uploaded
+    from the arrays themselves."""
+    import os
+    import sys
+
+    import torch
+    from exec_beholdd_b200 import synth
+    from exec_beholdd_b200.gguf import GgufFile
+    from exec_beholdd_b200.qwen3moe import Qwen3MoeConfig, Qwen3MoeModel
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import make_moe_block_golden as g
+
+    cfg, host = small_model(synth, Qwen3MoeConfig)
+    A = "qwen3moe"
+    meta = [("general.architecture", 8, A), (f"{A}.block_count", 4, cfg.n_layers), (f"{A}.embedding_length", 4, cfg.dim),
+            (f"{A}.attention.head_count", 4, cfg.n_heads), (f"{A}.attention.head_count_kv", 4, cfg.n_kv_heads),
+            (f"{A}.attention.key_length", 4, cfg.head_dim), (f"{A}.expert_count", 4, cfg.n_experts), (f"{A}.expert_used_count", 4, cfg.top_k),
+            (f"{A}.expert_feed_forward_length", 4, cfg.expert_ff), (f"{A}.attention.layer_norm_rms_epsilon", 6, cfg.eps),
+            (f"{A}.rope.freq_base", 6, cfg.rope_theta)]
+    f32b = lambda a: np.ascontiguousarray(a, dtype="<f4").tobytes()
+    qw, kvw = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    tensors = [("token_embd.weight", 0, [cfg.dim, cfg.vocab], f32b(host["token_embd"])), ("output_norm.weight", 0, [cfg.dim], f32b(host["out_norm"])),
+               ("output.weight", 8, [cfg.dim, cfg.vocab], host["lm_head"].tobytes())]
+    for i, L in enumerate(host["layers"]):
+        P = f"blk.{i}."
+        tensors += [(P + "attn_norm.weight", 0, [cfg.dim], f32b(L["attn_norm"])), (P + "attn_q_norm.weight", 0, [cfg.head_dim], f32b(L["q_norm"])),
+                    (P + "attn_k_norm.weight", 0, [cfg.head_dim], f32b(L["k_norm"])), (P + "ffn_norm.weight", 0, [cfg.dim], f32b(L["ffn_norm"])),
+                    (P + "attn_q.weight", 8, [cfg.dim, qw], L["wq"].tobytes()), (P + "attn_k.weight", 8, [cfg.dim, kvw], L["wk"].tobytes()),
+                    (P + "attn_v.weight", 8, [cfg.dim, kvw], L["wv"].tobytes()), (P + "attn_output.weight", 8, [qw, cfg.dim], L["wo"].tobytes()),
+                    (P + "ffn_gate_inp.weight", 0, [cfg.dim, cfg.n_experts], f32b(L["router"])),
+                    (P + "ffn_gate_exps.weight", 8, [cfg.dim, cfg.expert_ff, cfg.n_experts], L["gate"].tobytes()),
+                    (P + "ffn_up_exps.weight", 8, [cfg.dim, cfg.expert_ff, cfg.n_experts], L["up"].tobytes()),
+                    (P + "ffn_down_exps.weight", 8, [cfg.expert_ff, cfg.dim, cfg.n_experts], L["down"].tobytes())]
+    path = str(tmp_path / "small.gguf")
+    g.write_gguf(path, meta, tensors)
+    ids = cuda(np.array([3, 250, 17, 299, 42], dtype=np.int32))
+    a = Qwen3MoeModel.from_host(dev, cfg, host)
+    want = a.forward(ids, start=0, all_logits=True).clone()
+    a.free()
+    with GgufFile(path) as f:
+        b = Qwen3MoeModel.from_gguf(dev, f, context=cfg.context)
+        import dataclasses
+
+        assert dataclasses.replace(b.cfg, eps=cfg.eps) == cfg and abs(b.cfg.eps - cfg.eps) < 1e-12   # eps travels as an f32
+        got = b.forward(ids, start=0, all_logits=True)
+        dev.check_status()
+        assert torch.equal(got, want)
+        b.free()
