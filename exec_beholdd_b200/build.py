@@ -12,7 +12,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libbeholdd_b200.so")
 
-SOURCES = ["api.cu", "basic_kernels.cu", "moe.cu", "matvec_mma.cu", "matvec_decode.cu", "gemm_q8_tcgen05.cu", "matvec_decode_i8.cu", "moe_grouped_i8.cu", "moe_plan.cu", "moe_rows_f16.cu", "gemm_q8_ts.cu", "peer.cu", "ep.cu", "layer_ops.cu", "synth_kernels.cu"]
+SOURCES = ["api.cu", "basic_kernels.cu", "moe.cu", "matvec_mma.cu", "matvec_decode.cu", "gemm_q8_tcgen05.cu", "matvec_decode_i8.cu", "moe_grouped_i8.cu", "moe_plan.cu", "moe_rows_f16.cu", "gemm_q8_ts.cu", "gemm_q8_persistent.cu", "gemm_q8_pair.cu", "peer.cu", "ep.cu", "layer_ops.cu", "synth_kernels.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared", "-lcuda"]
 

@@ -482,12 +482,16 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     const uint64_t n_elems = uint64_t(M) * K;
     k_f32_to_f16<<<unsigned((n_elems / 4 + 255) / 256), 256, 0, s>>>(x, x16, n_elems, ctx->status_dev);
     BHD_LAUNCHED(ctx, "activation fp16 conversion kernel");
-    if (ctx->gemm_impl == 2) {  // weight operand in tensor memory
-        st = bhd_launch_gemm_q8_ts_dense(ctx, w, slab, x16, y, M, s);
+    // 0: the library's choice (CTA pairs from 256 tokens on, one CTA per tile below), 1: one CTA per tile, 2: one CTA per
+    // tile with the weight operand in tensor memory, 3: CTA pairs, 4: persistent single CTAs.
+    const uint32_t impl = ctx->gemm_impl == 0 ? (M >= 256 ? 3u : 1u) : ctx->gemm_impl;
+    if (impl != 1) {
+        if (impl == 3 && M >= 256) st = bhd_launch_gemm_q8_pair(ctx, w, slab, x16, y, M, s);
+        else if (impl == 2) st = bhd_launch_gemm_q8_ts_dense(ctx, w, slab, x16, y, M, s);
+        else st = bhd_launch_gemm_q8_persistent(ctx, w, slab, x16, y, M, s);
         *handled = st == BHD_OK;
         return st;
     }
-
     EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode);
     CUtensorMap map_w, map_x;
     {
