@@ -42,7 +42,7 @@ struct bhd_ctx {
     uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)
     uint32_t moe_tc_plain;   // 1: the tensor-core grouped kernel with singly rounded fp16 operands in shared memory
     uint32_t router_variant; // tiling of the router-logits kernel for more than 64 positions (0: default)
-    uint32_t gemm_impl;      // prefill matmul: 0 the library's choice, 1 one CTA per tile, 2 the same with the weight operand in tensor memory, 3 CTA pairs, 4 persistent CTAs
+    uint32_t gemm_impl;      // prefill matmul: 0 the library's choice, 1 one CTA per tile, 2 the same with the weight operand in tensor memory, 3 CTA pairs, 4 persistent CTAs, 5 CTA pairs on 512-token tiles
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
 };
@@ -263,7 +263,7 @@ int32_t bhd_launch_gemm_q8_ts_grouped(bhd_ctx* ctx, const bhd_weight* w0, const 
                                       uint32_t n_slots, float* out0, float* out1, float* const* row_dst, const float* col_scale,
                                       cudaStream_t s);
 int32_t bhd_launch_gemm_q8_ts_dense(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, cudaStream_t s);
-int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, cudaStream_t s);
+int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, bool wide, cudaStream_t s);
 int32_t bhd_launch_gemm_q8_persistent(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, cudaStream_t s);
 bool bhd_gemm_q8_ts_usable(const bhd_ctx* ctx, const bhd_weight* w);
 int32_t bhd_launch_gemm_q8_grouped(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const void* hdr, const void* groups,

@@ -43,7 +43,8 @@ constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
 constexpr int B_BYTES = HALF_TOK * SLICE_K * 2; // 16384
 constexpr int THREADS = 16 * 32;
-constexpr int SA = 3, SB = 6;          // weight-tile and token-tile stages
+constexpr int SA = 3;                  // weight-tile stages
+constexpr int SB_BYTES = 6 * B_BYTES;  // token ring: six slices of one 256-token tile, or three of a 512-token tile
 constexpr int DONE = 16;               // "slice done" barriers; more than either ring's depth
 constexpr uint32_t SPIN_LIMIT = 1u << 24;       // polls, roughly a second
 
@@ -202,14 +203,23 @@ struct PairParams {
     uint32_t row_base;   // tensor-map row of the slab's first row
     uint32_t m;          // tokens
     uint32_t k;          // columns
-    uint32_t tok_tiles;  // ceil(M / 256); tile t = (row pair t / tok_tiles, token tile t % tok_tiles)
+    uint32_t tok_tiles;  // ceil(M / tokens per tile); tile t = (row pair t / tok_tiles, token tile t % tok_tiles)
     uint32_t tiles;      // row pairs * token tiles
 };
 
+// WIDE = false: 256-token tiles, one issuer, the two accumulators alternate between consecutive tiles (the write-back
+// of one tile overlaps the MMAs of the next). WIDE = true: 512-token tiles, every converted weight slice is used
+// twice: two issuer threads (warps 1 and 11) each own one accumulator and one 256-token half of the tile, so the
+// per-slice cost of an issuer (two barrier reads, four MMAs, a commit: about as long as the four MMAs run) is
+// paid in parallel and half as much weight conversion is done per flop; the write-back is not overlapped.
+template <bool WIDE>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_constant__ CUtensorMap tmap_w,
                                                              const __grid_constant__ CUtensorMap tmap_x, const PairParams p) {
+    constexpr uint32_t TOKT = WIDE ? 2 * TOK : TOK;              // tokens per tile
+    constexpr uint32_t BS_BYTES = WIDE ? 2 * B_BYTES : B_BYTES;  // token bytes per stage and CTA
+    constexpr uint32_t SB = SB_BYTES / BS_BYTES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[SA], b_full[SB], done[DONE], tmem_full[2], tmem_empty[2];
+    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[SA], b_full[6], done[DONE], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -225,12 +235,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
         for (int i = 0; i < 2; ++i) {
             mbar_init(&pk_full[i], 1);
             mbar_init(&pk_empty[i], 8);
-            mbar_init(&tmem_full[i], 1);
-            mbar_init(&tmem_empty[i], 8);     // four write-back warps of each CTA
+            mbar_init(&tmem_full[i], WIDE ? 2 : 1);   // WIDE: both issuers (only barrier 0 is used)
+            mbar_init(&tmem_empty[i], 8);             // four write-back warps of each CTA
         }
         for (int i = 0; i < SA; ++i) mbar_init(&a_full[i], 16);  // eight converter warps of each CTA
-        for (int i = 0; i < SB; ++i) mbar_init(&b_full[i], 1);   // one arrival (with the byte count of both halves)
-        for (int i = 0; i < DONE; ++i) mbar_init(&done[i], 1);
+        for (int i = 0; i < int(SB); ++i) mbar_init(&b_full[i], 1);   // one arrival (with the byte count of both CTAs' loads)
+        for (int i = 0; i < DONE; ++i) mbar_init(&done[i], WIDE ? 2 : 1);  // one commit per issuer
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -265,38 +275,48 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
         if (lane == 0) {
             uint32_t g = 0;
             for (uint32_t i = 0; i < n_my && !aborted(); ++i) {
-                const uint32_t t = pair + i * n_pairs, m0 = (t % p.tok_tiles) * TOK + rank * HALF_TOK;
+                const uint32_t t = pair + i * n_pairs, m_tile = (t % p.tok_tiles) * TOKT, m0 = m_tile + rank * HALF_TOK;
+                const bool two = WIDE && m_tile + TOK < p.m;   // the tile's second 256 tokens exist
                 for (uint32_t it = 0; it < slices; ++it, ++g) {
                     const uint32_t s = g % SB;
                     if (aborted() || (g >= SB && !slice_done(g - SB))) { give_up(); break; }
-                    if (rank == 0) mbar_arrive_expect_tx(&b_full[s], 2 * B_BYTES);
-                    tma_load_2d_pair(b_addr + s * B_BYTES, &tmap_x, int(it * SLICE_K), int(m0), in_cta(smem_u32(&b_full[s]), 0));
+                    const uint32_t bar = in_cta(smem_u32(&b_full[s]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&b_full[s], (two ? 4 : 2) * B_BYTES);
+                    tma_load_2d_pair(b_addr + s * BS_BYTES, &tmap_x, int(it * SLICE_K), int(m0), bar);
+                    if (two) tma_load_2d_pair(b_addr + s * BS_BYTES + B_BYTES, &tmap_x, int(it * SLICE_K), int(m0 + TOK), bar);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA issuer (even CTA only): tile i accumulates into buffer i & 1 of both CTAs' tensor memory ----
+    } else if (warp == 1 || (WIDE && warp == 11)) {
+        // ---- MMA issuers (even CTA only). Narrow: warp 1, tile i accumulates into buffer i & 1 of both CTAs' tensor
+        // memory. Wide: warp 1 owns accumulator 0 and the tile's first 256 tokens, warp 11 accumulator 1 and the rest. ----
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = umma_idesc(2 * TILE_N, TOK);
+            const uint32_t which = warp == 1 ? 0u : 1u;
             uint32_t g = 0;
             bool ok = true;
             for (uint32_t i = 0; i < n_my && ok; ++i) {
-                const uint32_t buf = i & 1, acc = tmem_base + buf * TOK;
-                if (i >= 2) {  // both CTAs' write-back of tile i - 2 must have emptied this accumulator
-                    if (aborted() || !mbar_wait(&tmem_empty[buf], ((i >> 1) & 1) ^ 1)) { give_up(); break; }
+                const uint32_t buf = WIDE ? which : (i & 1), acc = tmem_base + buf * TOK;
+                const uint32_t t = pair + i * n_pairs, m_tile = (t % p.tok_tiles) * TOKT;
+                const bool mine = !WIDE || which == 0 || m_tile + TOK < p.m;   // this issuer's tokens exist
+                if (WIDE ? i >= 1 : i >= 2) {  // both CTAs' write-back must have emptied the accumulator
+                    const uint32_t par = WIDE ? ((i - 1) & 1) : (((i >> 1) & 1) ^ 1);
+                    if (aborted() || !mbar_wait(&tmem_empty[WIDE ? 0 : buf], par)) { give_up(); break; }
                     tc_fence_after();
                 }
                 for (uint32_t it = 0; it < slices; ++it, ++g) {
                     const uint32_t sa = g % SA, sb = g % SB;
                     if (!mbar_wait(&b_full[sb], (g / SB) & 1) || !mbar_wait(&a_full[sa], (g / SA) & 1)) { give_up(); ok = false; break; }
                     tc_fence_after();
-                    const uint64_t da = umma_desc(a_addr + sa * A_BYTES), db = umma_desc(b_addr + sb * B_BYTES);
+                    if (mine) {
+                        const uint64_t da = umma_desc(a_addr + sa * A_BYTES), db = umma_desc(b_addr + sb * BS_BYTES + (WIDE ? which * B_BYTES : 0u));
 #pragma unroll
-                    for (uint32_t k16 = 0; k16 < 4; ++k16)  // 32 bytes (16 fp16) further along the swizzled row per step
-                        tc_mma_pair(acc, da + 2 * k16, db + 2 * k16, idesc, (it | k16) ? 1u : 0u);
-                    tc_commit_pair(&done[g % DONE]);  // both CTAs: the MMAs have finished reading slice g's stages
+                        for (uint32_t k16 = 0; k16 < 4; ++k16)  // 32 bytes (16 fp16) further along the swizzled row per step
+                            tc_mma_pair(acc, da + 2 * k16, db + 2 * k16, idesc, (it | k16) ? 1u : 0u);
+                    }
+                    tc_commit_pair(&done[g % DONE]);  // both CTAs: this issuer's MMAs have finished reading slice g's stages
                 }
-                if (ok) tc_commit_pair(&tmem_full[buf]);  // both CTAs: every MMA of the tile is complete
+                if (ok) tc_commit_pair(&tmem_full[WIDE ? 0 : buf]);  // both CTAs: every MMA of this issuer for the tile is complete
             }
         }
     } else if (warp >= 2 && warp < 10) {
@@ -363,12 +383,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
         // ---- write-back of this CTA's 128 rows: TMEM lane = weight row, column = token; warp % 4 = its lane quarter ----
         const uint32_t q = uint32_t(warp) & 3u;
         for (uint32_t i = 0; i < n_my; ++i) {
-            const uint32_t t = pair + i * n_pairs, n0 = (t / p.tok_tiles) * (2 * TILE_N) + rank * TILE_N, m0 = (t % p.tok_tiles) * TOK;
-            const uint32_t buf = i & 1;
-            if (aborted() || !mbar_wait_sleep(&tmem_full[buf], (i >> 1) & 1)) { give_up(); break; }
+            const uint32_t t = pair + i * n_pairs, n0 = (t / p.tok_tiles) * (2 * TILE_N) + rank * TILE_N, m0 = (t % p.tok_tiles) * TOKT;
+            const uint32_t buf = WIDE ? 0u : (i & 1), par = WIDE ? (i & 1) : ((i >> 1) & 1);
+            if (aborted() || !mbar_wait_sleep(&tmem_full[buf], par)) { give_up(); break; }
             tc_fence_after();
             const uint32_t n = n0 + q * 32 + lane;
-            for (uint32_t col = 0; col < TOK; col += 32) {
+            for (uint32_t col = 0; col < TOKT; col += 32) {
                 if (m0 + col >= p.m) break;            // uniform across the warp
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((q * 32u) << 16) + buf * TOK + col, r);
@@ -398,18 +418,22 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 }  // namespace
 
 // Dense prefill on CTA pairs, M >= 256: Y[m][n] = sum_k fp16(X[m][k]) * fp16(W[n][k]); x16 is the fp16 copy of X.
-int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, cudaStream_t s) {
+// wide: 512-token tiles with two issuers (see the kernel); else 256-token tiles with an overlapped write-back.
+int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, bool wide,
+                                cudaStream_t s) {
     const uint32_t K = uint32_t(w->cols), N = uint32_t(w->rows);
     static int sm_count[BHD_MAX_DEVICES] = {};
     static bhd_once_per_device once;
-    const size_t dyn = 1024 + 2 * size_t(PACK_BYTES) + size_t(SA) * A_BYTES + size_t(SB) * B_BYTES;
+    const size_t dyn = 1024 + 2 * size_t(PACK_BYTES) + size_t(SA) * A_BYTES + size_t(SB_BYTES);
     if (once.pending(ctx)) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
         BHD_CUDA(ctx, cudaDeviceGetAttribute(&sm_count[ctx->device], cudaDevAttrMultiProcessorCount, ctx->device), "reading the SM count");
         once.mark(ctx);
     }
     const uint32_t sms = uint32_t(sm_count[ctx->device] > 1 ? sm_count[ctx->device] : 148);
-    const uint32_t row_pairs = (N + 2 * TILE_N - 1) / (2 * TILE_N), tok_tiles = (M + TOK - 1) / TOK, tiles = row_pairs * tok_tiles;
+    const uint32_t tokt = wide ? 2 * TOK : TOK;
+    const uint32_t row_pairs = (N + 2 * TILE_N - 1) / (2 * TILE_N), tok_tiles = (M + tokt - 1) / tokt, tiles = row_pairs * tok_tiles;
     const uint32_t n_pairs = tiles < sms / 2 ? tiles : sms / 2;
 
     EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(ctx->tmap_encode);
@@ -453,7 +477,8 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    if (wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    else BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
     ctx->launches += 1;
     return BHD_OK;
 }

@@ -482,11 +482,23 @@ int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t s
     const uint64_t n_elems = uint64_t(M) * K;
     k_f32_to_f16<<<unsigned((n_elems / 4 + 255) / 256), 256, 0, s>>>(x, x16, n_elems, ctx->status_dev);
     BHD_LAUNCHED(ctx, "activation fp16 conversion kernel");
-    // 0: the library's choice (CTA pairs from 256 tokens on, one CTA per tile below), 1: one CTA per tile, 2: one CTA per
-    // tile with the weight operand in tensor memory, 3: CTA pairs, 4: persistent single CTAs.
-    const uint32_t impl = ctx->gemm_impl == 0 ? (M >= 256 ? 3u : 1u) : ctx->gemm_impl;
+    // 0: the library's choice, 1: one CTA per tile, 2: the same with the weight operand in tensor memory, 3: CTA pairs on
+    // 256-token tiles, 4: persistent single CTAs, 5: CTA pairs on 512-token tiles.
+    // The choice: pairs from 256 tokens on. A 512-token tile takes about 1.6 times as long as a 256-token tile (its
+    // write-back is not overlapped) for twice the work, and tiles are dealt to the SM pairs in whole rounds.
+    uint32_t impl = ctx->gemm_impl;
+    if (impl == 0) {
+        impl = 1;
+        if (M >= 256) {
+            int sms = 148;
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device);
+            const uint32_t pairs = uint32_t(sms > 1 ? sms / 2 : 1), row_pairs = (N + 255) / 256;
+            const uint32_t rounds_narrow = (row_pairs * ((M + 255) / 256) + pairs - 1) / pairs, rounds_wide = (row_pairs * ((M + 511) / 512) + pairs - 1) / pairs;
+            impl = (M > 256 && 1.6f * float(rounds_wide) <= float(rounds_narrow)) ? 5u : 3u;
+        }
+    }
     if (impl != 1) {
-        if (impl == 3 && M >= 256) st = bhd_launch_gemm_q8_pair(ctx, w, slab, x16, y, M, s);
+        if ((impl == 3 || impl == 5) && M >= 256) st = bhd_launch_gemm_q8_pair(ctx, w, slab, x16, y, M, impl == 5, s);
         else if (impl == 2) st = bhd_launch_gemm_q8_ts_dense(ctx, w, slab, x16, y, M, s);
         else st = bhd_launch_gemm_q8_persistent(ctx, w, slab, x16, y, M, s);
         *handled = st == BHD_OK;

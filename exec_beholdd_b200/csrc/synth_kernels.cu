@@ -23,6 +23,19 @@ __device__ __forceinline__ double uniform01(uint64_t key, uint64_t index) {  // 
     return double(mix64(key + (index + 1) * GAMMA) >> 11) * (1.0 / 9007199254740992.0);
 }
 
+// binary16 bits of a positive double in the normal binary16 range, rounded to nearest even, in integer arithmetic
+// (the same rounding as the host generator's float64 -> float16 cast).
+__device__ __forceinline__ uint16_t f16_bits_of(double d) {
+    const uint64_t b = uint64_t(__double_as_longlong(d));
+    int e = int((b >> 52) & 0x7ff) - 1023 + 15;
+    const uint64_t m = b & ((1ull << 52) - 1);
+    uint64_t keep = m >> 42;
+    const uint64_t rest = m & ((1ull << 42) - 1), half = 1ull << 41;
+    if (rest > half || (rest == half && (keep & 1))) ++keep;
+    if (keep == 1024) { keep = 0; ++e; }
+    return uint16_t((uint32_t(e) << 10) | uint32_t(keep));
+}
+
 // Slab s uses field streams (stream0 + s * stream_step) * 16 + 1 (scales) and * 16 + 2 (quants); block indices restart per slab.
 __global__ void k_fill_q8_0(uint8_t* __restrict__ out, uint64_t blocks_per_slab, uint64_t n_slabs, uint64_t seed, uint64_t stream0,
                             uint64_t stream_step) {
@@ -33,7 +46,7 @@ __global__ void k_fill_q8_0(uint8_t* __restrict__ out, uint64_t blocks_per_slab,
     const uint64_t key_d = stream_key(seed, stream * 16 + 1), key_q = stream_key(seed, stream * 16 + 2);
     uint8_t* blk = out + i * 34;
     const double d = 1e-3 + (1e-2 - 1e-3) * uniform01(key_d, b);
-    const uint16_t dbits = __half_as_ushort(__double2half(d));
+    const uint16_t dbits = f16_bits_of(d);
     blk[0] = uint8_t(dbits & 0xff);
     blk[1] = uint8_t(dbits >> 8);
     for (int j = 0; j < 32; ++j) {

@@ -322,7 +322,8 @@ int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one
  *                                (faster, about 1e-3 less accurate); 0: exact hi + lo operands (default).
  *   BHD_OPTION_GEMM_IMPL         prefill matmul: 0 = the library's choice (persistent CTA pairs from 256 tokens on, one CTA
  *                                per tile below), 1 = one CTA per tile, 2 = one CTA per tile with the weight operand in
- *                                tensor memory, 3 = persistent CTA pairs (tcgen05 cta_group::2), 4 = persistent single CTAs.
+ *                                tensor memory, 3 = persistent CTA pairs (tcgen05 cta_group::2) on 256-token tiles,
+ *                                4 = persistent single CTAs, 5 = CTA pairs on 512-token tiles with two MMA issuers.
  *   BHD_OPTION_ROUTER_TILING     router-logits kernel for more than 64 positions: 0 = 32 positions per CTA and 3
  *                                tiles in flight, 1 = 32 and 5, 2 = 16 and 6, 3 = 8 and 7 (the small-batch tiling). */
 #define BHD_OPTION_MOE_TC_MIN_CLASS 1u

@@ -119,6 +119,39 @@ def test_prefill_matmul_full_size_against_oracle_sample(dev, oracle, m, n, k):
     w.free()
 
 
+@pytest.mark.parametrize("m,n,k", [(700, 520, 2048), (256, 130, 1024), (1300, 256, 3072)])
+def test_every_prefill_kernel_form_gives_the_same_bits(dev, oracle, m, n, k):
+    """The prefill matmul exists as one CTA per tile, persistent CTAs, and persistent CTA pairs on 256- and 512-token
+    tiles (the library chooses by shape). Ragged shapes (a last row pair with few rows, a last token tile with few
+    tokens): every form against the oracle on a sample; the forms that add a column's products in one chain (all but
+    the one-CTA-per-tile form, which keeps even and odd slices in two accumulators) are bit-identical."""
+    import torch
+    from exec_beholdd_b200 import Weight, synth
+
+    packed = synth.q8_0_matrix(151, n, k)
+    x = synth.activations(153, (m, k), outliers=True)
+    sample = np.unique(np.minimum(np.concatenate([np.arange(0, m, max(1, m // 12)), [255, 256, m - 1]]), m - 1))
+    want = oracle.matvec_batch(packed, 8, n, k, x[sample])
+    w = dev.upload_weight(Weight(packed, 8, n, k))
+    xd = cuda(x)
+    outs = {}
+    try:
+        for impl in (1, 3, 4, 5, 0):
+            assert dev.lib.bhd_debug_option(dev.ctx, 3, impl) == 0
+            y = torch.full((m, n), float("nan"), device="cuda")
+            dev.matmul_resident(w, xd, y)
+            dev.check_status()
+            outs[impl] = y.cpu().numpy()
+            assert np.isfinite(outs[impl]).all()
+            assert max_rel_err(outs[impl][sample], want) <= TOL, impl
+    finally:
+        dev.lib.bhd_debug_option(dev.ctx, 3, 0)
+    for impl in (4, 5, 0):
+        assert np.array_equal(outs[impl].view(np.uint32), outs[3].view(np.uint32)), impl
+    assert max_rel_err(outs[1], outs[3]) <= 1e-4
+    w.free()
+
+
 def moe_inputs(seed, n_experts, dim, ff, T, tails):
     from exec_beholdd_b200 import synth
 
