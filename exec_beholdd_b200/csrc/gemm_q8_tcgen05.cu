@@ -42,7 +42,7 @@ constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
 // per weight row) that take alternating slices; the first group is also the epilogue.
 // after the converters: one warp that requests the activation tiles and the second MMA issuer
 __host__ __device__ constexpr int gemm_threads(int ng) { return 64 + 128 * ng + 64; }
-constexpr uint32_t SPIN_LIMIT = 1u << 20;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -60,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
             : "r"(addr), "r"(parity)
