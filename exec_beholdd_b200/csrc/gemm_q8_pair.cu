@@ -46,6 +46,7 @@ constexpr int THREADS = 16 * 32;
 constexpr int SA = 3;                  // weight-tile stages
 constexpr int SB_BYTES = 6 * B_BYTES;  // token ring: six slices of one 256-token tile, or three of a 512-token tile
 constexpr int DONE = 16;               // "slice done" barriers; more than either ring's depth
+constexpr int FULL = 6;                // "slice ready" barriers; at least either ring's depth
 constexpr uint32_t SPIN_LIMIT = 1u << 24;       // polls, roughly a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
     constexpr uint32_t BS_BYTES = WIDE ? 2 * B_BYTES : B_BYTES;  // token bytes per stage and CTA
     constexpr uint32_t SB = SB_BYTES / BS_BYTES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t pk_full[2], pk_empty[2], a_full[SA], b_full[6], done[DONE], tmem_full[2], tmem_empty[2];
+    __shared__ uint64_t pk_full[2], pk_empty[2], full[FULL], done[DONE], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -238,8 +239,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
             mbar_init(&tmem_full[i], WIDE ? 2 : 1);   // WIDE: both issuers (only barrier 0 is used)
             mbar_init(&tmem_empty[i], 8);             // four write-back warps of each CTA
         }
-        for (int i = 0; i < SA; ++i) mbar_init(&a_full[i], 16);  // eight converter warps of each CTA
-        for (int i = 0; i < int(SB); ++i) mbar_init(&b_full[i], 1);   // one arrival (with the byte count of both CTAs' loads)
+        // Slice g is ready when the sixteen converter warps of the pair have arrived and the token bytes of both CTAs have
+        // landed: ONE barrier per slice (full[g % FULL]) for both rings, so the issuer reads one barrier per slice. No
+        // arrival for slice g + FULL can come before slice g's phase is complete: both producers first wait for a slice
+        // >= g to be done (FULL is at least either ring's depth), and its MMAs are issued after the phase completed.
+        for (int i = 0; i < FULL; ++i) mbar_init(&full[i], 17);
         for (int i = 0; i < DONE; ++i) mbar_init(&done[i], WIDE ? 2 : 1);  // one commit per issuer
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -280,8 +284,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                 for (uint32_t it = 0; it < slices; ++it, ++g) {
                     const uint32_t s = g % SB;
                     if (aborted() || (g >= SB && !slice_done(g - SB))) { give_up(); break; }
-                    const uint32_t bar = in_cta(smem_u32(&b_full[s]), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(&b_full[s], (two ? 4 : 2) * B_BYTES);
+                    const uint32_t bar = in_cta(smem_u32(&full[g % FULL]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&full[g % FULL], (two ? 4 : 2) * B_BYTES);
                     tma_load_2d_pair(b_addr + s * BS_BYTES, &tmap_x, int(it * SLICE_K), int(m0), bar);
                     if (two) tma_load_2d_pair(b_addr + s * BS_BYTES + B_BYTES, &tmap_x, int(it * SLICE_K), int(m0 + TOK), bar);
                 }
@@ -306,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                 }
                 for (uint32_t it = 0; it < slices; ++it, ++g) {
                     const uint32_t sa = g % SA, sb = g % SB;
-                    if (!mbar_wait(&b_full[sb], (g / SB) & 1) || !mbar_wait(&a_full[sa], (g / SA) & 1)) { give_up(); ok = false; break; }
+                    if (!mbar_wait(&full[g % FULL], (g / FULL) & 1)) { give_up(); ok = false; break; }
                     tc_fence_after();
                     if (mine) {
                         const uint64_t da = umma_desc(a_addr + sa * A_BYTES), db = umma_desc(b_addr + sb * BS_BYTES + (WIDE ? which * B_BYTES : 0u));
@@ -372,7 +376,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(in_cta(smem_u32(&a_full[s]), 0));  // one arrival per converter warp
+                    if (lane == 0) mbar_arrive_cluster(in_cta(smem_u32(&full[g % FULL]), 0));  // one arrival per converter warp
                     ++g;
                 }
                 __syncwarp();
