@@ -409,7 +409,7 @@ def bench_moe_single(dev, torch, T, steps, warmup):
 def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128):
     """The full-forward configuration: a random-init 48-layer Qwen3-30B-A3B-architecture model in Q8_0, a 512-token
     prefill of uniform random token ids and 128 greedy decode steps with a KV cache; with several ranks every rank
-    runs its own sequence and the experts are split over the ranks. Device-timed; eager launches from the host."""
+    runs its own sequence and the experts are split over the ranks. Device-timed."""
     from exec_beholdd_b200 import synth
     from exec_beholdd_b200.qwen3moe import Qwen3MoeConfig, Qwen3MoeModel
 
@@ -420,7 +420,8 @@ def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128)
     build_s = time.perf_counter() - t0
     ids = torch.from_numpy((synth.u64(SEED + 50 + rank, 3, prompt_len) % np.uint64(cfg.vocab)).astype(np.int32)).cuda()
     model.forward(ids[:64], start=0)                      # warm-up: sizes the workspace, loads the kernels
-    model.forward(ids[64:65], start=64)
+    warm = model.forward(ids[64:65], start=64)
+    model.decode_greedy(warm, 3)                          # captures the decode step's CUDA graph
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -428,11 +429,7 @@ def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128)
     ev[0].record()
     logits = model.forward(ids, start=0)
     ev[1].record()
-    out = torch.empty(n_new, dtype=torch.int32, device="cuda")
-    for i in range(n_new):
-        out[i] = torch.argmax(logits).to(torch.int32)
-        if i + 1 < n_new:
-            logits = model.forward(out[i:i + 1])
+    out, logits = model.decode_greedy(logits, n_new)      # one graph launch per token
     ev[2].record()
     torch.cuda.synchronize()
     prefill_s, decode_s = ev[0].elapsed_time(ev[1]) / 1e3, ev[1].elapsed_time(ev[2]) / 1e3
@@ -448,7 +445,8 @@ def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128)
            "prefill_tokens_per_gpu": prompt_len, "decode_steps": n_new, "prefill_ms": prefill_s * 1e3,
            "prefill_tokens_per_s": world * prompt_len / prefill_s, "decode_ms_per_token": decode_s / (n_new - 1) * 1e3,
            "decode_tokens_per_s": world * (n_new - 1) / decode_s, "weights_generated_in_s": build_s, "logits_finite": finite,
-           "generated_ids_head": out[:8].cpu().tolist(), "launch": "eager, host-paced"}
+           "generated_ids_head": out[:8].cpu().tolist(),
+           "launch": "prefill: eager launches; decode: one CUDA graph launch per step (captured during warm-up)"}
     if status_error:
         res["status_error"] = status_error
     if world > 1:

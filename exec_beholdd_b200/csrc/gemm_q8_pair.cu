@@ -12,7 +12,7 @@
 // a token tile needs to stay off the critical path.
 //
 // Schedule as in gemm_q8_persistent.cu: one cluster per SM pair walks a list of tiles; producers run ahead across
-// tile boundaries; two accumulators in tensor memory so that four write-back warps per CTA drain one tile while
+// tile boundaries; two accumulators in tensor memory so that eight write-back warps per CTA drain one tile while
 // the MMAs of the next fill the other; waits on the critical path poll with mbarrier.test_wait. The two rings
 // are released by ONE tcgen05.commit per slice onto a ring of "slice done" barriers (multicast to both CTAs)
 // that every producer watches at its own distance.
@@ -42,7 +42,7 @@ constexpr int PACK_ROW = 272;          // packed bytes per row per chunk
 constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
 constexpr int B_BYTES = HALF_TOK * SLICE_K * 2; // 16384
-constexpr int THREADS = 16 * 32;
+constexpr int THREADS = 20 * 32;       // warps 0-11: producers, issuers, converters; warps 12-19: write-back
 constexpr int SA = 3;                  // weight-tile stages
 constexpr int SB_BYTES = 6 * B_BYTES;  // token ring: six slices of one 256-token tile, or three of a 512-token tile
 constexpr int DONE = 16;               // "slice done" barriers; more than either ring's depth
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
             mbar_init(&pk_full[i], 1);
             mbar_init(&pk_empty[i], 8);
             mbar_init(&tmem_full[i], WIDE ? 2 : 1);   // WIDE: both issuers (only barrier 0 is used)
-            mbar_init(&tmem_empty[i], 8);             // four write-back warps of each CTA
+            mbar_init(&tmem_empty[i], 16);            // eight write-back warps of each CTA
         }
         // Slice g is ready when the sixteen converter warps of the pair have arrived and the token bytes of both CTAs have
         // landed: ONE barrier per slice (full[g % FULL]) for both rings, so the issuer reads one barrier per slice. No
@@ -384,15 +384,17 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
             }
         }
     } else if (warp >= 12) {
-        // ---- write-back of this CTA's 128 rows: TMEM lane = weight row, column = token; warp % 4 = its lane quarter ----
-        const uint32_t q = uint32_t(warp) & 3u;
+        // ---- write-back of this CTA's 128 rows: TMEM lane = weight row, column = token. A warp may read the lane quarter
+        // warp % 4; the two warps of a quarter each take half of the tile's columns. ----
+        const uint32_t q = uint32_t(warp) & 3u, part = uint32_t(warp - 12) >> 2;
+        constexpr uint32_t COLS = TOKT / 2;   // columns per warp
         for (uint32_t i = 0; i < n_my; ++i) {
             const uint32_t t = pair + i * n_pairs, n0 = (t / p.tok_tiles) * (2 * TILE_N) + rank * TILE_N, m0 = (t % p.tok_tiles) * TOKT;
             const uint32_t buf = WIDE ? 0u : (i & 1), par = WIDE ? (i & 1) : ((i >> 1) & 1);
             if (aborted() || !mbar_wait_sleep(&tmem_full[buf], par)) { give_up(); break; }
             tc_fence_after();
             const uint32_t n = n0 + q * 32 + lane;
-            for (uint32_t col = 0; col < TOKT; col += 32) {
+            for (uint32_t col = part * COLS; col < (part + 1) * COLS; col += 32) {
                 if (m0 + col >= p.m) break;            // uniform across the warp
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((q * 32u) << 16) + buf * TOK + col, r);

@@ -45,11 +45,12 @@ __global__ void __launch_bounds__(256) k_rmsnorm(float* __restrict__ y, const fl
 }
 
 // x [n_positions][vectors_per_position][2 * n_pairs]; cos / sin [n_positions][n_pairs].
+// With pos_dev, the first position's table row is read from device memory (a decode step replayed as a CUDA graph).
 __global__ void k_rope(float* __restrict__ x, const float* __restrict__ cos, const float* __restrict__ sin, uint64_t n_vectors,
-                       uint32_t vectors_per_position, uint32_t n_pairs, int layout, int inverse) {
+                       uint32_t vectors_per_position, uint32_t n_pairs, int layout, int inverse, const int32_t* __restrict__ pos_dev) {
     const uint64_t idx = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
     if (idx >= n_vectors * n_pairs) return;
-    const uint64_t vec = idx / n_pairs, i = idx - vec * n_pairs, pos = vec / vectors_per_position;
+    const uint64_t vec = idx / n_pairs, i = idx - vec * n_pairs, pos = vec / vectors_per_position + (pos_dev ? uint64_t(*pos_dev) : 0ull);
     float* xv = x + vec * 2 * n_pairs;
     const uint64_t ia = layout == 0 ? 2 * i : i, ib = layout == 0 ? 2 * i + 1 : i + n_pairs;
     const float a = xv[ia], b = xv[ib];
@@ -61,10 +62,19 @@ __global__ void k_rope(float* __restrict__ x, const float* __restrict__ cos, con
 // One CTA per (query position, head). scores in shared memory (f32, one per visible key position).
 __global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
                                                    const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_heads,
-                                                   uint32_t n_kv_heads, uint32_t head_dim, float scale) {
+                                                   uint32_t n_kv_heads, uint32_t head_dim, float scale, const int32_t* __restrict__ start_dev,
+                                                   uint32_t max_positions, uint32_t* __restrict__ status) {
     extern __shared__ float scores[];
     __shared__ float s_max, s_inv;
     const uint32_t qp = blockIdx.x, head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
+    if (start_dev) {  // the query's position is read from device memory; the score buffer holds max_positions entries
+        const int32_t sd = *start_dev;
+        if (sd < 0 || uint32_t(sd) + qp >= max_positions) {
+            if (threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+            return;
+        }
+        query_start = uint32_t(sd);
+    }
     const uint32_t visible = query_start + qp + 1;
     const float* query = q + (uint64_t(qp) * n_heads + head) * head_dim;
     // scores: f64 dot product in element order, scaled in f64, rounded to f32
@@ -123,6 +133,18 @@ __global__ void k_sigmoid_gate(float* __restrict__ out, const float* __restrict_
     out[i] = __fmul_rn(in[i], sig);
 }
 
+// dst[*pos_dev][0 .. row_floats) = src: appends one row to a cache at a position read from device memory.
+__global__ void k_store_row_at(float* __restrict__ dst, const float* __restrict__ src, const int32_t* __restrict__ pos_dev, uint64_t row_floats,
+                               uint64_t max_rows, uint32_t* __restrict__ status) {
+    const int32_t pos = *pos_dev;
+    if (pos < 0 || uint64_t(pos) >= max_rows) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+        return;
+    }
+    const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (i < row_floats) dst[uint64_t(pos) * row_floats + i] = src[i];
+}
+
 template <uint32_t KIND>
 __global__ void k_embedding_rows(const uint8_t* __restrict__ w, uint64_t row_bytes, uint64_t rows, uint64_t cols, const int32_t* __restrict__ ids,
                                  float* __restrict__ out, uint32_t* __restrict__ status) {
@@ -161,8 +183,60 @@ extern "C" int32_t bhd_rope(bhd_ctx* ctx, float* x_dev, const float* cos_dev, co
     bhd_device_guard guard(ctx);
     const uint64_t n = n_vectors * n_pairs;
     k_rope<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(x_dev, cos_dev, sin_dev, n_vectors, vectors_per_position, n_pairs, layout,
-                                                                         inverse);
+                                                                         inverse, nullptr);
     BHD_LAUNCHED(ctx, "rotary embedding kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_rope_at(bhd_ctx* ctx, float* x_dev, const float* cos_table_dev, const float* sin_table_dev, const int32_t* pos_dev,
+                               uint32_t n_vectors, uint32_t n_pairs, int32_t layout, int32_t inverse, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (layout != 0 && layout != 1) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: layout must be 0 (interleaved) or 1 (split half)");
+    if (n_vectors == 0 || n_pairs == 0) return BHD_OK;
+    if (!x_dev || !cos_table_dev || !sin_table_dev || !pos_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: null buffer");
+    bhd_device_guard guard(ctx);
+    const uint64_t n = uint64_t(n_vectors) * n_pairs;
+    k_rope<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(x_dev, cos_table_dev, sin_table_dev, n_vectors, n_vectors, n_pairs, layout,
+                                                                         inverse, pos_dev);
+    BHD_LAUNCHED(ctx, "rotary embedding kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_store_row_at(bhd_ctx* ctx, float* dst_dev, const float* src_dev, const int32_t* pos_dev, uint64_t row_floats,
+                                    uint64_t max_rows, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (row_floats == 0) return BHD_OK;
+    if (!dst_dev || !src_dev || !pos_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "store_row_at: null buffer");
+    if (row_floats > (1ull << 38)) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: row too long");
+    bhd_device_guard guard(ctx);
+    k_store_row_at<<<unsigned((row_floats + 255) / 256), 256, 0, cudaStream_t(stream)>>>(dst_dev, src_dev, pos_dev, row_floats, max_rows,
+                                                                                          ctx->status_dev);
+    BHD_LAUNCHED(ctx, "cache append kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_incremental_attention_at(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev,
+                                                const float* v_cache_dev, const int32_t* pos_dev, uint64_t max_positions, uint32_t n_heads,
+                                                uint32_t n_kv_heads, uint32_t head_dim, float scale, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (max_positions == 0) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention requires at least one cached position");
+    if (n_heads == 0 || n_kv_heads == 0 || head_dim == 0 || n_heads % n_kv_heads != 0)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention got heads=%u kv_heads=%u head_dim=%u", n_heads, n_kv_heads, head_dim);
+    if (!isfinite(scale) || scale <= 0.0f)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: incremental causal attention scale must be positive and finite, got %g", double(scale));
+    if (n_heads > 65535u || max_positions > (200u * 1024u) / 4u)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: attention over %llu positions and %u heads is beyond this kernel",
+                        (unsigned long long)max_positions, n_heads);
+    if (!out_dev || !q_dev || !k_cache_dev || !v_cache_dev || !pos_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "attention: null buffer");
+    bhd_device_guard guard(ctx);
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+        once.mark(ctx);
+    }
+    k_attention<<<dim3(1, n_heads), 128, size_t(max_positions) * sizeof(float), cudaStream_t(stream)>>>(
+        out_dev, q_dev, k_cache_dev, v_cache_dev, 0u, n_heads, n_kv_heads, head_dim, scale, pos_dev, uint32_t(max_positions), ctx->status_dev);
+    BHD_LAUNCHED(ctx, "attention kernel");
     return BHD_OK;
 }
 
@@ -196,7 +270,7 @@ extern "C" int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const
     }
     k_attention<<<dim3(unsigned(n_query_positions), n_heads), 128, smem, cudaStream_t(stream)>>>(out_dev, q_dev, k_cache_dev, v_cache_dev,
                                                                                                   uint32_t(query_start), n_heads, n_kv_heads,
-                                                                                                  head_dim, scale);
+                                                                                                  head_dim, scale, nullptr, 0u, ctx->status_dev);
     BHD_LAUNCHED(ctx, "attention kernel");
     return BHD_OK;
 }

@@ -230,6 +230,23 @@ int32_t bhd_sigmoid_gate(bhd_ctx* ctx, float* out_dev, const float* in_dev, cons
  * into a CUDA graph, so a host that records graphs reserves the largest workspace its commands need first. */
 int32_t bhd_workspace_reserve(bhd_ctx* ctx, uint64_t n_bytes);
 
+/* The same operators for a decode step replayed as a CUDA graph, where the position may not be a launch parameter:
+ * it is read from device memory (*pos_dev, an int32 the host or a kernel advances between replays). No counterpart in
+ * the reference, which records one batch per position (execution.rs:1093-1099).
+ *   bhd_rope_at                  rotates n_vectors vectors of the one position *pos_dev with row *pos_dev of the tables
+ *                                [max_positions][n_pairs]
+ *   bhd_store_row_at             dst[*pos_dev][0 .. row_floats) = src (appends a key or value row to its cache)
+ *   bhd_incremental_attention_at one query at position *pos_dev against cache rows 0 .. *pos_dev; max_positions sizes
+ *                                the score buffer
+ * A position outside [0, max) is reported through the status word and the kernel writes nothing. */
+int32_t bhd_rope_at(bhd_ctx* ctx, float* x_dev, const float* cos_table_dev, const float* sin_table_dev, const int32_t* pos_dev,
+                    uint32_t n_vectors, uint32_t n_pairs, int32_t layout, int32_t inverse, void* stream);
+int32_t bhd_store_row_at(bhd_ctx* ctx, float* dst_dev, const float* src_dev, const int32_t* pos_dev, uint64_t row_floats,
+                         uint64_t max_rows, void* stream);
+int32_t bhd_incremental_attention_at(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev,
+                                     const float* v_cache_dev, const int32_t* pos_dev, uint64_t max_positions, uint32_t n_heads,
+                                     uint32_t n_kv_heads, uint32_t head_dim, float scale, void* stream);
+
 /* Embedding lookup (forward.rs:954-972): rows ids[i] of `table` decoded to f32, out [n_ids][cols]; an id outside the
  * table is reported through the status word. */
 int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, const int32_t* ids_dev, uint64_t n_ids, float* out_dev,

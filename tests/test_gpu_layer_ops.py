@@ -347,8 +347,18 @@ def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
         dev.check_status()
         assert max_rel_err(got.cpu().numpy(), want) <= TOL, (lo, hi)
         assert int(torch.argmax(got[-1])) == int(np.argmax(want[-1]))
-    out = model.generate_greedy(cuda(ids[:5]), 3)
-    assert out.shape[0] == 3 and int(out.min()) >= 0 and int(out.max()) < cfg.vocab
+    # Greedy decoding: the decode step replayed as one CUDA graph (position and token read from device memory)
+    # gives the tokens and the last logits of the step-by-step loop, to the bit; a second call reuses the graph.
+    eager = model.generate_greedy(cuda(ids[:5]), 6, use_graph=False)
+    eager_logits = model.forward(eager[5:6]).clone()
+    graph = model.generate_greedy(cuda(ids[:5]), 6)
+    graph_logits = model.forward(graph[5:6]).clone()
+    dev.check_status()
+    assert graph.shape[0] == 6 and int(graph.min()) >= 0 and int(graph.max()) < cfg.vocab
+    assert np.array_equal(graph.cpu().numpy(), eager.cpu().numpy())
+    assert np.array_equal(bits(graph_logits.cpu().numpy()), bits(eager_logits.cpu().numpy()))
+    again = model.generate_greedy(cuda(ids[:5]), 4)
+    assert np.array_equal(again.cpu().numpy(), eager.cpu().numpy()[:4])
     model.free()
 
 
