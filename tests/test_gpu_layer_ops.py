@@ -351,13 +351,13 @@ def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
     # gives the tokens and the last logits of the step-by-step loop, to the bit; a second call reuses the graph.
     eager = model.generate_greedy(cuda(ids[:5]), 6, use_graph=False)
     eager_logits = model.forward(eager[5:6]).clone()
-    graph = model.generate_greedy(cuda(ids[:5]), 6)
+    graph = model.generate_greedy(cuda(ids[:5]), 6, use_graph=True)
     graph_logits = model.forward(graph[5:6]).clone()
     dev.check_status()
     assert graph.shape[0] == 6 and int(graph.min()) >= 0 and int(graph.max()) < cfg.vocab
     assert np.array_equal(graph.cpu().numpy(), eager.cpu().numpy())
     assert np.array_equal(bits(graph_logits.cpu().numpy()), bits(eager_logits.cpu().numpy()))
-    again = model.generate_greedy(cuda(ids[:5]), 4)
+    again = model.generate_greedy(cuda(ids[:5]), 4, use_graph=True)
     assert np.array_equal(again.cpu().numpy(), eager.cpu().numpy()[:4])
     model.free()
 
