@@ -304,6 +304,10 @@ extern "C" int32_t bhd_sigmoid_gate(bhd_ctx* ctx, float* out_dev, const float* i
 
 // Grows the context's workspace to at least n_bytes now, so that later calls (a CUDA graph capture in particular, during
 // which nothing may be allocated) find it large enough.
+// The workspace's current size. It only changes when the workspace is replaced by a larger one, so a host that holds
+// CUDA graphs compares it with the size at capture time to know whether the graphs still point into live memory.
+extern "C" uint64_t bhd_workspace_bytes(const bhd_ctx* ctx) { return ctx_ok(ctx) ? uint64_t(ctx->workspace_bytes) : 0ull; }
+
 extern "C" int32_t bhd_workspace_reserve(bhd_ctx* ctx, uint64_t n_bytes) {
     if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
     bhd_device_guard guard(ctx);

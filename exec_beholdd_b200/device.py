@@ -30,7 +30,7 @@ EXPORTS = [
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
     "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option", "bhd_peer_alloc", "bhd_peer_open", "bhd_peer_close", "bhd_peer_free",
     "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy", "bhd_rowsplit_create", "bhd_rowsplit_connect",
-    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal", "bhd_sigmoid_gate", "bhd_workspace_reserve", "bhd_rope_at", "bhd_store_row_at", "bhd_incremental_attention_at",
+    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal", "bhd_sigmoid_gate", "bhd_workspace_reserve", "bhd_rope_at", "bhd_store_row_at", "bhd_incremental_attention_at", "bhd_workspace_bytes",
 ]
 
 
@@ -117,6 +117,8 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_debug_fill_normal.argtypes = [vp, vp, u64, u64, u64, f32, vp]
     lib.bhd_sigmoid_gate.argtypes = [vp, vp, vp, vp, u64, vp]
     lib.bhd_workspace_reserve.argtypes = [vp, u64]
+    lib.bhd_workspace_bytes.restype = u64
+    lib.bhd_workspace_bytes.argtypes = [vp]
     lib.bhd_rope_at.argtypes = [vp, vp, vp, vp, vp, u32, u32, i32, i32, vp]
     lib.bhd_store_row_at.argtypes = [vp, vp, vp, vp, u64, u64, vp]
     lib.bhd_incremental_attention_at.argtypes = [vp, vp, vp, vp, vp, vp, u64, u32, u32, u32, C.c_float, vp]
@@ -360,6 +362,11 @@ class CudaDevice:
         n_q, n_heads, hd = q.shape
         self._check(self.lib.bhd_incremental_attention(self.ctx, _ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), n_q, query_start,
                                                        n_kv_positions, n_heads, k_cache.shape[1], hd, scale, self._stream()))
+
+    def workspace_bytes(self) -> int:
+        """Size of the context's workspace; it changes exactly when the workspace is replaced (CUDA graphs captured before
+        then point into freed memory)."""
+        return int(self.lib.bhd_workspace_bytes(self.ctx))
 
     def rope_at_resident(self, x, cos_table, sin_table, pos_dev, split_half: bool = True, inverse: bool = False) -> None:
         """x [heads x head_dim] of the one position *pos_dev, rotated with row *pos_dev of the tables."""

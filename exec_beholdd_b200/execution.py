@@ -422,6 +422,7 @@ class CudaExecutionDevice:
                 raise BackendFailure(str(e)) from e
         batch = RecordedBatch(self.owner, graph, list(commands.commands))
         batch._keep = aux
+        batch._ws_bytes = self.dev.workspace_bytes()
         return batch
 
     def submit(self, batch: RecordedBatch) -> Submission:
@@ -429,6 +430,8 @@ class CudaExecutionDevice:
 
         if batch.owner != self.owner:
             raise ForeignResource("the recorded batch belongs to another execution device")
+        if batch._ws_bytes != self.dev.workspace_bytes():
+            raise IncompatibleResource("the device's workspace was replaced by a larger one after this batch was recorded; record it again")
         with torch.cuda.stream(self.stream):
             batch.graph.replay()
             ev = torch.cuda.Event()

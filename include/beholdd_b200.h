@@ -229,6 +229,9 @@ int32_t bhd_sigmoid_gate(bhd_ctx* ctx, float* out_dev, const float* in_dev, cons
 /* Grows the context's workspace to at least n_bytes now. Nothing may be allocated while a stream is being captured
  * into a CUDA graph, so a host that records graphs reserves the largest workspace its commands need first. */
 int32_t bhd_workspace_reserve(bhd_ctx* ctx, uint64_t n_bytes);
+/* The workspace's current size in bytes. The workspace is only ever replaced by a larger one, so a graph captured when
+ * this returned v is valid exactly as long as it still returns v. */
+uint64_t bhd_workspace_bytes(const bhd_ctx* ctx);
 
 /* The same operators for a decode step replayed as a CUDA graph, where the position may not be a launch parameter:
  * it is read from device memory (*pos_dev, an int32 the host or a kernel advances between replays). No counterpart in

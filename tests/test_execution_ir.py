@@ -180,6 +180,11 @@ def test_recorded_decode_layer_matches_the_oracle_and_replays(oracle):
     cl.linear(h.full_view(), h.full_view(), Wo)
     with pytest.raises(ex.IncompatibleResource):
         d.record(cl)
+    # A batch recorded before the device's workspace was replaced by a larger one points into freed memory: refused.
+    assert d.dev.lib.bhd_workspace_reserve(d.dev.ctx, d.dev.workspace_bytes() + (64 << 20)) == 0
+    with pytest.raises(ex.IncompatibleResource):
+        d.submit(batch)
+    d.wait(d.submit(record_step(2, 2)))
     other = ex.CudaExecutionDevice(0)
     with pytest.raises(ex.ForeignResource):
         other.record(_list_of(ex, h, x, N, eps))

@@ -359,6 +359,13 @@ def test_small_model_forward_matches_the_oracle_composition(dev, oracle):
     assert np.array_equal(bits(graph_logits.cpu().numpy()), bits(eager_logits.cpu().numpy()))
     again = model.generate_greedy(cuda(ids[:5]), 4, use_graph=True)
     assert np.array_equal(again.cpu().numpy(), eager.cpu().numpy()[:4])
+    # A larger workspace replaces the one the captured kernels point into: the step must be captured again, not replayed.
+    captured = model._dec["graph"]
+    assert dev.lib.bhd_workspace_reserve(dev.ctx, dev.workspace_bytes() + (64 << 20)) == 0
+    regrown = model.generate_greedy(cuda(ids[:5]), 6, use_graph=True)
+    dev.check_status()
+    assert model._dec["graph"] is not captured
+    assert np.array_equal(regrown.cpu().numpy(), eager.cpu().numpy())
     model.free()
 
 
