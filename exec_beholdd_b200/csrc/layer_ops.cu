@@ -122,6 +122,158 @@ __global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, cons
     }
 }
 
+// The same arithmetic in the same order, arranged so that memory latency stays off the dependent f64 chains (a decode
+// step has only one CTA per head, so nothing else hides it): 256 threads; a thread forms the dot products of its keys
+// from 16-byte loads, one 32-element batch ahead of the chain; the value rows are staged through shared memory in tiles
+// of 8192 floats, the next tile's loads in flight (in registers) while thread d runs the position-ordered chain of
+// output dimension d over the current tile. head_dim a multiple of 4, 32..256.
+constexpr int ATT_THREADS = 256, ATT_TILE_FLOATS = 8192;
+__global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                                 const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_heads,
+                                                                 uint32_t n_kv_heads, uint32_t head_dim, float scale,
+                                                                 const int32_t* __restrict__ start_dev, uint32_t max_positions,
+                                                                 uint32_t* __restrict__ status) {
+    extern __shared__ __align__(16) float att_smem[];
+    __shared__ float s_max, s_inv;
+    const uint32_t qp = blockIdx.x, head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
+    if (start_dev) {
+        const int32_t sd = *start_dev;
+        if (sd < 0 || uint32_t(sd) + qp >= max_positions) {
+            if (threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+            return;
+        }
+        query_start = uint32_t(sd);
+    }
+    const uint32_t visible = query_start + qp + 1;
+    float* tile = att_smem;                          // ATT_TILE_FLOATS
+    float* qs = att_smem + ATT_TILE_FLOATS;          // head_dim
+    float* scores = qs + head_dim;                   // one per visible position (max_positions or the launch's bound)
+    const float* query = q + (uint64_t(qp) * n_heads + head) * head_dim;
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = query[d];
+    __syncthreads();
+    const uint64_t row_stride = uint64_t(n_kv_heads) * head_dim;
+    // scores: f64 dot product in element order, scaled in f64, rounded to f32
+    for (uint32_t kp = threadIdx.x; kp < visible; kp += blockDim.x) {
+        const float4* key = reinterpret_cast<const float4*>(k_cache + uint64_t(kp) * row_stride + uint64_t(kv_head) * head_dim);
+        double dot = 0.0;
+        float4 cur[8], nxt[8];
+        const uint32_t n4 = head_dim / 4;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = j < int(n4) ? key[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t b0 = 0; b0 < n4; b0 += 8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) nxt[j] = (b0 + 8 + j < n4) ? key[b0 + 8 + j] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (b0 + j < n4) {
+                    const float* qq = qs + 4 * (b0 + j);
+                    dot = __dadd_rn(dot, __dmul_rn(double(qq[0]), double(cur[j].x)));
+                    dot = __dadd_rn(dot, __dmul_rn(double(qq[1]), double(cur[j].y)));
+                    dot = __dadd_rn(dot, __dmul_rn(double(qq[2]), double(cur[j].z)));
+                    dot = __dadd_rn(dot, __dmul_rn(double(qq[3]), double(cur[j].w)));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+        }
+        scores[kp] = float(__dmul_rn(dot, double(scale)));
+    }
+    __syncthreads();
+    // softmax as vecops::softmax: max, exp(v - max) (0 for -inf), sequential f32 sum, multiply by 1 / sum
+    if (threadIdx.x < 32) {
+        float m = -INFINITY;
+        for (uint32_t i = threadIdx.x; i < visible; i += 32) m = fmaxf(m, scores[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x == 0) s_max = m;
+    }
+    __syncthreads();
+    const float m = s_max;
+    const bool all_masked = !isfinite(m);
+    for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) {
+        const float v = scores[i];
+        scores[i] = all_masked ? 0.0f : (isfinite(v) ? bhd_expf_exact(__fsub_rn(v, m)) : 0.0f);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.0f;
+        uint32_t i = 0;
+        for (; i + 8 <= visible; i += 8) {
+            float e[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) e[j] = scores[i + j];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum = __fadd_rn(sum, e[j]);
+        }
+        for (; i < visible; ++i) sum = __fadd_rn(sum, scores[i]);
+        s_inv = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    if (!all_masked) {
+        const float inv = s_inv;
+        for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) scores[i] = __fmul_rn(scores[i], inv);
+    }
+    __syncthreads();
+    // values: per output dimension an f64 sum over the visible positions, in position order
+    const uint32_t tp = ATT_TILE_FLOATS / head_dim;              // positions per tile
+    const uint32_t per_thread = ATT_TILE_FLOATS / 4 / ATT_THREADS;  // float4 per thread per tile: 8
+    const uint32_t row4 = head_dim / 4;
+    float4 stage[ATT_TILE_FLOATS / 4 / ATT_THREADS];
+    auto fetch = [&](uint32_t p0) {   // tile of positions p0 .. p0 + tp into registers (rows beyond `visible` are not read)
+#pragma unroll
+        for (uint32_t j = 0; j < per_thread; ++j) {
+            const uint32_t idx = threadIdx.x + j * ATT_THREADS, pr = idx / row4, c4 = idx - pr * row4;
+            stage[j] = (p0 + pr < visible) ? reinterpret_cast<const float4*>(v_cache + uint64_t(p0 + pr) * row_stride + uint64_t(kv_head) * head_dim)[c4]
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    double sum = 0.0;
+    fetch(0);
+    for (uint32_t p0 = 0; p0 < visible; p0 += tp) {
+#pragma unroll
+        for (uint32_t j = 0; j < per_thread; ++j) reinterpret_cast<float4*>(tile)[threadIdx.x + j * ATT_THREADS] = stage[j];
+        __syncthreads();
+        if (p0 + tp < visible) fetch(p0 + tp);       // in flight while the chain below runs
+        if (threadIdx.x < head_dim) {
+            const uint32_t n = min(tp, visible - p0);
+            uint32_t pr = 0;
+            for (; pr + 8 <= n; pr += 8) {   // the eight products do not depend on the chain: formed ahead of it
+                double prod[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) prod[j] = __dmul_rn(double(scores[p0 + pr + j]), double(tile[(pr + j) * head_dim + threadIdx.x]));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum = __dadd_rn(sum, prod[j]);
+            }
+            for (; pr < n; ++pr) sum = __dadd_rn(sum, __dmul_rn(double(scores[p0 + pr]), double(tile[pr * head_dim + threadIdx.x])));
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x < head_dim) out[(uint64_t(qp) * n_heads + head) * head_dim + threadIdx.x] = float(sum);
+}
+
+// Launches the tiled kernel when the head shape allows, else the plain one. `score_slots` bounds the visible positions.
+static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const float* k, const float* v, uint32_t n_query, uint32_t query_start,
+                                uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, float scale, const int32_t* start_dev,
+                                uint32_t max_positions, uint64_t score_slots, cudaStream_t s) {
+    static bhd_once_per_device once;
+    if (once.pending(ctx)) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_tiled, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+        once.mark(ctx);
+    }
+    const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+    const size_t tiled_smem = (size_t(ATT_TILE_FLOATS) + head_dim + score_slots) * sizeof(float);
+    if (aligned && head_dim % 4 == 0 && head_dim >= 32 && head_dim <= 256 && ATT_TILE_FLOATS % head_dim == 0 && tiled_smem <= 200 * 1024) {
+        k_attention_tiled<<<dim3(n_query, n_heads), ATT_THREADS, tiled_smem, s>>>(out, q, k, v, query_start, n_heads, n_kv_heads, head_dim, scale,
+                                                                                   start_dev, max_positions, ctx->status_dev);
+    } else {
+        k_attention<<<dim3(n_query, n_heads), 128, size_t(score_slots) * sizeof(float), s>>>(out, q, k, v, query_start, n_heads, n_kv_heads, head_dim,
+                                                                                              scale, start_dev, max_positions, ctx->status_dev);
+    }
+    BHD_LAUNCHED(ctx, "attention kernel");
+    return BHD_OK;
+}
+
 // Command::SigmoidGate (crates/beholdd-backend/src/execution.rs:1425-1441): out = in * sigmoid(gate), the sigmoid in its
 // overflow-free form.
 __global__ void k_sigmoid_gate(float* __restrict__ out, const float* __restrict__ in, const float* __restrict__ gate, uint64_t n) {
@@ -229,15 +381,8 @@ extern "C" int32_t bhd_incremental_attention_at(bhd_ctx* ctx, float* out_dev, co
                         (unsigned long long)max_positions, n_heads);
     if (!out_dev || !q_dev || !k_cache_dev || !v_cache_dev || !pos_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "attention: null buffer");
     bhd_device_guard guard(ctx);
-    static bhd_once_per_device once;
-    if (once.pending(ctx)) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
-        once.mark(ctx);
-    }
-    k_attention<<<dim3(1, n_heads), 128, size_t(max_positions) * sizeof(float), cudaStream_t(stream)>>>(
-        out_dev, q_dev, k_cache_dev, v_cache_dev, 0u, n_heads, n_kv_heads, head_dim, scale, pos_dev, uint32_t(max_positions), ctx->status_dev);
-    BHD_LAUNCHED(ctx, "attention kernel");
-    return BHD_OK;
+    return launch_attention(ctx, out_dev, q_dev, k_cache_dev, v_cache_dev, 1, 0, n_heads, n_kv_heads, head_dim, scale, pos_dev, uint32_t(max_positions),
+                            max_positions, cudaStream_t(stream));
 }
 
 extern "C" int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
@@ -262,17 +407,8 @@ extern "C" int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const
                         (unsigned long long)n_kv_positions, n_heads);
     if (!out_dev || !q_dev || !k_cache_dev || !v_cache_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "attention: null buffer");
     bhd_device_guard guard(ctx);
-    const size_t smem = size_t(query_start + n_query_positions) * sizeof(float);
-    static bhd_once_per_device once;
-    if (once.pending(ctx)) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
-        once.mark(ctx);
-    }
-    k_attention<<<dim3(unsigned(n_query_positions), n_heads), 128, smem, cudaStream_t(stream)>>>(out_dev, q_dev, k_cache_dev, v_cache_dev,
-                                                                                                  uint32_t(query_start), n_heads, n_kv_heads,
-                                                                                                  head_dim, scale, nullptr, 0u, ctx->status_dev);
-    BHD_LAUNCHED(ctx, "attention kernel");
-    return BHD_OK;
+    return launch_attention(ctx, out_dev, q_dev, k_cache_dev, v_cache_dev, uint32_t(n_query_positions), uint32_t(query_start), n_heads, n_kv_heads,
+                            head_dim, scale, nullptr, 0, query_start + n_query_positions, cudaStream_t(stream));
 }
 
 extern "C" int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, const int32_t* ids_dev, uint64_t n_ids, float* out_dev,

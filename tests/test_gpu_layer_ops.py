@@ -126,7 +126,28 @@ def test_attention_reference_vectors_and_seeded_cache_bit_exact(dev, oracle):
     out = torch.empty((3, n_heads, hd), device="cuda")
     dev.attention_resident(out, cuda(q[70:]), kd, vd, 70, 73, scale)
     assert np.array_equal(bits(out.cpu().numpy()), bits(want[70:]))
+    # a longer cache (several value tiles of the kernel), one decode query: the launch-parameter form and the form that
+    # reads the position from device memory, both against the oracle to the bit
+    n_pos = 203
+    q1 = synth.activations(34, (1, n_heads, hd))
+    k = synth.activations(35, (n_pos + 5, n_kv, hd))
+    v = synth.activations(36, (n_pos + 5, n_kv, hd))
+    want = oracle.incremental_attention(q1, k[:n_pos], v[:n_pos], 1, n_pos - 1, n_pos, n_heads, n_kv, hd, scale).reshape(1, n_heads, hd)
+    kd, vd = cuda(k), cuda(v)
+    out = torch.empty((1, n_heads, hd), device="cuda")
+    dev.attention_resident(out, cuda(q1), kd, vd, n_pos - 1, n_pos, scale)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+    out.fill_(float("nan"))
+    pos = torch.tensor([n_pos - 1], dtype=torch.int32, device="cuda")
+    dev.attention_at_resident(out, cuda(q1), kd, vd, pos, scale)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
     dev.check_status()
+    pos.fill_(n_pos + 5)                       # a position outside the cache: reported, nothing written
+    out.fill_(7.0)
+    dev.attention_at_resident(out, cuda(q1), kd, vd, pos, scale)
+    with pytest.raises(Exception):
+        dev.check_status()
+    assert float(out.min()) == 7.0
 
 
 def test_embedding_rows_and_bf16_weights(dev, oracle):
