@@ -16,12 +16,9 @@ namespace {
 
 bool ctx_ok(const bhd_ctx* c) { return c && c->magic == BHD_CTX_MAGIC; }
 
-__global__ void __launch_bounds__(256) k_rmsnorm(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, uint64_t n,
-                                                 float eps) {
-    __shared__ double s_part[8];
-    __shared__ float s_inv;
-    const float* xr = x + blockIdx.x * n;
-    float* yr = y + blockIdx.x * n;
+// One row by one CTA of 256 threads (y may be x).
+__device__ __forceinline__ void rmsnorm_row(float* yr, const float* xr, const float* __restrict__ w, uint64_t n, float eps,
+                                            double* s_part, float* s_inv) {
     double ss = 0.0;
     for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) {
         const double v = double(xr[i]);
@@ -34,13 +31,68 @@ __global__ void __launch_bounds__(256) k_rmsnorm(float* __restrict__ y, const fl
     if (threadIdx.x == 0) {
         double t = 0.0;
         for (unsigned i = 0; i < (blockDim.x >> 5); ++i) t += s_part[i];
-        s_inv = float(1.0 / sqrt(t / double(n) + double(eps)));
+        *s_inv = float(1.0 / sqrt(t / double(n) + double(eps)));
     }
     __syncthreads();
-    const float inv = s_inv;
+    const float inv = *s_inv;
     for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = __fmul_rn(xr[i], inv);
         yr[i] = w ? __fmul_rn(v, w[i]) : v;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_rmsnorm(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, uint64_t n,
+                                                 float eps) {
+    __shared__ double s_part[8];
+    __shared__ float s_inv;
+    rmsnorm_row(y + blockIdx.x * n, x + blockIdx.x * n, w, n, eps, s_part, &s_inv);
+}
+
+// What a decode step does to the new position's query, key and value heads between the projections and attention, in one
+// launch instead of six: per-head RMSNorm of q and k (k_rmsnorm's arithmetic), rope with the table row of position
+// *pos_dev (k_rope's arithmetic), and the key and value rows appended to their caches at that position. One CTA per head
+// vector: n_heads query heads, n_kv_heads key heads, n_kv_heads value heads.
+__global__ void __launch_bounds__(256) k_qk_norm_rope_store(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
+                                                            const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                                                            const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                                            float* __restrict__ k_cache, float* __restrict__ v_cache,
+                                                            const int32_t* __restrict__ pos_dev, uint32_t max_positions, uint32_t n_heads,
+                                                            uint32_t n_kv_heads, uint32_t head_dim, float eps, int layout,
+                                                            uint32_t* __restrict__ status) {
+    __shared__ double s_part[8];
+    __shared__ float s_inv;
+    const int32_t pos = *pos_dev;
+    if (pos < 0 || uint32_t(pos) >= max_positions) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+        return;
+    }
+    const uint32_t c = blockIdx.x;
+    const uint64_t cache_row = uint64_t(pos) * n_kv_heads * head_dim;
+    if (c >= n_heads + n_kv_heads) {   // a value head: copy
+        const uint32_t j = c - n_heads - n_kv_heads;
+        for (uint32_t i = threadIdx.x; i < head_dim; i += blockDim.x) v_cache[cache_row + uint64_t(j) * head_dim + i] = v[uint64_t(j) * head_dim + i];
+        return;
+    }
+    const bool is_q = c < n_heads;
+    float* xv = is_q ? q + uint64_t(c) * head_dim : k + uint64_t(c - n_heads) * head_dim;
+    rmsnorm_row(xv, xv, is_q ? q_norm : k_norm, head_dim, eps, s_part, &s_inv);
+    __syncthreads();
+    const uint32_t n_pairs = head_dim / 2;
+    float a = 0.f, b = 0.f;
+    const uint32_t i = threadIdx.x;
+    const uint32_t ia = layout == 0 ? 2 * i : i, ib = layout == 0 ? 2 * i + 1 : i + n_pairs;
+    if (i < n_pairs) {   // head_dim <= 512: one pair per thread
+        const float x0 = xv[ia], x1 = xv[ib];
+        const float cs = cos_table[uint64_t(pos) * n_pairs + i], sn = sin_table[uint64_t(pos) * n_pairs + i];
+        a = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+        b = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+        xv[ia] = a;
+        xv[ib] = b;
+        if (!is_q) {
+            float* kc = k_cache + cache_row + uint64_t(c - n_heads) * head_dim;
+            kc[ia] = a;
+            kc[ib] = b;
+        }
     }
 }
 
@@ -351,6 +403,27 @@ extern "C" int32_t bhd_rope_at(bhd_ctx* ctx, float* x_dev, const float* cos_tabl
     k_rope<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(x_dev, cos_table_dev, sin_table_dev, n_vectors, n_vectors, n_pairs, layout,
                                                                          inverse, pos_dev);
     BHD_LAUNCHED(ctx, "rotary embedding kernel");
+    return BHD_OK;
+}
+
+extern "C" int32_t bhd_qk_norm_rope_store_at(bhd_ctx* ctx, float* q_dev, float* k_dev, const float* v_dev, const float* q_norm_dev,
+                                             const float* k_norm_dev, const float* cos_table_dev, const float* sin_table_dev, float* k_cache_dev,
+                                             float* v_cache_dev, const int32_t* pos_dev, uint64_t max_positions, uint32_t n_heads,
+                                             uint32_t n_kv_heads, uint32_t head_dim, float eps, int32_t layout, void* stream) {
+    if (!ctx_ok(ctx)) return BHD_ERR_INVALID_ARGUMENT;
+    if (layout != 0 && layout != 1) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: layout must be 0 (interleaved) or 1 (split half)");
+    if (n_heads == 0 || n_kv_heads == 0 || head_dim == 0 || head_dim % 2 != 0 || head_dim > 512 || max_positions == 0 || max_positions > 0x7fffffffull)
+        return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: heads=%u kv_heads=%u head_dim=%u positions=%llu", n_heads, n_kv_heads, head_dim,
+                        (unsigned long long)max_positions);
+    if (!isfinite(eps) || eps < 0.0f) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: RMSNorm epsilon must be finite and non-negative, got %g", double(eps));
+    if (!q_dev || !k_dev || !v_dev || !cos_table_dev || !sin_table_dev || !k_cache_dev || !v_cache_dev || !pos_dev)
+        return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "qk_norm_rope_store: null buffer");
+    bhd_device_guard guard(ctx);
+    k_qk_norm_rope_store<<<n_heads + 2 * n_kv_heads, 256, 0, cudaStream_t(stream)>>>(q_dev, k_dev, v_dev, q_norm_dev, k_norm_dev, cos_table_dev,
+                                                                                      sin_table_dev, k_cache_dev, v_cache_dev, pos_dev,
+                                                                                      uint32_t(max_positions), n_heads, n_kv_heads, head_dim, eps, layout,
+                                                                                      ctx->status_dev);
+    BHD_LAUNCHED(ctx, "query/key norm, rope and cache append kernel");
     return BHD_OK;
 }
 

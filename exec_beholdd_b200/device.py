@@ -30,7 +30,7 @@ EXPORTS = [
     "bhd_matmul", "bhd_softmax", "bhd_swiglu", "bhd_add_in_place", "bhd_moe_route", "bhd_moe_experts", "bhd_moe_combine", "bhd_moe_layer",
     "bhd_moe_layer_host", "bhd_check_status", "bhd_launch_count", "bhd_debug_wait_test", "bhd_debug_expf", "bhd_debug_option", "bhd_peer_alloc", "bhd_peer_open", "bhd_peer_close", "bhd_peer_free",
     "bhd_ep_create", "bhd_ep_connect", "bhd_ep_layer", "bhd_ep_destroy", "bhd_rowsplit_create", "bhd_rowsplit_connect",
-    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal", "bhd_sigmoid_gate", "bhd_workspace_reserve", "bhd_rope_at", "bhd_store_row_at", "bhd_incremental_attention_at", "bhd_workspace_bytes",
+    "bhd_rowsplit_matvec", "bhd_rowsplit_destroy", "bhd_rmsnorm", "bhd_rope", "bhd_incremental_attention", "bhd_embedding_rows", "bhd_debug_fill_q8_0", "bhd_debug_fill_normal", "bhd_sigmoid_gate", "bhd_workspace_reserve", "bhd_rope_at", "bhd_store_row_at", "bhd_incremental_attention_at", "bhd_workspace_bytes", "bhd_qk_norm_rope_store_at",
 ]
 
 
@@ -117,6 +117,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.bhd_debug_fill_normal.argtypes = [vp, vp, u64, u64, u64, f32, vp]
     lib.bhd_sigmoid_gate.argtypes = [vp, vp, vp, vp, u64, vp]
     lib.bhd_workspace_reserve.argtypes = [vp, u64]
+    lib.bhd_qk_norm_rope_store_at.argtypes = [vp] * 11 + [u64, u32, u32, u32, f32, i32, vp]
     lib.bhd_workspace_bytes.restype = u64
     lib.bhd_workspace_bytes.argtypes = [vp]
     lib.bhd_rope_at.argtypes = [vp, vp, vp, vp, vp, u32, u32, i32, i32, vp]
@@ -373,6 +374,15 @@ class CudaDevice:
         heads, hd = x.shape[-2], x.shape[-1]
         self._check(self.lib.bhd_rope_at(self.ctx, _ptr(x), _ptr(cos_table), _ptr(sin_table), _ptr(pos_dev), heads, hd // 2,
                                          1 if split_half else 0, 1 if inverse else 0, self._stream()))
+
+    def qk_norm_rope_store_at_resident(self, q, k, v, q_norm, k_norm, cos_table, sin_table, k_cache, v_cache, pos_dev, eps: float,
+                                       split_half: bool = True) -> None:
+        """q [n_heads x head_dim], k / v [n_kv_heads x head_dim] of the position *pos_dev: QK-norm and rope in place, k and v
+        appended to the caches [max_positions x n_kv_heads x head_dim]."""
+        n_heads, hd = q.shape[-2], q.shape[-1]
+        self._check(self.lib.bhd_qk_norm_rope_store_at(self.ctx, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm), _ptr(k_norm), _ptr(cos_table),
+                                                       _ptr(sin_table), _ptr(k_cache), _ptr(v_cache), _ptr(pos_dev), k_cache.shape[0], n_heads,
+                                                       k_cache.shape[1], hd, eps, 1 if split_half else 0, self._stream()))
 
     def store_row_at_resident(self, dst, src, pos_dev) -> None:
         """dst[*pos_dev] = src; dst [max_rows x row]."""

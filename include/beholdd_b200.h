@@ -241,7 +241,16 @@ uint64_t bhd_workspace_bytes(const bhd_ctx* ctx);
  *   bhd_store_row_at             dst[*pos_dev][0 .. row_floats) = src (appends a key or value row to its cache)
  *   bhd_incremental_attention_at one query at position *pos_dev against cache rows 0 .. *pos_dev; max_positions sizes
  *                                the score buffer
+ *   bhd_qk_norm_rope_store_at    what a decode step does between the projections and attention in one launch: per-head
+ *                                RMSNorm of q [n_heads][head_dim] and k [n_kv_heads][head_dim] in place (null weights:
+ *                                plain normalisation), rope of both with row *pos_dev of the tables, k and v appended to
+ *                                their caches [max_positions][n_kv_heads][head_dim] at *pos_dev; same bits as the
+ *                                separate calls
  * A position outside [0, max) is reported through the status word and the kernel writes nothing. */
+int32_t bhd_qk_norm_rope_store_at(bhd_ctx* ctx, float* q_dev, float* k_dev, const float* v_dev, const float* q_norm_dev,
+                                  const float* k_norm_dev, const float* cos_table_dev, const float* sin_table_dev, float* k_cache_dev,
+                                  float* v_cache_dev, const int32_t* pos_dev, uint64_t max_positions, uint32_t n_heads, uint32_t n_kv_heads,
+                                  uint32_t head_dim, float eps, int32_t layout, void* stream);
 int32_t bhd_rope_at(bhd_ctx* ctx, float* x_dev, const float* cos_table_dev, const float* sin_table_dev, const int32_t* pos_dev,
                     uint32_t n_vectors, uint32_t n_pairs, int32_t layout, int32_t inverse, void* stream);
 int32_t bhd_store_row_at(bhd_ctx* ctx, float* dst_dev, const float* src_dev, const int32_t* pos_dev, uint64_t row_floats,

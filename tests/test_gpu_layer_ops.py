@@ -150,6 +150,48 @@ def test_attention_reference_vectors_and_seeded_cache_bit_exact(dev, oracle):
     assert float(out.min()) == 7.0
 
 
+def test_fused_decode_step_operator_equals_the_separate_calls(dev):
+    """QK-norm, rope and the cache append of one decode position in one launch, with the position read from device
+    memory, against the separate operators (which are checked against the oracle above): the same bits."""
+    import torch
+    from exec_beholdd_b200 import synth
+    from exec_beholdd_b200.qwen3moe import rope_tables
+
+    n_heads, n_kv, hd, ctx_len, eps = 32, 4, 128, 40, 1e-6
+    cos, sin = rope_tables(1.0e6, hd, ctx_len)
+    cos, sin = cuda(cos), cuda(sin)
+    qn, kn = cuda(synth.normal(3, 1, hd) * np.float32(0.1) + np.float32(1.0)), cuda(synth.normal(3, 2, hd) * np.float32(0.1) + np.float32(1.0))
+    for p in (0, 17, 39):
+        q, k, v = cuda(synth.activations(50 + p, (1, n_heads, hd))), cuda(synth.activations(60 + p, (1, n_kv, hd))), cuda(synth.activations(70 + p, (1, n_kv, hd)))
+        pos = torch.tensor([p], dtype=torch.int32, device="cuda")
+        q1, k1 = q.clone(), k.clone()
+        kc1, vc1 = torch.zeros((ctx_len, n_kv, hd), device="cuda"), torch.zeros((ctx_len, n_kv, hd), device="cuda")
+        dev.rmsnorm_resident(q1, q1, qn, eps)
+        dev.rmsnorm_resident(k1, k1, kn, eps)
+        dev.rope_at_resident(q1, cos, sin, pos)
+        dev.rope_at_resident(k1, cos, sin, pos)
+        dev.store_row_at_resident(kc1.view(ctx_len, -1), k1.view(-1), pos)
+        dev.store_row_at_resident(vc1.view(ctx_len, -1), v.view(-1), pos)
+        ref = torch.empty_like(q)                      # and rope_at against the launch-parameter form
+        ref.copy_(q)
+        dev.rmsnorm_resident(ref, ref, qn, eps)
+        dev.rope_resident(ref, cos[p:p + 1], sin[p:p + 1])
+        assert torch.equal(ref, q1)
+        q2, k2 = q.clone(), k.clone()
+        kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+        dev.qk_norm_rope_store_at_resident(q2, k2, v, qn, kn, cos, sin, kc2, vc2, pos, eps)
+        dev.check_status()
+        for a, b in ((q1, q2), (k1, k2), (kc1, kc2), (vc1, vc2)):
+            assert np.array_equal(bits(a.cpu().numpy()), bits(b.cpu().numpy()))
+        assert float(kc2[p].abs().max()) > 0 and float(vc2[p].abs().max()) > 0
+    pos = torch.tensor([ctx_len], dtype=torch.int32, device="cuda")   # outside the cache: reported, nothing written
+    kc2.zero_()
+    dev.qk_norm_rope_store_at_resident(q2, k2, v, qn, kn, cos, sin, kc2, vc2, pos, eps)
+    with pytest.raises(Exception):
+        dev.check_status()
+    assert float(kc2.abs().max()) == 0.0
+
+
 def test_embedding_rows_and_bf16_weights(dev, oracle):
     import torch
     from exec_beholdd_b200 import DeviceError, Weight, synth
