@@ -301,6 +301,6 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
                              cudaStream_t s, bool* handled, const MoePeerOut* peer);
 size_t bhd_moe_plan_scratch_words(uint32_t n_routes, uint32_t n_local);
 int32_t bhd_launch_moe_plan(bhd_ctx* ctx, const int32_t* experts, const float* weights, uint32_t n_routes, uint32_t first_expert,
-                            uint32_t n_local, uint32_t n_total, uint32_t cap, const MoePlanBuffers& b, cudaStream_t s);
+                            uint32_t n_local, uint32_t n_total, uint32_t cap, uint32_t n_positions, const MoePlanBuffers& b, cudaStream_t s);
 bool bhd_moe_i8_usable(const bhd_weight* w);
 

@@ -707,15 +707,15 @@ int32_t bhd_launch_matvec_fast(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab,
 
 namespace {
 
-// One launch per size class that can occur (a class only exists when there are enough routes for its
-// smallest group): the integer kernel below `tc_min`, the tensor-core kernel from there on.
+// One launch per size class that can occur (a class only exists when there are enough routes and enough
+// positions for its smallest group: an expert has at most one route per position): the integer kernel below `tc_min`, the tensor-core kernel from there on.
 int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, const MoePlanBuffers& pb, uint32_t n_routes,
-                           uint32_t n_local, uint32_t cap, uint32_t tc_min, const void* xq, const void* x16, const void* x16_lo, float* out0,
+                           uint32_t n_positions, uint32_t n_local, uint32_t cap, uint32_t tc_min, const void* xq, const void* x16, const void* x16_lo, float* out0,
                            float* out1, float* const* slot_dst, const float* i8_scale, const float* tc_scale, cudaStream_t s) {
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
     for (uint32_t cls = 0; cls < uint32_t(BHD_MOE_CLASSES); ++cls) {
         const uint32_t least = bhd_moe_cls_least(int(cls));
-        if (n_routes < least || least > cap) break;
+        if (n_routes < least || least > cap || least > n_positions) break;  // an expert has at most one route per position
         // An expert cut into several groups only yields groups of more than cap / 2 routes, so the classes below hold
         // at most one group per expert; every class holds at most routes / (its smallest group) groups.
         const uint32_t by_size = n_routes / least;
@@ -807,17 +807,17 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
     float* ascale = reinterpret_cast<float*>(ws + o_as);
     const bool tc_possible = tc_ok && R >= bhd_moe_cls_least(int(tc_min));
 
-    if ((st = bhd_launch_moe_plan(ctx, experts, weights, R, first_expert, E, n_total, cap, pb, s)) != BHD_OK) return st;
+    if ((st = bhd_launch_moe_plan(ctx, experts, weights, R, first_expert, E, n_total, cap, uint32_t(T), pb, s)) != BHD_OK) return st;
     // gate and up: [ff x dim] per expert, both matrices in one launch per size class
     if ((st = bhd_launch_moe_slots_i8(ctx, 0, pb.hdr, pb.slot_route, pb.slot_cls, tc_min - 1, top_k, x, nullptr, uint32_t(dim), R, ws + o_xq, s)) != BHD_OK) return st;
     if (tc_possible && (st = bhd_launch_moe_rows_f16(ctx, 0, pb.hdr, pb.slot_route, pb.slot_cls, tc_min, top_k, x, nullptr, uint32_t(dim), R,
                                                       ws + o_x16, ws + o_x16l, nullptr, xscale, s)) != BHD_OK) return st;
-    if ((st = launch_grouped_all(ctx, gate, up, pb, R, E, cap, tc_min, ws + o_xq, ws + o_x16, ws + o_x16l, gbuf, ubuf, nullptr, nullptr, xscale, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, gate, up, pb, R, uint32_t(T), E, cap, tc_min, ws + o_xq, ws + o_x16, ws + o_x16l, gbuf, ubuf, nullptr, nullptr, xscale, s)) != BHD_OK) return st;
     // down: [dim x ff] per expert, each output row scaled by its route weight
     if ((st = bhd_launch_moe_slots_i8(ctx, 1, pb.hdr, pb.slot_route, pb.slot_cls, tc_min - 1, top_k, gbuf, ubuf, uint32_t(ff), R, ws + o_aq, s)) != BHD_OK) return st;
     if (tc_possible && (st = bhd_launch_moe_rows_f16(ctx, 1, pb.hdr, pb.slot_route, pb.slot_cls, tc_min, top_k, gbuf, ubuf, uint32_t(ff), R,
                                                       ws + o_a16, ws + o_a16l, pb.slot_weight, ascale, s)) != BHD_OK) return st;
-    if ((st = launch_grouped_all(ctx, down, nullptr, pb, R, E, cap, tc_min, ws + o_aq, ws + o_a16, ws + o_a16l, dbuf, nullptr, pb.slot_dst, pb.slot_weight, ascale, s)) != BHD_OK) return st;
+    if ((st = launch_grouped_all(ctx, down, nullptr, pb, R, uint32_t(T), E, cap, tc_min, ws + o_aq, ws + o_a16, ws + o_a16l, dbuf, nullptr, pb.slot_dst, pb.slot_weight, ascale, s)) != BHD_OK) return st;
     if (peer) {  // the rows went to their owners; the caller signals them and combines what it received
         *handled = true;
         return BHD_OK;

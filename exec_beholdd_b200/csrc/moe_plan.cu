@@ -95,7 +95,8 @@ __device__ __forceinline__ void scatter_block(const int32_t* __restrict__ expert
 
 __global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __restrict__ experts, const float* __restrict__ weights,
                                                            uint32_t n_routes, uint32_t first, uint32_t n_local, uint32_t n_total,
-                                                           uint32_t cap, MoePlanBuffers b, uint32_t* ticket, uint32_t* status) {
+                                                           uint32_t cap, uint32_t n_positions, MoePlanBuffers b, uint32_t* ticket,
+                                                           uint32_t* status) {
     extern __shared__ uint32_t hist[];  // [PLAN_WARPS][n_local], later the per-expert totals
     __shared__ uint32_t s_warp[PLAN_WARPS][NQ], s_carry[NQ];
     __shared__ bool s_last;
@@ -131,6 +132,9 @@ __global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __rest
             run += c;
         }
         total[e] = run;
+        // A position names an expert at most once (the selection is a top-k of distinct experts), so no expert has more
+        // routes than there are positions; the grouped kernels are only launched for the size classes that rule allows.
+        if (run > n_positions) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
     }
     if (threadIdx.x < NQ) s_carry[threadIdx.x] = 0u;
     __syncthreads();
@@ -229,12 +233,13 @@ size_t bhd_moe_plan_scratch_words(uint32_t n_routes, uint32_t n_local) {
 }
 
 int32_t bhd_launch_moe_plan(bhd_ctx* ctx, const int32_t* experts, const float* weights, uint32_t n_routes, uint32_t first_expert,
-                            uint32_t n_local, uint32_t n_total, uint32_t cap, const MoePlanBuffers& b, cudaStream_t s) {
+                            uint32_t n_local, uint32_t n_total, uint32_t cap, uint32_t n_positions, const MoePlanBuffers& b, cudaStream_t s) {
     if (n_routes == 0 || n_local == 0 || n_local > 1024) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: route plan for %u routes, %u experts", n_routes, n_local);
     const unsigned blocks = unsigned((n_routes + BLOCK_ROUTES - 1) / BLOCK_ROUTES);
     const size_t smem = size_t(PLAN_WARPS) * n_local * sizeof(uint32_t);  // at most 32 KB
     uint32_t* ticket = ctx->status_dev + 1;  // a spare word next to the status word; zero between launches
-    k_moe_hist<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, b, ticket, ctx->status_dev);
+    k_moe_hist<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, n_positions, b, ticket,
+                                                  ctx->status_dev);
     BHD_LAUNCHED(ctx, "route histogram kernel");
     if (blocks > 1) {  // a single block scatters inside the first launch
         k_moe_scatter<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, b);

@@ -482,6 +482,13 @@ def test_moe_experts_with_skewed_and_empty_routing(dev, oracle, T, top_k, patter
         dev.moe_experts(gw, uw, dw, cuda(x), cuda(bad), cuda(weights), y)
         with pytest.raises(DeviceError):
             dev.check_status()
+        if pattern == "two_hot":
+            # positions that name one expert twice (a top-k never does): more routes for the expert than positions, reported
+            dup = experts.copy()
+            dup[:, 1] = dup[:, 0]
+            dev.moe_experts(gw, uw, dw, cuda(x), cuda(dup), cuda(weights), y)
+            with pytest.raises(DeviceError):
+                dev.check_status()
     for h in (gw, uw, dw):
         h.free()
 
