@@ -56,7 +56,7 @@ L2_BYTES = 126 * 1024 * 1024
 HEAD_TRAFFIC_BYTES = 28_345_088
 MOE = dict(n_experts=128, dim=2048, ff=768, top_k=8)
 TOL = 2e-3                         # the path's floating-point tolerance
-DTYPE = ("f32 in / f32 out; weights as packed (s8 / u4 / u6 quants, f16 block scales), activations as 15-bit "
+DTYPE = ("f32 in / f32 out; weights as packed (s8 / u4 / u6 quants, f16 block scales), activations as 16-bit "
          "block-floating integers (decode, routed experts) or fp16 (prefill), s32 + f32 accumulation")
 
 

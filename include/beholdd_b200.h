@@ -185,8 +185,9 @@ int32_t bhd_moe_route(bhd_ctx* ctx, const bhd_weight* router, const float* x_dev
  * n_local = n_experts this is the whole layer. `n_experts` is the layer's expert count over all
  * ranks: an id outside [0, n_experts) is reported through the status word (pass 0 if unknown; only
  * negative ids can then be told from another rank's). The experts of one position must be distinct, as the
- * reference's stable top-k yields them; an expert named by more routes than there are positions is reported
- * through the status word.
+ * reference's stable top-k yields them: the grouped kernels (Q8_0 experts with 16-byte aligned rows) report an
+ * expert named by more routes than there are positions through the status word; the general kernels compute
+ * any assignment.
  *   accumulate == 0: y[t] = out[t];  accumulate != 0: y[t] += out[t]  (forward.rs:1405-1407) */
 int32_t bhd_moe_experts(bhd_ctx* ctx, const bhd_weight* gate_exps, const bhd_weight* up_exps,
                         const bhd_weight* down_exps, const float* x_dev, uint64_t n_positions, uint32_t top_k,

@@ -482,13 +482,34 @@ def test_moe_experts_with_skewed_and_empty_routing(dev, oracle, T, top_k, patter
         dev.moe_experts(gw, uw, dw, cuda(x), cuda(bad), cuda(weights), y)
         with pytest.raises(DeviceError):
             dev.check_status()
-        if pattern == "two_hot":
-            # positions that name one expert twice (a top-k never does): more routes for the expert than positions, reported
-            dup = experts.copy()
-            dup[:, 1] = dup[:, 0]
-            dev.moe_experts(gw, uw, dw, cuda(x), cuda(dup), cuda(weights), y)
-            with pytest.raises(DeviceError):
-                dev.check_status()
+    for h in (gw, uw, dw):
+        h.free()
+
+
+def test_grouped_expert_path_reports_an_expert_named_twice_by_a_position(dev, oracle):
+    """The grouped kernels are launched only for the group sizes the number of positions allows (an expert has at most
+    one route per position, as a top-k of distinct experts guarantees). Assignments that break the rule are reported
+    through the status word instead of being computed wrongly."""
+    import torch
+    from exec_beholdd_b200 import DeviceError, Weight, synth
+
+    n_experts, dim, ff, T, top_k = 8, 512, 256, 6, 2
+    _, gate, up, down, x = moe_inputs(779, n_experts, dim, ff, T)
+    experts = np.stack([np.arange(T) % n_experts, (np.arange(T) + 3) % n_experts], axis=1).astype(np.int32)
+    weights = np.abs(synth.activations(780, (T, top_k))).astype(np.float32) + np.float32(0.25)
+    gw = dev.upload_weight(Weight(gate, 8, ff, dim), slabs=n_experts)
+    uw = dev.upload_weight(Weight(up, 8, ff, dim), slabs=n_experts)
+    dw = dev.upload_weight(Weight(down, 8, dim, ff), slabs=n_experts)
+    y = torch.full((T, dim), float("nan"), device="cuda")
+    dev.moe_experts(gw, uw, dw, cuda(x), cuda(experts), cuda(weights), y)
+    dev.check_status()
+    assert max_rel_err(y.cpu().numpy(), oracle.moe_experts(gate, up, down, n_experts, dim, ff, x, experts, weights)) <= TOL
+    dup = np.full((T, top_k), 5, dtype=np.int32)     # expert 5 gets 12 routes from 6 positions
+    dev.moe_experts(gw, uw, dw, cuda(x), cuda(dup), cuda(weights), y)
+    with pytest.raises(DeviceError):
+        dev.check_status()
+    dev.moe_experts(gw, uw, dw, cuda(x), cuda(experts), cuda(weights), y)   # the next call works
+    dev.check_status()
     for h in (gw, uw, dw):
         h.free()
 
