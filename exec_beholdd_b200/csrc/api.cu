@@ -155,6 +155,17 @@ int32_t bhd_ctx_create(int32_t device, bhd_ctx** out_ctx) {
         delete c;
         return BHD_ERR_ALLOCATION;
     }
+    // streams and events of the routed experts' side-by-side size classes: made now, not on first use, which may be
+    // inside a stream capture
+    bool side_ok = cudaEventCreateWithFlags(&c->fork_event, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 3 && side_ok; ++i)
+        side_ok = cudaStreamCreateWithFlags(&c->side_stream[i], cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&c->join_event[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!side_ok) {
+        cudaGetLastError();
+        bhd_ctx_destroy(c);
+        return BHD_ERR_ALLOCATION;
+    }
     cudaDriverEntryPointQueryResult q;
     void* fn = nullptr;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
@@ -172,6 +183,11 @@ int32_t bhd_ctx_destroy(bhd_ctx* ctx) {
     bhd_device_guard guard(ctx);
     cudaDeviceSynchronize();
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+    for (int i = 0; i < 3; ++i) {
+        if (ctx->side_stream[i]) cudaStreamDestroy(ctx->side_stream[i]);
+        if (ctx->join_event[i]) cudaEventDestroy(ctx->join_event[i]);
+    }
+    if (ctx->fork_event) cudaEventDestroy(ctx->fork_event);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);

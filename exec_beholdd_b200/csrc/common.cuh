@@ -37,6 +37,8 @@ struct bhd_ctx {
     void* pinned;           // pinned bounce buffer for host entry points
     size_t pinned_bytes;
     cudaStream_t host_stream;  // non-blocking stream of the host-buffer entry points
+    cudaStream_t side_stream[3];  // the routed experts' size classes run side by side: forked from and joined to the caller's stream
+    cudaEvent_t fork_event, join_event[3];
     uint32_t spin_limit;    // polls a bounded wait makes before it gives up (0: the kernel's default)
     uint32_t debug_drop;    // test hook: the next decode matvec leaves this many copies unrequested
     uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)

@@ -713,23 +713,43 @@ int32_t launch_grouped_all(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight*
                            uint32_t n_positions, uint32_t n_local, uint32_t cap, uint32_t tc_min, const void* xq, const void* x16, const void* x16_lo, float* out0,
                            float* out1, float* const* slot_dst, const float* i8_scale, const float* tc_scale, cudaStream_t s) {
     const uint32_t small = n_local < n_routes ? n_local : n_routes;
+    uint32_t n_cls = 0;
     for (uint32_t cls = 0; cls < uint32_t(BHD_MOE_CLASSES); ++cls) {
         const uint32_t least = bhd_moe_cls_least(int(cls));
         if (n_routes < least || least > cap || least > n_positions) break;  // an expert has at most one route per position
+        ++n_cls;
+    }
+    // The classes work on disjoint groups, so their kernels need not wait for one another: with the integer kernels
+    // (at most four classes) every class after the first runs on a side stream forked from the caller's stream and joined
+    // to it again, which also holds inside a stream capture (the side streams join the capture and leave it at the join).
+    // A class that turns out to be empty then costs the chain nothing.
+    const bool side_by_side = n_cls > 1 && n_cls <= 4 && tc_min >= n_cls;
+    if (side_by_side) BHD_CUDA(ctx, cudaEventRecord(ctx->fork_event, s), "forking the size classes");
+    for (uint32_t cls = 0; cls < n_cls; ++cls) {
+        const uint32_t least = bhd_moe_cls_least(int(cls));
         // An expert cut into several groups only yields groups of more than cap / 2 routes, so the classes below hold
         // at most one group per expert; every class holds at most routes / (its smallest group) groups.
         const uint32_t by_size = n_routes / least;
         const uint32_t bound = (2 * (4u << cls) >= cap) ? by_size : (small < by_size ? small : by_size);
+        cudaStream_t cs = s;
+        if (side_by_side && cls > 0) {
+            cs = ctx->side_stream[cls - 1];
+            BHD_CUDA(ctx, cudaStreamWaitEvent(cs, ctx->fork_event, 0), "forking the size classes");
+        }
         int32_t st;
         if (cls < tc_min)
             st = bhd_launch_moe_grouped_i8(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, xq, n_routes, out0,
-                                           out1, slot_dst, i8_scale, s);
+                                           out1, slot_dst, i8_scale, cs);
         else if (ctx->moe_tc_plain && !slot_dst)
             st = bhd_launch_gemm_q8_grouped(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, x16, n_routes,
-                                            out0, out1, tc_scale, s);
+                                            out0, out1, tc_scale, cs);
         else
             st = bhd_launch_gemm_q8_ts_grouped(ctx, w0, w1, pb.hdr, pb.groups, pb.glist + uint64_t(cls) * pb.gmax, cls, bound, x16, x16_lo,
-                                               n_routes, out0, out1, slot_dst, tc_scale, s);
+                                               n_routes, out0, out1, slot_dst, tc_scale, cs);
+        if (side_by_side && cls > 0) {  // joined even after a failed launch, so that a capture in progress stays well-formed
+            cudaEventRecord(ctx->join_event[cls - 1], cs);
+            cudaStreamWaitEvent(s, ctx->join_event[cls - 1], 0);
+        }
         if (st != BHD_OK) return st;
     }
     return BHD_OK;
