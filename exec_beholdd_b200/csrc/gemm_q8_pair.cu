@@ -1,6 +1,6 @@
-// Prefill matmul for packed Q8_0 weights: persistent CTA pairs (tcgen05 cta_group::2).
+// Prefill matmul for packed Q8_0 and Q4_K weights: persistent CTA pairs (tcgen05 cta_group::2).
 //
-//   Y[m][n] = sum_k X[m][k] * W[n][k],   W packed Q8_0 [N x K], X fp16 [M x K] (converted once per call), Y f32.
+//   Y[m][n] = sum_k X[m][k] * W[n][k],   W packed Q8_0 or Q4_K [N x K], X fp16 [M x K] (converted once per call), Y f32.
 //
 // A cluster of two CTAs on neighbouring SMs works on one 256-row x 256-token tile at a time. Each CTA converts its
 // own 128 weight rows (packed chunk by TMA -> fp16 K-major 128B-swizzled tile in its shared memory, block scale
@@ -38,8 +38,9 @@ constexpr int TOK = 256;               // tokens per tile
 constexpr int HALF_TOK = 128;          // tokens each CTA loads
 constexpr int CHUNK_K = 256;           // columns per packed chunk
 constexpr int SLICE_K = 64;            // columns per fp16 stage (one 128-byte swizzle row)
-constexpr int PACK_ROW = 272;          // packed bytes per row per chunk
-constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024
+constexpr int PACK_ROW = 272;          // packed bytes per row per chunk: Q8_0 (eight blocks of 34 bytes); Q4_K: 144 (one superblock)
+constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024: the size of a chunk buffer for either format
+__host__ __device__ constexpr int pack_row_of(uint32_t kind) { return kind == BHD_TYPE_Q4_K ? 144 : 272; }
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
 constexpr int B_BYTES = HALF_TOK * SLICE_K * 2; // 16384
 constexpr int THREADS = 20 * 32;       // warps 0-11: producers, issuers, converters; warps 12-19: write-back
@@ -213,12 +214,16 @@ struct PairParams {
 // twice: two issuer threads (warps 1 and 11) each own one accumulator and one 256-token half of the tile, so the
 // per-slice cost of an issuer (two barrier reads, four MMAs, a commit: about as long as the four MMAs run) is
 // paid in parallel and half as much weight conversion is done per flop; the write-back is not overlapped.
-template <bool WIDE>
+// KIND: BHD_TYPE_Q8_0, or BHD_TYPE_Q4_K (crates/beholdd-kernel/src/kquant.rs:176-241): the converter then forms
+// fp16((d * sc) * q - dmin * m) from a sub-block's nibbles; a 64-column slice is the pair of sub-blocks that shares 32
+// quant bytes (low nibbles, high nibbles), so a thread still converts one 32-column block of one row.
+template <uint32_t KIND, bool WIDE>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_constant__ CUtensorMap tmap_w,
                                                              const __grid_constant__ CUtensorMap tmap_x, const PairParams p) {
     constexpr uint32_t TOKT = WIDE ? 2 * TOK : TOK;              // tokens per tile
     constexpr uint32_t BS_BYTES = WIDE ? 2 * B_BYTES : B_BYTES;  // token bytes per stage and CTA
     constexpr uint32_t SB = SB_BYTES / BS_BYTES;
+    constexpr int PROW = pack_row_of(KIND), PBYTES = TILE_N * PROW;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t pk_full[2], pk_empty[2], full[FULL], done[DONE], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -269,8 +274,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                 for (uint32_t c = 0; c < chunks; ++c, ++gc) {
                     const uint32_t pb = gc & 1;
                     if (aborted() || !mbar_wait_relaxed(&pk_empty[pb], ((gc >> 1) & 1) ^ 1)) { give_up(); break; }
-                    mbar_arrive_expect_tx(&pk_full[pb], PACK_BYTES);
-                    tma_load_2d(pack_addr + pb * PACK_BYTES, &tmap_w, int(c * (PACK_ROW / 2)), int(p.row_base + n0), &pk_full[pb]);
+                    mbar_arrive_expect_tx(&pk_full[pb], PBYTES);
+                    tma_load_2d(pack_addr + pb * PACK_BYTES, &tmap_w, int(c * (PROW / 2)), int(p.row_base + n0), &pk_full[pb]);
                 }
             }
         }
@@ -335,44 +340,83 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
             for (uint32_t c = 0; c < chunks && ok; ++c, ++gc) {
                 const uint32_t pb = gc & 1;
                 if (aborted() || !mbar_wait_relaxed(&pk_full[pb], (gc >> 1) & 1)) { give_up(); ok = false; break; }
-                const uint32_t src_row = pack_addr + pb * PACK_BYTES + row * PACK_ROW + blk * 32;
+                const uint32_t src_row = pack_addr + pb * PACK_BYTES + row * PROW + (KIND == BHD_TYPE_Q8_0 ? blk * 32 : 0u);
 #pragma unroll
                 for (uint32_t kb = 0; kb < 4; ++kb) {  // unrolled: the register indices below are constants
                     if (c * 4 + kb >= slices) break;
                     const uint32_t s = g % SA;
                     if (aborted() || (g >= SA && !slice_done(g - SA))) { give_up(); ok = false; break; }
-                    // Two Q8_0 blocks = 68 bytes = 17 words [d0 | q0..q31 | d1 | q32..q63] from word 17 * kb of the row;
-                    // this thread's block is words 0..8 (block 0: d in the low half of word 0, quants straddling words)
-                    // or 8..16 (block 1: d in the high half of word 8, quants word-aligned). Read as three aligned
-                    // 16-byte loads from word 16 * kb: rows are 272 bytes apart, so the eight lanes of a quarter-warp
-                    // hit eight different 16-byte bank groups, and the nine words are v[kb .. kb + 8].
-                    uint32_t v[12];
-#pragma unroll
-                    for (int j = 0; j < 3; ++j) {
-                        const uint4 q4 = lds128(src_row + kb * 64 + 16 * j);
-                        v[4 * j] = q4.x; v[4 * j + 1] = q4.y; v[4 * j + 2] = q4.z; v[4 * j + 3] = q4.w;
-                    }
-                    const uint32_t* w = v + kb;
-                    const uint32_t dbits = blk == 0 ? (w[0] & 0xffffu) : (w[0] >> 16);
-                    const __half2 d2 = __half2half2(__ushort_as_half(uint16_t(dbits)));
                     const uint32_t a_dst = a_addr + s * A_BYTES + a_row_off;
+                    if constexpr (KIND == BHD_TYPE_Q8_0) {
+                        // Two Q8_0 blocks = 68 bytes = 17 words [d0 | q0..q31 | d1 | q32..q63] from word 17 * kb of the row;
+                        // this thread's block is words 0..8 (block 0: d in the low half of word 0, quants straddling words)
+                        // or 8..16 (block 1: d in the high half of word 8, quants word-aligned). Read as three aligned
+                        // 16-byte loads from word 16 * kb: rows are 272 bytes apart, so the eight lanes of a quarter-warp
+                        // hit eight different 16-byte bank groups, and the nine words are v[kb .. kb + 8].
+                        uint32_t v[12];
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {  // 8 quants -> one 16-byte chunk of the swizzled row
-                        uint32_t h[4];
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            const int q = 2 * ch + j;
-                            const uint32_t quad = blk == 0 ? __funnelshift_r(w[q], w[q + 1], 16) : w[q + 1];
-                            const uint32_t u = quad ^ 0x80808080u;  // 0x6400 | (q + 128) is the fp16 q + 1152
-                            const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140), hi = __byte_perm(u, 0x64646464u, 0x4342);
-                            const __half2 qa = __hsub2(*reinterpret_cast<const __half2*>(&lo), off);
-                            const __half2 qb = __hsub2(*reinterpret_cast<const __half2*>(&hi), off);
-                            const __half2 a = __hmul2(qa, d2), b = __hmul2(qb, d2);
-                            h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
-                            h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
+                        for (int j = 0; j < 3; ++j) {
+                            const uint4 q4 = lds128(src_row + kb * 64 + 16 * j);
+                            v[4 * j] = q4.x; v[4 * j + 1] = q4.y; v[4 * j + 2] = q4.z; v[4 * j + 3] = q4.w;
                         }
-                        const uint32_t chunk16 = (blk * 4 + uint32_t(ch)) ^ sw;  // 128B swizzle: chunk index XOR row mod 8
-                        sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
+                        const uint32_t* w = v + kb;
+                        const uint32_t dbits = blk == 0 ? (w[0] & 0xffffu) : (w[0] >> 16);
+                        const __half2 d2 = __half2half2(__ushort_as_half(uint16_t(dbits)));
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {  // 8 quants -> one 16-byte chunk of the swizzled row
+                            uint32_t h[4];
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const int q = 2 * ch + j;
+                                const uint32_t quad = blk == 0 ? __funnelshift_r(w[q], w[q + 1], 16) : w[q + 1];
+                                const uint32_t u = quad ^ 0x80808080u;  // 0x6400 | (q + 128) is the fp16 q + 1152
+                                const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140), hi = __byte_perm(u, 0x64646464u, 0x4342);
+                                const __half2 qa = __hsub2(*reinterpret_cast<const __half2*>(&lo), off);
+                                const __half2 qb = __hsub2(*reinterpret_cast<const __half2*>(&hi), off);
+                                const __half2 a = __hmul2(qa, d2), b = __hmul2(qb, d2);
+                                h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
+                                h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
+                            }
+                            const uint32_t chunk16 = (blk * 4 + uint32_t(ch)) ^ sw;  // 128B swizzle: chunk index XOR row mod 8
+                            sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
+                        }
+                    } else {
+                        // Q4_K superblock of the row (144 bytes: d, dmin, 12 scale bytes, 128 quant bytes). Slice kb is the
+                        // pair of sub-blocks (2kb, 2kb + 1) = the low and the high nibbles of quant bytes 32kb .. 32kb + 31.
+                        // Rows are 144 bytes apart: the 16-byte loads of a quarter-warp fall into eight different bank groups.
+                        const uint4 hd = lds128(src_row);
+                        const uint4 qa = lds128(src_row + 16 + 32 * kb), qb = lds128(src_row + 32 + 32 * kb);
+                        const uint32_t sc_w[3] = {hd.y, hd.z, hd.w};
+                        auto sbyte = [&](uint32_t i) { return (sc_w[i >> 2] >> (8 * (i & 3))) & 0xffu; };  // i is uniform in the warp
+                        const uint32_t sb = 2 * kb + blk;
+                        uint32_t sc, mn;   // scale_min_k4 (kquant.rs:176-185)
+                        if (sb < 4) {
+                            sc = sbyte(sb) & 63u;
+                            mn = sbyte(sb + 4) & 63u;
+                        } else {
+                            sc = (sbyte(sb + 4) & 0xFu) | ((sbyte(sb - 4) >> 6) << 4);
+                            mn = (sbyte(sb + 4) >> 4) | ((sbyte(sb) >> 6) << 4);
+                        }
+                        const float d = __half2float(__ushort_as_half(uint16_t(hd.x & 0xffffu))), dmin = __half2float(__ushort_as_half(uint16_t(hd.x >> 16)));
+                        const __half2 dsc2 = __float2half2_rn(__fmul_rn(d, float(sc))), ndm2 = __float2half2_rn(-__fmul_rn(dmin, float(mn)));
+                        const __half2 k1024 = __half2half2(__ushort_as_half(uint16_t(0x6400)));
+                        const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t h[4];
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const uint32_t u = (blk == 0 ? qw[2 * ch + j] : (qw[2 * ch + j] >> 4)) & 0x0F0F0F0Fu;  // 0x6400 | n is the fp16 1024 + n
+                                const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140), hi = __byte_perm(u, 0x64646464u, 0x4342);
+                                const __half2 na = __hsub2(*reinterpret_cast<const __half2*>(&lo), k1024);
+                                const __half2 nb = __hsub2(*reinterpret_cast<const __half2*>(&hi), k1024);
+                                const __half2 a = __hfma2(na, dsc2, ndm2), b = __hfma2(nb, dsc2, ndm2);
+                                h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
+                                h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
+                            }
+                            const uint32_t chunk16 = (blk * 4 + uint32_t(ch)) ^ sw;
+                            sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
                     __syncwarp();
@@ -423,7 +467,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 }  // namespace
 
-// Dense prefill on CTA pairs, M >= 256: Y[m][n] = sum_k fp16(X[m][k]) * fp16(W[n][k]); x16 is the fp16 copy of X.
+// Dense prefill on CTA pairs (Q8_0 or Q4_K weights), M >= 256: Y[m][n] = sum_k fp16(X[m][k]) * fp16(W[n][k]); x16 is the fp16 copy of X.
 // wide: 512-token tiles with two issuers (see the kernel); else 256-token tiles with an overlapped write-back.
 int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, bool wide,
                                 cudaStream_t s) {
@@ -432,8 +476,10 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
     static bhd_once_per_device once;
     const size_t dyn = 1024 + 2 * size_t(PACK_BYTES) + size_t(SA) * A_BYTES + size_t(SB_BYTES);
     if (once.pending(ctx)) {
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
-        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q4_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q4_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
         BHD_CUDA(ctx, cudaDeviceGetAttribute(&sm_count[ctx->device], cudaDevAttrMultiProcessorCount, ctx->device), "reading the SM count");
         once.mark(ctx);
     }
@@ -447,7 +493,7 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
     {
         const cuuint64_t dims[2] = {w->row_bytes / 2, w->rows * w->slabs};
         const cuuint64_t strides[1] = {w->row_bytes};
-        const cuuint32_t box[2] = {PACK_ROW / 2, TILE_N};
+        const cuuint32_t box[2] = {cuuint32_t(pack_row_of(w->kind) / 2), TILE_N};
         const cuuint32_t estr[2] = {1, 1};
         if (encode(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->dev, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -483,8 +529,11 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
-    else BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    const bool q4 = w->kind == BHD_TYPE_Q4_K;
+    if (q4 && wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q4_K, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    else if (q4) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q4_K, false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    else if (wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q8_0, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    else BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q8_0, false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
     ctx->launches += 1;
     return BHD_OK;
 }

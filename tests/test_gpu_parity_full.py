@@ -152,6 +152,39 @@ def test_every_prefill_kernel_form_gives_the_same_bits(dev, oracle, m, n, k):
     w.free()
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 4096, 4096), (2048, 12288, 4096), (700, 520, 2048), (256, 130, 1024)])
+def test_q4_k_prefill_on_the_tensor_cores_against_oracle_sample(dev, oracle, m, n, k):
+    """Q4_K weights take the CTA-pair matmul from 256 tokens on (the converter forms fp16((d * sc) * q - dmin * m) from
+    the nibbles): 16 sampled positions against the oracle on all columns, both tile widths bit-identical."""
+    import torch
+    from exec_beholdd_b200 import Weight, synth
+
+    packed = synth.q4_k_matrix(161, n, k)
+    x = synth.activations(163, (m, k), outliers=True)
+    sample = np.unique(np.minimum(np.concatenate([np.arange(0, m, max(1, m // 14)), [255, 256, m - 1]]), m - 1))
+    want = oracle.matvec_batch(packed, 12, n, k, x[sample])
+    w = dev.upload_weight(Weight(packed, 12, n, k))
+    xd = cuda(x)
+    outs = {}
+    try:
+        for impl in (0, 3, 5):
+            assert dev.lib.bhd_debug_option(dev.ctx, 3, impl) == 0
+            launches = dev.launch_count
+            y = torch.full((m, n), float("nan"), device="cuda")
+            dev.matmul_resident(w, xd, y)
+            dev.check_status()
+            assert dev.launch_count - launches == 2          # the fp16 conversion of x and one matmul kernel
+            outs[impl] = y.cpu().numpy()
+            assert np.isfinite(outs[impl]).all()
+            err = max_rel_err(outs[impl][sample], want)
+            print(f"Q4_K prefill M={m} N={n} K={k} form {impl}: max-rel-err {err:.2e}")
+            assert err <= TOL, impl
+    finally:
+        dev.lib.bhd_debug_option(dev.ctx, 3, 0)
+    assert np.array_equal(outs[3].view(np.uint32), outs[5].view(np.uint32))
+    w.free()
+
+
 def moe_inputs(seed, n_experts, dim, ff, T, tails):
     from exec_beholdd_b200 import synth
 
