@@ -215,7 +215,7 @@ struct PairParams {
 // per-slice cost of an issuer (two barrier reads, four MMAs, a commit: about as long as the four MMAs run) is
 // paid in parallel and half as much weight conversion is done per flop; the write-back is not overlapped.
 // KIND: BHD_TYPE_Q8_0, or BHD_TYPE_Q4_K (crates/beholdd-kernel/src/kquant.rs:176-241): the converter then forms
-// fp16((d * sc) * q - dmin * m) from a sub-block's nibbles; a 64-column slice is the pair of sub-blocks that shares 32
+// fp16((d * sc) * q - dmin * m), computed in f32, from a sub-block's nibbles; a 64-column slice is the pair of sub-blocks that shares 32
 // quant bytes (low nibbles, high nibbles), so a thread still converts one 32-column block of one row.
 template <uint32_t KIND, bool WIDE>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_constant__ CUtensorMap tmap_w,
@@ -398,19 +398,20 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                             mn = (sbyte(sb + 4) >> 4) | ((sbyte(sb) >> 6) << 4);
                         }
                         const float d = __half2float(__ushort_as_half(uint16_t(hd.x & 0xffffu))), dmin = __half2float(__ushort_as_half(uint16_t(hd.x >> 16)));
-                        const __half2 dsc2 = __float2half2_rn(__fmul_rn(d, float(sc))), ndm2 = __float2half2_rn(-__fmul_rn(dmin, float(mn)));
-                        const __half2 k1024 = __half2half2(__ushort_as_half(uint16_t(0x6400)));
+                        // The value is formed in f32 and rounded to fp16 once: d * sc * q and dmin * m usually cancel to a large
+                        // part, so rounding the two terms to fp16 first would double the error of the difference.
+                        const float dsc = __fmul_rn(d, float(sc)), ndm = -__fmul_rn(dmin, float(mn));
                         const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                        // byte k of u under the exponent of 2^23: the f32 8388608 + n, from which n by one subtraction
+                        auto nib = [](uint32_t u, uint32_t sel) { return __uint_as_float(__byte_perm(u, 0x4B000000u, sel)) - 8388608.0f; };
 #pragma unroll
                         for (int ch = 0; ch < 4; ++ch) {
                             uint32_t h[4];
 #pragma unroll
                             for (int j = 0; j < 2; ++j) {
-                                const uint32_t u = (blk == 0 ? qw[2 * ch + j] : (qw[2 * ch + j] >> 4)) & 0x0F0F0F0Fu;  // 0x6400 | n is the fp16 1024 + n
-                                const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140), hi = __byte_perm(u, 0x64646464u, 0x4342);
-                                const __half2 na = __hsub2(*reinterpret_cast<const __half2*>(&lo), k1024);
-                                const __half2 nb = __hsub2(*reinterpret_cast<const __half2*>(&hi), k1024);
-                                const __half2 a = __hfma2(na, dsc2, ndm2), b = __hfma2(nb, dsc2, ndm2);
+                                const uint32_t u = (blk == 0 ? qw[2 * ch + j] : (qw[2 * ch + j] >> 4)) & 0x0F0F0F0Fu;
+                                const __half2 a = __floats2half2_rn(fmaf(nib(u, 0x7440), dsc, ndm), fmaf(nib(u, 0x7441), dsc, ndm));
+                                const __half2 b = __floats2half2_rn(fmaf(nib(u, 0x7442), dsc, ndm), fmaf(nib(u, 0x7443), dsc, ndm));
                                 h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
                                 h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
                             }
