@@ -346,12 +346,12 @@ def bench_matvec_e2e(dev, torch, kind, steps, warmup, copies, passes):
             "how": "bhd_matvec_host_async per matvec, bhd_sync and a host read of y once per pass over the weight copies"}
 
 
-def bench_prefill(dev, torch, M, N, K, steps, warmup, peak_tflops):
-    """Q8_0 prefill matmul Y[M x N] = X[M x K] W^T (tensor-core bound for M >= 512)."""
+def bench_prefill(dev, torch, M, N, K, steps, warmup, peak_tflops, kind=8):
+    """Q8_0 (or Q4_K) prefill matmul Y[M x N] = X[M x K] W^T (tensor-core bound for M >= 512)."""
     from exec_beholdd_b200 import synth
 
-    packed = torch.from_numpy(synth.q8_0_matrix(SEED + 5, N, K)).cuda()
-    w = dev.wrap_weight(packed, 8, N, K)
+    packed = torch.from_numpy(synth.matrix(kind, SEED + 5, N, K)).cuda()
+    w = dev.wrap_weight(packed, kind, N, K)
     x = torch.from_numpy(synth.activations(SEED + 6, (M, K), outliers=True)).cuda()
     y = torch.empty((M, N), device="cuda")
     secs = time_region(torch, lambda: dev.matmul_resident(w, x, y), steps, warmup)
@@ -644,12 +644,16 @@ def run_gpu_arm(args):
                     detail[f"{KIND_NAME[kind]}_b{batch}"] = r if "error" in r else {
                         "gbs": round(r["gbs"], 1), "us": round(r["us_per_matvec"], 2), "frac_of_peak": round(r["gbs"] / peak, 4),
                         "timed_ms": round(r["timed_ms"], 1), "sm_mhz": r.get("sm_mhz")}
-        prefill = {}
+        prefill, prefill_q4 = {}, {}
         if not args.quick and "prefill" in sections and world == 1:
             shapes = [tuple(int(d) for d in v.split("x")) for v in args.prefill_shapes.split(",") if v]
             for (M, N) in shapes:
                 psteps = max(dsteps, min(2000, int(0.2 / (2.0 * M * N * 4096 / (0.5 * tpeak * 1e12)))))  # about 0.2 s per leg
                 prefill[f"M{M}_N{N}"] = leg(f"prefill_M{M}_N{N}", lambda: bench_prefill(dev, torch, M, N, 4096, psteps, 3, tpeak))
+            for (M, N) in shapes:   # the same kernel with Q4_K weights (from 256 tokens on), on the large row count
+                if M >= 256 and N == max(n for _, n in shapes):
+                    psteps = max(dsteps, min(2000, int(0.2 / (2.0 * M * N * 4096 / (0.5 * tpeak * 1e12)))))
+                    prefill_q4[f"M{M}_N{N}"] = leg(f"prefill_q4_k_M{M}_N{N}", lambda: bench_prefill(dev, torch, M, N, 4096, psteps, 3, tpeak, kind=12))
         moe = {}
         tokens = () if (args.quick or "moe" not in sections) else tuple(int(v) for v in args.moe_tokens.split(",") if v)
         if world == 1:
@@ -700,7 +704,7 @@ def run_gpu_arm(args):
                          "traffic": HEAD_TRAFFIC_BYTES, "peak_source": peak_kind,
                          "kernel": "k_matvec_decode_i8 (the only kernel of the step)", "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
-            "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "moe_layer": moe,
+            "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "prefill_q4_k_k4096": prefill_q4, "moe_layer": moe,
             "row_split_projection": row_split, "full_forward": full,
         }
         if errors:
