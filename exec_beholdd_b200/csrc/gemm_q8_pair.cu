@@ -1,6 +1,6 @@
-// Prefill matmul for packed Q8_0 and Q4_K weights: persistent CTA pairs (tcgen05 cta_group::2).
+// Prefill matmul for packed Q8_0, Q4_K and Q6_K weights: persistent CTA pairs (tcgen05 cta_group::2).
 //
-//   Y[m][n] = sum_k X[m][k] * W[n][k],   W packed Q8_0 or Q4_K [N x K], X fp16 [M x K] (converted once per call), Y f32.
+//   Y[m][n] = sum_k X[m][k] * W[n][k],   W packed Q8_0, Q4_K or Q6_K [N x K], X fp16 [M x K] (converted once per call), Y f32.
 //
 // A cluster of two CTAs on neighbouring SMs works on one 256-row x 256-token tile at a time. Each CTA converts its
 // own 128 weight rows (packed chunk by TMA -> fp16 K-major 128B-swizzled tile in its shared memory, block scale
@@ -40,7 +40,9 @@ constexpr int CHUNK_K = 256;           // columns per packed chunk
 constexpr int SLICE_K = 64;            // columns per fp16 stage (one 128-byte swizzle row)
 constexpr int PACK_ROW = 272;          // packed bytes per row per chunk: Q8_0 (eight blocks of 34 bytes); Q4_K: 144 (one superblock)
 constexpr int PACK_BYTES = TILE_N * PACK_ROW;   // 34816, a multiple of 1024: the size of a chunk buffer for either format
-__host__ __device__ constexpr int pack_row_of(uint32_t kind) { return kind == BHD_TYPE_Q4_K ? 144 : 272; }
+// Q6_K: a 240-byte window that starts at the 16-byte boundary at or below the row's 210-byte superblock (a TMA copy must
+// start on one) and so holds it at an even offset of 0..14 bytes.
+__host__ __device__ constexpr int pack_row_of(uint32_t kind) { return kind == BHD_TYPE_Q4_K ? 144 : (kind == BHD_TYPE_Q6_K ? 240 : 272); }
 constexpr int A_BYTES = TILE_N * SLICE_K * 2;   // 16384
 constexpr int B_BYTES = HALF_TOK * SLICE_K * 2; // 16384
 constexpr int THREADS = 20 * 32;       // warps 0-11: producers, issuers, converters; warps 12-19: write-back
@@ -275,7 +277,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                     const uint32_t pb = gc & 1;
                     if (aborted() || !mbar_wait_relaxed(&pk_empty[pb], ((gc >> 1) & 1) ^ 1)) { give_up(); break; }
                     mbar_arrive_expect_tx(&pk_full[pb], PBYTES);
-                    tma_load_2d(pack_addr + pb * PACK_BYTES, &tmap_w, int(c * (PROW / 2)), int(p.row_base + n0), &pk_full[pb]);
+                    const uint32_t byte0 = KIND == BHD_TYPE_Q6_K ? ((210u * c) & ~15u) : uint32_t(PROW) * c;
+                    tma_load_2d(pack_addr + pb * PACK_BYTES, &tmap_w, int(byte0 / 2), int(p.row_base + n0), &pk_full[pb]);
                 }
             }
         }
@@ -380,7 +383,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                             const uint32_t chunk16 = (blk * 4 + uint32_t(ch)) ^ sw;  // 128B swizzle: chunk index XOR row mod 8
                             sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
                         }
-                    } else {
+                    } else if constexpr (KIND == BHD_TYPE_Q4_K) {
                         // Q4_K superblock of the row (144 bytes: d, dmin, 12 scale bytes, 128 quant bytes). Slice kb is the
                         // pair of sub-blocks (2kb, 2kb + 1) = the low and the high nibbles of quant bytes 32kb .. 32kb + 31.
                         // Rows are 144 bytes apart: the 16-byte loads of a quarter-warp fall into eight different bank groups.
@@ -412,6 +415,58 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
                                 const uint32_t u = (blk == 0 ? qw[2 * ch + j] : (qw[2 * ch + j] >> 4)) & 0x0F0F0F0Fu;
                                 const __half2 a = __floats2half2_rn(fmaf(nib(u, 0x7440), dsc, ndm), fmaf(nib(u, 0x7441), dsc, ndm));
                                 const __half2 b = __floats2half2_rn(fmaf(nib(u, 0x7442), dsc, ndm), fmaf(nib(u, 0x7443), dsc, ndm));
+                                h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
+                                h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
+                            }
+                            const uint32_t chunk16 = (blk * 4 + uint32_t(ch)) ^ sw;
+                            sts128(a_dst + chunk16 * 16, make_uint4(h[0], h[1], h[2], h[3]));
+                        }
+                    } else {
+                        // Q6_K superblock (crates/beholdd-kernel/src/kquant.rs:115-162; 210 bytes: ql[128], qh[64], 16 int8 scales, d)
+                        // at byte `o` of the row's window. Slice kb covers two of the four 32-element groups of the 128-element half
+                        // kb / 2; this thread's group gi takes the low (gi < 2) or high nibbles of 32 ql bytes and two bits of 32
+                        // qh bytes: value = d * scale * (code - 32), one scale per 16 elements. Both byte fields start `o` bytes after
+                        // a 32-byte boundary: three aligned 16-byte loads each (rows 240 bytes apart: no bank conflicts), then the
+                        // words are moved down by o / 4 words with two layers of selects and by the odd half-word with funnel shifts.
+                        const uint32_t o = (210u * c) & 15u, o4 = o >> 2, ob = (o & 2u) * 8u;   // uniform in the CTA
+                        const uint32_t half = kb >> 1, gi = 2 * (kb & 1) + blk;
+                        auto field = [&](uint32_t addr, uint32_t (&w)[8]) {
+                            uint32_t v[12];
+#pragma unroll
+                            for (int j = 0; j < 3; ++j) {
+                                const uint4 q4 = lds128(addr + 16 * j);
+                                v[4 * j] = q4.x; v[4 * j + 1] = q4.y; v[4 * j + 2] = q4.z; v[4 * j + 3] = q4.w;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 11; ++i) v[i] = (o4 & 1u) ? v[i + 1] : v[i];
+#pragma unroll
+                            for (int i = 0; i < 9; ++i) v[i] = (o4 & 2u) ? v[i + 2] : v[i];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], ob);
+                        };
+                        uint32_t wl[8], wh[8];
+                        field(src_row + 64 * half + 32 * (gi & 1), wl);
+                        field(src_row + 128 + 32 * half, wh);
+                        const uint32_t meta = src_row + o;
+                        int sc0, sc1;
+                        uint32_t dbits;
+                        asm volatile("ld.shared.s8 %0, [%1];" : "=r"(sc0) : "r"(meta + 192 + 8 * half + 2 * gi));
+                        asm volatile("ld.shared.s8 %0, [%1];" : "=r"(sc1) : "r"(meta + 193 + 8 * half + 2 * gi));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits) : "r"(meta + 208));
+                        const float d = __half2float(__ushort_as_half(uint16_t(dbits)));
+                        const float ds[2] = {__fmul_rn(d, float(sc0)), __fmul_rn(d, float(sc1))};
+                        // byte k of the codes under the exponent of 2^23: the f32 8388608 + code, from which code - 32 by one subtraction
+                        auto code = [](uint32_t u, uint32_t sel) { return __uint_as_float(__byte_perm(u, 0x4B000000u, sel)) - 8388640.0f; };
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t h[4];
+                            const float dsc = ds[ch >> 1];   // elements 8ch .. 8ch + 7: scale 0 for the first sixteen
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const uint32_t lo4 = ((gi & 2u) ? (wl[2 * ch + j] >> 4) : wl[2 * ch + j]) & 0x0F0F0F0Fu;
+                                const uint32_t u = lo4 | (((wh[2 * ch + j] >> (2 * gi)) & 0x03030303u) << 4);
+                                const __half2 a = __floats2half2_rn(__fmul_rn(code(u, 0x7440), dsc), __fmul_rn(code(u, 0x7441), dsc));
+                                const __half2 b = __floats2half2_rn(__fmul_rn(code(u, 0x7442), dsc), __fmul_rn(code(u, 0x7443), dsc));
                                 h[2 * j] = *reinterpret_cast<const uint32_t*>(&a);
                                 h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
                             }
@@ -468,7 +523,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 }  // namespace
 
-// Dense prefill on CTA pairs (Q8_0 or Q4_K weights), M >= 256: Y[m][n] = sum_k fp16(X[m][k]) * fp16(W[n][k]); x16 is the fp16 copy of X.
+// Dense prefill on CTA pairs (Q8_0, Q4_K or Q6_K weights), M >= 256: Y[m][n] = sum_k fp16(X[m][k]) * fp16(W[n][k]); x16 is the fp16 copy of X.
 // wide: 512-token tiles with two issuers (see the kernel); else 256-token tiles with an overlapped write-back.
 int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const void* x16, float* y, uint32_t M, bool wide,
                                 cudaStream_t s) {
@@ -481,6 +536,8 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
         BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
         BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q4_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
         BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q4_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q6_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_gemm_q8_pair<BHD_TYPE_Q6_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn)), "raising the shared memory limit");
         BHD_CUDA(ctx, cudaDeviceGetAttribute(&sm_count[ctx->device], cudaDevAttrMultiProcessorCount, ctx->device), "reading the SM count");
         once.mark(ctx);
     }
@@ -530,8 +587,10 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const bool q4 = w->kind == BHD_TYPE_Q4_K;
-    if (q4 && wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q4_K, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    const bool q4 = w->kind == BHD_TYPE_Q4_K, q6 = w->kind == BHD_TYPE_Q6_K;
+    if (q6 && wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q6_K, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    else if (q6) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q6_K, false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
+    else if (q4 && wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q4_K, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
     else if (q4) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q4_K, false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
     else if (wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q8_0, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
     else BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q8_0, false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");

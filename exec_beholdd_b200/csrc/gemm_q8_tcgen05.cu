@@ -466,8 +466,10 @@ bool bhd_gemm_q8_grouped_usable(const bhd_ctx* ctx, const bhd_weight* w) {
 int32_t bhd_launch_gemm_q8_tcgen05(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab, const float* x, float* y, uint64_t m,
                                    cudaStream_t s, bool* handled) {
     *handled = false;
-    // Q8_0 from 64 tokens on; Q4_K from 256 tokens on (the CTA-pair kernel converts both, the per-tile kernels Q8_0 only)
-    const bool q4 = w->kind == BHD_TYPE_Q4_K && m >= 256 && w->cols % 256 == 0 && (ctx->gemm_impl == 0 || ctx->gemm_impl == 3 || ctx->gemm_impl == 5);
+    // Q8_0 from 64 tokens on; Q4_K and Q6_K from 256 tokens on (the CTA-pair kernel converts all three, the per-tile kernels
+    // Q8_0 only)
+    const bool q4 = (w->kind == BHD_TYPE_Q4_K || w->kind == BHD_TYPE_Q6_K) && m >= 256 && w->cols % 256 == 0 && w->row_bytes % 16 == 0 &&
+                    (ctx->gemm_impl == 0 || ctx->gemm_impl == 3 || ctx->gemm_impl == 5);
     if ((w->kind != BHD_TYPE_Q8_0 && !q4) || !ctx->tmap_encode || m < 64 || m > 0x7fffffffull) return BHD_OK;
     if (w->row_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(w->dev) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return BHD_OK;
     if (w->cols == 0 || w->cols % 32 != 0 || w->rows > 0x7fffffffull || w->rows * w->slabs > 0x7fffffffull) return BHD_OK;

@@ -185,6 +185,60 @@ def test_q4_k_prefill_on_the_tensor_cores_against_oracle_sample(dev, oracle, m, 
     w.free()
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 4096, 4096), (2048, 12288, 4096), (700, 520, 2048), (256, 130, 6144)])
+def test_q6_k_prefill_on_the_tensor_cores_against_oracle_sample(dev, oracle, m, n, k):
+    """Q6_K weights whose rows are a multiple of 16 bytes (columns a multiple of 2048) take the CTA-pair matmul from 256
+    tokens on: the 210-byte superblocks sit at every even offset 0..14 of their 16-byte aligned windows over a row, and the
+    converter forms fp16((d * scale) * (code - 32)). 16 sampled positions against the oracle, both tile widths
+    bit-identical."""
+    import torch
+    from exec_beholdd_b200 import Weight, synth
+
+    packed = synth.q6_k_matrix(171, n, k)
+    x = synth.activations(173, (m, k), outliers=True)
+    sample = np.unique(np.minimum(np.concatenate([np.arange(0, m, max(1, m // 14)), [255, 256, m - 1]]), m - 1))
+    want = oracle.matvec_batch(packed, 14, n, k, x[sample])
+    w = dev.upload_weight(Weight(packed, 14, n, k))
+    xd = cuda(x)
+    outs = {}
+    try:
+        for impl in (0, 3, 5):
+            assert dev.lib.bhd_debug_option(dev.ctx, 3, impl) == 0
+            launches = dev.launch_count
+            y = torch.full((m, n), float("nan"), device="cuda")
+            dev.matmul_resident(w, xd, y)
+            dev.check_status()
+            assert dev.launch_count - launches == 2          # the fp16 conversion of x and one matmul kernel
+            outs[impl] = y.cpu().numpy()
+            assert np.isfinite(outs[impl]).all()
+            err = max_rel_err(outs[impl][sample], want)
+            print(f"Q6_K prefill M={m} N={n} K={k} form {impl}: max-rel-err {err:.2e}")
+            assert err <= TOL, impl
+    finally:
+        dev.lib.bhd_debug_option(dev.ctx, 3, 0)
+    assert np.array_equal(outs[3].view(np.uint32), outs[5].view(np.uint32))
+    w.free()
+
+
+def test_q6_k_prefill_with_rows_off_the_16_byte_grid_keeps_the_batched_kernels(dev, oracle):
+    """Three Q6_K superblocks a row are 630 bytes: no tensor map can stride over such rows, so the matmul stays on the
+    integer batched kernels and still agrees with the oracle."""
+    from exec_beholdd_b200 import Weight, synth
+
+    m, n, k = 256, 96, 768
+    packed = synth.q6_k_matrix(175, n, k)
+    x = synth.activations(177, (m, k))
+    w = dev.upload_weight(Weight(packed, 14, n, k))
+    import torch
+    y = torch.full((m, n), float("nan"), device="cuda")
+    dev.matmul_resident(w, cuda(x), y)
+    dev.check_status()
+    got = y.cpu().numpy()
+    want = oracle.matvec_batch(packed, 14, n, k, x)
+    assert max_rel_err(got, want) <= TOL
+    w.free()
+
+
 def moe_inputs(seed, n_experts, dim, ff, T, tails):
     from exec_beholdd_b200 import synth
 
