@@ -644,7 +644,7 @@ def run_gpu_arm(args):
                     detail[f"{KIND_NAME[kind]}_b{batch}"] = r if "error" in r else {
                         "gbs": round(r["gbs"], 1), "us": round(r["us_per_matvec"], 2), "frac_of_peak": round(r["gbs"] / peak, 4),
                         "timed_ms": round(r["timed_ms"], 1), "sm_mhz": r.get("sm_mhz")}
-        prefill, prefill_q4 = {}, {}
+        prefill, prefill_q4, prefill_q6 = {}, {}, {}
         if not args.quick and "prefill" in sections and world == 1:
             shapes = [tuple(int(d) for d in v.split("x")) for v in args.prefill_shapes.split(",") if v]
             for (M, N) in shapes:
@@ -654,6 +654,7 @@ def run_gpu_arm(args):
                 if M >= 256 and N == max(n for _, n in shapes):
                     psteps = max(dsteps, min(2000, int(0.2 / (2.0 * M * N * 4096 / (0.5 * tpeak * 1e12)))))
                     prefill_q4[f"M{M}_N{N}"] = leg(f"prefill_q4_k_M{M}_N{N}", lambda: bench_prefill(dev, torch, M, N, 4096, psteps, 3, tpeak, kind=12))
+                    prefill_q6[f"M{M}_N{N}"] = leg(f"prefill_q6_k_M{M}_N{N}", lambda: bench_prefill(dev, torch, M, N, 4096, psteps, 3, tpeak, kind=14))
         moe = {}
         tokens = () if (args.quick or "moe" not in sections) else tuple(int(v) for v in args.moe_tokens.split(",") if v)
         if world == 1:
@@ -704,7 +705,7 @@ def run_gpu_arm(args):
                          "traffic": HEAD_TRAFFIC_BYTES, "peak_source": peak_kind,
                          "kernel": "k_matvec_decode_i8 (the only kernel of the step)", "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
-            "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "prefill_q4_k_k4096": prefill_q4, "moe_layer": moe,
+            "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "prefill_q4_k_k4096": prefill_q4, "prefill_q6_k_k4096": prefill_q6, "moe_layer": moe,
             "row_split_projection": row_split, "full_forward": full,
         }
         if errors:
