@@ -535,6 +535,7 @@ int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value) {
         case BHD_OPTION_MOE_TC_PLAIN: ctx->moe_tc_plain = value; return BHD_OK;
         case BHD_OPTION_GEMM_IMPL: ctx->gemm_impl = value; return BHD_OK;
         case BHD_OPTION_ROUTER_TILING: ctx->router_variant = value; return BHD_OK;
+        case BHD_OPTION_PLAIN_LAUNCHES: ctx->plain_launches = value; return BHD_OK;
         default: return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "debug_option: unknown key %u", key);
     }
 }

@@ -185,6 +185,7 @@ namespace {
 
 // SiLU gating, crates/beholdd-kernel/src/vecops.rs:91-111.
 __global__ void k_swiglu(float* __restrict__ gate, const float* __restrict__ up, uint64_t n, float limit) {
+    bhd_wait_for_prior_kernels();
     const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
     if (i >= n) return;
     float g = gate[i], u = up[i];
@@ -196,6 +197,7 @@ __global__ void k_swiglu(float* __restrict__ gate, const float* __restrict__ up,
 }
 
 __global__ void k_add_in_place(float* __restrict__ out, const float* __restrict__ res, uint64_t n) {
+    bhd_wait_for_prior_kernels();
     const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
     if (i < n) out[i] = __fadd_rn(out[i], res[i]);
 }
@@ -208,7 +210,7 @@ extern "C" int32_t bhd_swiglu(bhd_ctx* ctx, float* gate_dev, const float* up_dev
     if (n == 0) return BHD_OK;
     if (!gate_dev || !up_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "swiglu: null buffer");
     bhd_device_guard guard(ctx);
-    k_swiglu<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(gate_dev, up_dev, n, limit);
+    bhd_launch_dependent(ctx, k_swiglu, dim3(unsigned((n + 255) / 256)), dim3(256), 0, cudaStream_t(stream), gate_dev, up_dev, n, limit);
     BHD_LAUNCHED(ctx, "swiglu kernel");
     return BHD_OK;
 }
@@ -219,7 +221,7 @@ extern "C" int32_t bhd_add_in_place(bhd_ctx* ctx, float* output_dev, const float
     if (n == 0) return BHD_OK;
     if (!output_dev || !residual_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "add_in_place: null buffer");
     bhd_device_guard guard(ctx);
-    k_add_in_place<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(output_dev, residual_dev, n);
+    bhd_launch_dependent(ctx, k_add_in_place, dim3(unsigned((n + 255) / 256)), dim3(256), 0, cudaStream_t(stream), output_dev, residual_dev, n);
     BHD_LAUNCHED(ctx, "add_in_place kernel");
     return BHD_OK;
 }

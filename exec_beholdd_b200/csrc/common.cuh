@@ -44,6 +44,7 @@ struct bhd_ctx {
     uint32_t moe_tc_min_cls; // smallest group size class the tensor-core grouped kernel takes (0: the default)
     uint32_t moe_tc_plain;   // 1: the tensor-core grouped kernel with singly rounded fp16 operands in shared memory
     uint32_t router_variant; // tiling of the router-logits kernel for more than 64 positions (0: default)
+    uint32_t plain_launches; // 1: no programmatic dependent launches (every kernel starts after the one before it ended)
     uint32_t gemm_impl;      // prefill matmul: 0 the library's choice, 1 one CTA per tile, 2 the same with the weight operand in tensor memory, 3 CTA pairs, 4 persistent CTAs, 5 CTA pairs on 512-token tiles
     uint64_t launches;
     void* tmap_encode;      // cuTensorMapEncodeTiled, resolved once at creation
@@ -118,6 +119,30 @@ bool bhd_block_geometry(uint32_t kind, uint64_t* elems, uint64_t* bytes);
         if (_e != cudaSuccess) return bhd_cuda_fail(ctx, _e, what); \
         (ctx)->launches += 1;                                       \
     } while (0)
+
+// ---- dependent launches -----------------------------------------------------------------
+// A kernel launched through bhd_launch_dependent may be scheduled while the kernel before it in the stream is still
+// draining (programmatic dependent launch), which hides most of the launch latency of a chain of short kernels. Such a
+// kernel executes bhd_wait_for_prior_kernels() as its first statement: that returns once every kernel before it in
+// the stream has finished and its writes are visible, so the ordering is that of a plain launch. Never give the
+// attribute to a kernel that does not wait: its successor would only wait for it, not for the kernels before it.
+__device__ __forceinline__ void bhd_wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void bhd_launch_dependent(const bhd_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->plain_launches ? 0 : 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);  // the caller reads the outcome with BHD_LAUNCHED
+}
 
 // ---- per-element decoders -------------------------------------------------------------
 // Each returns exactly the f32 the reference's CPU decoder produces for element k of a

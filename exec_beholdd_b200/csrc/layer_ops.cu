@@ -43,6 +43,7 @@ __device__ __forceinline__ void rmsnorm_row(float* yr, const float* xr, const fl
 
 __global__ void __launch_bounds__(256) k_rmsnorm(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, uint64_t n,
                                                  float eps) {
+    bhd_wait_for_prior_kernels();
     __shared__ double s_part[8];
     __shared__ float s_inv;
     rmsnorm_row(y + blockIdx.x * n, x + blockIdx.x * n, w, n, eps, s_part, &s_inv);
@@ -59,6 +60,7 @@ __global__ void __launch_bounds__(256) k_qk_norm_rope_store(float* __restrict__ 
                                                             const int32_t* __restrict__ pos_dev, uint32_t max_positions, uint32_t n_heads,
                                                             uint32_t n_kv_heads, uint32_t head_dim, float eps, int layout,
                                                             uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
     __shared__ double s_part[8];
     __shared__ float s_inv;
     const int32_t pos = *pos_dev;
@@ -100,6 +102,7 @@ __global__ void __launch_bounds__(256) k_qk_norm_rope_store(float* __restrict__ 
 // With pos_dev, the first position's table row is read from device memory (a decode step replayed as a CUDA graph).
 __global__ void k_rope(float* __restrict__ x, const float* __restrict__ cos, const float* __restrict__ sin, uint64_t n_vectors,
                        uint32_t vectors_per_position, uint32_t n_pairs, int layout, int inverse, const int32_t* __restrict__ pos_dev) {
+    bhd_wait_for_prior_kernels();
     const uint64_t idx = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
     if (idx >= n_vectors * n_pairs) return;
     const uint64_t vec = idx / n_pairs, i = idx - vec * n_pairs, pos = vec / vectors_per_position + (pos_dev ? uint64_t(*pos_dev) : 0ull);
@@ -116,6 +119,7 @@ __global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, cons
                                                    const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_heads,
                                                    uint32_t n_kv_heads, uint32_t head_dim, float scale, const int32_t* __restrict__ start_dev,
                                                    uint32_t max_positions, uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
     extern __shared__ float scores[];
     __shared__ float s_max, s_inv;
     const uint32_t qp = blockIdx.x, head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
@@ -185,6 +189,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
                                                                  uint32_t n_kv_heads, uint32_t head_dim, float scale,
                                                                  const int32_t* __restrict__ start_dev, uint32_t max_positions,
                                                                  uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
     extern __shared__ __align__(16) float att_smem[];
     __shared__ float s_max, s_inv;
     const uint32_t qp = blockIdx.x, head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
@@ -316,10 +321,10 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
     const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
     const size_t tiled_smem = (size_t(ATT_TILE_FLOATS) + head_dim + score_slots) * sizeof(float);
     if (aligned && head_dim % 4 == 0 && head_dim >= 32 && head_dim <= 256 && ATT_TILE_FLOATS % head_dim == 0 && tiled_smem <= 200 * 1024) {
-        k_attention_tiled<<<dim3(n_query, n_heads), ATT_THREADS, tiled_smem, s>>>(out, q, k, v, query_start, n_heads, n_kv_heads, head_dim, scale,
+        bhd_launch_dependent(ctx, k_attention_tiled, dim3(n_query, n_heads), dim3(ATT_THREADS), tiled_smem, s, out, q, k, v, query_start, n_heads, n_kv_heads, head_dim, scale,
                                                                                    start_dev, max_positions, ctx->status_dev);
     } else {
-        k_attention<<<dim3(n_query, n_heads), 128, size_t(score_slots) * sizeof(float), s>>>(out, q, k, v, query_start, n_heads, n_kv_heads, head_dim,
+        bhd_launch_dependent(ctx, k_attention, dim3(n_query, n_heads), dim3(128), size_t(score_slots) * sizeof(float), s, out, q, k, v, query_start, n_heads, n_kv_heads, head_dim,
                                                                                               scale, start_dev, max_positions, ctx->status_dev);
     }
     BHD_LAUNCHED(ctx, "attention kernel");
@@ -329,6 +334,7 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
 // Command::SigmoidGate (crates/beholdd-backend/src/execution.rs:1425-1441): out = in * sigmoid(gate), the sigmoid in its
 // overflow-free form.
 __global__ void k_sigmoid_gate(float* __restrict__ out, const float* __restrict__ in, const float* __restrict__ gate, uint64_t n) {
+    bhd_wait_for_prior_kernels();
     const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
     if (i >= n) return;
     const float g = gate[i];
@@ -340,6 +346,7 @@ __global__ void k_sigmoid_gate(float* __restrict__ out, const float* __restrict_
 // dst[*pos_dev][0 .. row_floats) = src: appends one row to a cache at a position read from device memory.
 __global__ void k_store_row_at(float* __restrict__ dst, const float* __restrict__ src, const int32_t* __restrict__ pos_dev, uint64_t row_floats,
                                uint64_t max_rows, uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
     const int32_t pos = *pos_dev;
     if (pos < 0 || uint64_t(pos) >= max_rows) {
         if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
@@ -352,6 +359,7 @@ __global__ void k_store_row_at(float* __restrict__ dst, const float* __restrict_
 template <uint32_t KIND>
 __global__ void k_embedding_rows(const uint8_t* __restrict__ w, uint64_t row_bytes, uint64_t rows, uint64_t cols, const int32_t* __restrict__ ids,
                                  float* __restrict__ out, uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
     const int32_t id = ids[blockIdx.x];
     if (id < 0 || uint64_t(id) >= rows) {
         if (threadIdx.x == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
@@ -372,7 +380,7 @@ extern "C" int32_t bhd_rmsnorm(bhd_ctx* ctx, float* y_dev, const float* x_dev, c
     if (n_rows > 0x7fffffffull) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: too many RMSNorm rows");
     if (!y_dev || !x_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rmsnorm: null buffer");
     bhd_device_guard guard(ctx);
-    k_rmsnorm<<<unsigned(n_rows), 256, 0, cudaStream_t(stream)>>>(y_dev, x_dev, weight_dev, n, eps);
+    bhd_launch_dependent(ctx, k_rmsnorm, dim3(unsigned(n_rows)), dim3(256), 0, cudaStream_t(stream), y_dev, x_dev, weight_dev, n, eps);
     BHD_LAUNCHED(ctx, "RMSNorm kernel");
     return BHD_OK;
 }
@@ -386,7 +394,7 @@ extern "C" int32_t bhd_rope(bhd_ctx* ctx, float* x_dev, const float* cos_dev, co
     if (!x_dev || !cos_dev || !sin_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: null buffer");
     bhd_device_guard guard(ctx);
     const uint64_t n = n_vectors * n_pairs;
-    k_rope<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(x_dev, cos_dev, sin_dev, n_vectors, vectors_per_position, n_pairs, layout,
+    bhd_launch_dependent(ctx, k_rope, dim3(unsigned((n + 255) / 256)), dim3(256), 0, cudaStream_t(stream), x_dev, cos_dev, sin_dev, n_vectors, vectors_per_position, n_pairs, layout,
                                                                          inverse, nullptr);
     BHD_LAUNCHED(ctx, "rotary embedding kernel");
     return BHD_OK;
@@ -400,7 +408,7 @@ extern "C" int32_t bhd_rope_at(bhd_ctx* ctx, float* x_dev, const float* cos_tabl
     if (!x_dev || !cos_table_dev || !sin_table_dev || !pos_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "rope: null buffer");
     bhd_device_guard guard(ctx);
     const uint64_t n = uint64_t(n_vectors) * n_pairs;
-    k_rope<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(x_dev, cos_table_dev, sin_table_dev, n_vectors, n_vectors, n_pairs, layout,
+    bhd_launch_dependent(ctx, k_rope, dim3(unsigned((n + 255) / 256)), dim3(256), 0, cudaStream_t(stream), x_dev, cos_table_dev, sin_table_dev, n_vectors, n_vectors, n_pairs, layout,
                                                                          inverse, pos_dev);
     BHD_LAUNCHED(ctx, "rotary embedding kernel");
     return BHD_OK;
@@ -419,7 +427,7 @@ extern "C" int32_t bhd_qk_norm_rope_store_at(bhd_ctx* ctx, float* q_dev, float* 
     if (!q_dev || !k_dev || !v_dev || !cos_table_dev || !sin_table_dev || !k_cache_dev || !v_cache_dev || !pos_dev)
         return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "qk_norm_rope_store: null buffer");
     bhd_device_guard guard(ctx);
-    k_qk_norm_rope_store<<<n_heads + 2 * n_kv_heads, 256, 0, cudaStream_t(stream)>>>(q_dev, k_dev, v_dev, q_norm_dev, k_norm_dev, cos_table_dev,
+    bhd_launch_dependent(ctx, k_qk_norm_rope_store, dim3(n_heads + 2 * n_kv_heads), dim3(256), 0, cudaStream_t(stream), q_dev, k_dev, v_dev, q_norm_dev, k_norm_dev, cos_table_dev,
                                                                                       sin_table_dev, k_cache_dev, v_cache_dev, pos_dev,
                                                                                       uint32_t(max_positions), n_heads, n_kv_heads, head_dim, eps, layout,
                                                                                       ctx->status_dev);
@@ -434,7 +442,7 @@ extern "C" int32_t bhd_store_row_at(bhd_ctx* ctx, float* dst_dev, const float* s
     if (!dst_dev || !src_dev || !pos_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "store_row_at: null buffer");
     if (row_floats > (1ull << 38)) return bhd_fail(ctx, BHD_ERR_SHAPE, "shape mismatch: row too long");
     bhd_device_guard guard(ctx);
-    k_store_row_at<<<unsigned((row_floats + 255) / 256), 256, 0, cudaStream_t(stream)>>>(dst_dev, src_dev, pos_dev, row_floats, max_rows,
+    bhd_launch_dependent(ctx, k_store_row_at, dim3(unsigned((row_floats + 255) / 256)), dim3(256), 0, cudaStream_t(stream), dst_dev, src_dev, pos_dev, row_floats, max_rows,
                                                                                           ctx->status_dev);
     BHD_LAUNCHED(ctx, "cache append kernel");
     return BHD_OK;
@@ -494,7 +502,7 @@ extern "C" int32_t bhd_embedding_rows(bhd_ctx* ctx, const bhd_weight* table, con
     bhd_device_guard guard(ctx);
     cudaStream_t s = cudaStream_t(stream);
 #define LAUNCH(K) \
-    k_embedding_rows<K><<<unsigned(n_ids), 256, 0, s>>>(table->dev, table->row_bytes, table->rows * table->slabs, table->cols, ids_dev, out_dev, ctx->status_dev)
+    bhd_launch_dependent(ctx, k_embedding_rows<K>, dim3(unsigned(n_ids)), dim3(256), 0, s, table->dev, table->row_bytes, table->rows * table->slabs, table->cols, ids_dev, out_dev, ctx->status_dev)
     BHD_DISPATCH_KIND(table->kind, LAUNCH)
 #undef LAUNCH
     BHD_LAUNCHED(ctx, "embedding row kernel");
@@ -506,7 +514,7 @@ extern "C" int32_t bhd_sigmoid_gate(bhd_ctx* ctx, float* out_dev, const float* i
     if (n == 0) return BHD_OK;
     if (!out_dev || !in_dev || !gate_dev) return bhd_fail(ctx, BHD_ERR_INVALID_ARGUMENT, "sigmoid_gate: null buffer");
     bhd_device_guard guard(ctx);
-    k_sigmoid_gate<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(out_dev, in_dev, gate_dev, n);
+    bhd_launch_dependent(ctx, k_sigmoid_gate, dim3(unsigned((n + 255) / 256)), dim3(256), 0, cudaStream_t(stream), out_dev, in_dev, gate_dev, n);
     BHD_LAUNCHED(ctx, "sigmoid gate kernel");
     return BHD_OK;
 }

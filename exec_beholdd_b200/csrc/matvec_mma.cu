@@ -536,6 +536,7 @@ __global__ void __launch_bounds__(THREADS) k_matvec_mma(const __grid_constant__ 
 // (crates/beholdd-model/src/qwen3moe/forward.rs:1385-1398); routes of other ranks are skipped.
 __global__ void k_moe_combine_slots(const float* __restrict__ d, const int32_t* __restrict__ route_slot,
                                     float* __restrict__ y, uint64_t n, uint32_t dim, uint32_t top_k, int accumulate) {
+    bhd_wait_for_prior_kernels();
     const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
     if (i >= n) return;
     const uint64_t t = i / dim, h = i - t * dim;
@@ -843,7 +844,7 @@ int32_t bhd_moe_experts_fast(bhd_ctx* ctx, const bhd_weight* gate, const bhd_wei
         return BHD_OK;
     }
     const uint64_t n = T * dim;
-    k_moe_combine_slots<<<unsigned((n + 255) / 256), 256, 0, s>>>(dbuf, pb.route_slot, y, n, uint32_t(dim), top_k, accumulate);
+    bhd_launch_dependent(ctx, k_moe_combine_slots, dim3(unsigned((n + 255) / 256)), dim3(256), 0, s, dbuf, pb.route_slot, y, n, uint32_t(dim), top_k, accumulate);
     BHD_LAUNCHED(ctx, "route combine kernel");
     *handled = true;
     return BHD_OK;

@@ -104,6 +104,7 @@ __global__ void k_moe_slots_i8(int mode, const MoeHeader* __restrict__ hdr, cons
                                const uint8_t* __restrict__ slot_cls, uint32_t max_cls, uint32_t top_k,
                                const float* __restrict__ src, const float* __restrict__ src2, uint32_t K, uint32_t n_slots,
                                uint8_t* __restrict__ out, uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
     const uint32_t chunk = blockIdx.y, slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (slot >= hdr->local_routes || slot >= n_slots) return;  // whole warps
     if (slot_cls[slot] > max_cls) return;                       // a group the tensor-core kernel takes (fp16 rows)
@@ -200,6 +201,7 @@ __global__ void __launch_bounds__((CW + 1) * 32) k_moe_grouped_i8(const __grid_c
     constexpr int TILE_ROWS = 16 * CW, CONSUMERS = CW, W_BYTES = TILE_ROWS * BOX;
     constexpr int X_MAX = NT * 4 * SLOT_BYTES;
     constexpr int STAGE = (W_BYTES + X_MAX + 127) / 128 * 128;
+    bhd_wait_for_prior_kernels();
     if (blockIdx.y >= p.hdr->gcount[p.cls]) return;  // whole CTA, before anything is set up
     const MoeGroup grp = p.groups[p.glist[blockIdx.y]];
     extern __shared__ uint8_t smem_raw[];
@@ -342,7 +344,7 @@ int32_t launch_nt(bhd_ctx* ctx, const bhd_weight* w0, const bhd_weight* w1, Grou
     memcpy(&m0, w0->tmap, sizeof(m0));
     memcpy(&m1, (w1 ? w1 : w0)->tmap, sizeof(m1));
     p.ring = RING;
-    kern<<<dim3(tiles, group_bound, w1 ? 2 : 1), THREADS, DYN, s>>>(m0, m1, p);
+    bhd_launch_dependent(ctx, kern, dim3(tiles, group_bound, w1 ? 2 : 1), dim3(THREADS), DYN, s, m0, m1, p);
     BHD_LAUNCHED(ctx, "integer grouped expert kernel");
     return BHD_OK;
 }
@@ -359,7 +361,7 @@ int32_t bhd_launch_moe_slots_i8(bhd_ctx* ctx, int mode, const void* hdr, const i
                                 uint32_t max_cls, uint32_t top_k, const float* src, const float* src2, uint32_t K, uint32_t n_slots,
                                 void* out, cudaStream_t s) {
     if (n_slots == 0) return BHD_OK;
-    k_moe_slots_i8<<<dim3((n_slots + 3) / 4, (K + CHUNK_K - 1) / CHUNK_K), 128, 0, s>>>(mode, static_cast<const MoeHeader*>(hdr), slot_route, slot_cls, max_cls, top_k,
+    bhd_launch_dependent(ctx, k_moe_slots_i8, dim3((n_slots + 3) / 4, (K + CHUNK_K - 1) / CHUNK_K), dim3(128), 0, s, mode, static_cast<const MoeHeader*>(hdr), slot_route, slot_cls, max_cls, top_k,
                                                                                          src, src2, K, n_slots, static_cast<uint8_t*>(out),
                                                                                          ctx->status_dev);
     BHD_LAUNCHED(ctx, mode ? "expert gating kernel" : "token gather kernel");

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __rest
                                                            uint32_t n_routes, uint32_t first, uint32_t n_local, uint32_t n_total,
                                                            uint32_t cap, uint32_t n_positions, MoePlanBuffers b, uint32_t* ticket,
                                                            uint32_t* status) {
+    bhd_wait_for_prior_kernels();
     extern __shared__ uint32_t hist[];  // [PLAN_WARPS][n_local], later the per-expert totals
     __shared__ uint32_t s_warp[PLAN_WARPS][NQ], s_carry[NQ];
     __shared__ bool s_last;
@@ -221,6 +222,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) k_moe_hist(const int32_t* __rest
 __global__ void __launch_bounds__(PLAN_THREADS) k_moe_scatter(const int32_t* __restrict__ experts, const float* __restrict__ weights,
                                                               uint32_t n_routes, uint32_t first, uint32_t n_local, uint32_t n_total,
                                                               uint32_t cap, MoePlanBuffers b) {
+    bhd_wait_for_prior_kernels();
     extern __shared__ uint32_t run[];  // [PLAN_WARPS][n_local]: routes of the expert already seen by this warp
     scatter_block(experts, weights, n_routes, first, n_local, n_total, cap, b, blockIdx.x, run);
 }
@@ -238,11 +240,11 @@ int32_t bhd_launch_moe_plan(bhd_ctx* ctx, const int32_t* experts, const float* w
     const unsigned blocks = unsigned((n_routes + BLOCK_ROUTES - 1) / BLOCK_ROUTES);
     const size_t smem = size_t(PLAN_WARPS) * n_local * sizeof(uint32_t);  // at most 32 KB
     uint32_t* ticket = ctx->status_dev + 1;  // a spare word next to the status word; zero between launches
-    k_moe_hist<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, n_positions, b, ticket,
+    bhd_launch_dependent(ctx, k_moe_hist, dim3(blocks), dim3(PLAN_THREADS), smem, s, experts, weights, n_routes, first_expert, n_local, n_total, cap, n_positions, b, ticket,
                                                   ctx->status_dev);
     BHD_LAUNCHED(ctx, "route histogram kernel");
     if (blocks > 1) {  // a single block scatters inside the first launch
-        k_moe_scatter<<<blocks, PLAN_THREADS, smem, s>>>(experts, weights, n_routes, first_expert, n_local, n_total, cap, b);
+        bhd_launch_dependent(ctx, k_moe_scatter, dim3(blocks), dim3(PLAN_THREADS), smem, s, experts, weights, n_routes, first_expert, n_local, n_total, cap, b);
         BHD_LAUNCHED(ctx, "route scatter kernel");
     }
     return BHD_OK;

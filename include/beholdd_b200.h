@@ -360,11 +360,16 @@ int32_t bhd_debug_wait_test(bhd_ctx* ctx, uint32_t spin_limit, uint32_t drop_one
  *                                tensor memory, 3 = persistent CTA pairs (tcgen05 cta_group::2) on 256-token tiles,
  *                                4 = persistent single CTAs, 5 = CTA pairs on 512-token tiles with two MMA issuers.
  *   BHD_OPTION_ROUTER_TILING     router-logits kernel for more than 64 positions: 0 = 32 positions per CTA and 3
- *                                tiles in flight, 1 = 32 and 5, 2 = 16 and 6, 3 = 8 and 7 (the small-batch tiling). */
+ *                                tiles in flight, 1 = 32 and 5, 2 = 16 and 6, 3 = 8 and 7 (the small-batch tiling).
+ *   BHD_OPTION_PLAIN_LAUNCHES    1: the short kernels of a layer (norms, rope, attention, routing, expert staging and
+ *                                combination) start only after the kernel before them has ended; 0 (default): they are
+ *                                launched as programmatic dependents, scheduled while their predecessor drains, and wait
+ *                                for it on the device before touching memory. Results are identical. */
 #define BHD_OPTION_MOE_TC_MIN_CLASS 1u
 #define BHD_OPTION_MOE_TC_PLAIN 2u
 #define BHD_OPTION_GEMM_IMPL 3u
 #define BHD_OPTION_ROUTER_TILING 5u
+#define BHD_OPTION_PLAIN_LAUNCHES 6u
 int32_t bhd_debug_option(bhd_ctx* ctx, uint32_t key, uint32_t value);
 
 /* Test hook, no counterpart in the reference: out[i] = the library's expf(in[i]), the function the
