@@ -285,6 +285,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_q8_pair(const __grid_consta
     } else if (warp == 10) {
         // ---- this CTA's half of the token tiles; the bytes of both halves are counted on the even CTA's barrier ----
         if (lane == 0) {
+            // The kernel is launched as a programmatic dependent of the fp16 conversion of the tokens: everything up to
+            // here (and the weight side) runs while that kernel drains; the tokens are read only after it has finished.
+            bhd_wait_for_prior_kernels();
             uint32_t g = 0;
             for (uint32_t i = 0; i < n_my && !aborted(); ++i) {
                 const uint32_t t = pair + i * n_pairs, m_tile = (t % p.tok_tiles) * TOKT, m0 = m_tile + rank * HALF_TOK;
@@ -580,13 +583,15 @@ int32_t bhd_launch_gemm_q8_pair(bhd_ctx* ctx, const bhd_weight* w, uint64_t slab
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = dyn;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->plain_launches ? 1 : 2;
     const bool q4 = w->kind == BHD_TYPE_Q4_K, q6 = w->kind == BHD_TYPE_Q6_K;
     if (q6 && wide) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q6_K, true>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");
     else if (q6) BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_gemm_q8_pair<BHD_TYPE_Q6_K, false>, map_w, map_x, p), "launching the paired tcgen05 matmul kernel");

@@ -138,6 +138,9 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t m, uint32_t n) { return 
 
 // f32 -> f16 for the activations, flagging values fp16 cannot hold.
 __global__ void k_f32_to_f16(const float* __restrict__ x, __half* __restrict__ out, uint64_t n, uint32_t* __restrict__ status) {
+    // The matmul kernel behind this one may be scheduled as soon as every CTA here has started: it sets up and converts
+    // its first weight slices meanwhile, and waits for this grid to finish before it loads a token.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint64_t i = (blockIdx.x * uint64_t(blockDim.x) + threadIdx.x) * 4;
     if (i >= n) return;
     const float4 v = *reinterpret_cast<const float4*>(x + i);
