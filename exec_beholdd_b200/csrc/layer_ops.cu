@@ -308,6 +308,173 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
     if (threadIdx.x < head_dim) out[(uint64_t(qp) * n_heads + head) * head_dim + threadIdx.x] = float(sum);
 }
 
+// Prefill form (head_dim 128, several query positions): the same sums in the same order, with the keys and values of a
+// kv head read once for a block of queries instead of once per (query, head). A CTA owns 32 (query, head) pairs: the G
+// query heads of one kv head for 32 / G consecutive positions; warp w owns pairs 4w .. 4w + 3. Keys and values pass through
+// shared memory in tiles of 32 positions (the next tile's loads in flight in registers).
+//   scores  lane = key of the tile; four chains a lane (its key against the warp's four queries, which sit in shared memory as
+//           f64 and are read as broadcasts). One fused multiply-add per element: the product of two f32 values is exact in
+//           f64, so fma(q, k, dot) rounds once, to the same value as the reference's add of the product.
+//   softmax per pair by its warp: max, exact exp, the sequential f32 sum by one lane per pair, 1 / sum.
+//   values  lane = output dimensions lane, lane + 32, lane + 64, lane + 96: sixteen chains a lane over the positions in order.
+constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_HD = 128, AB_KSTRIDE = AB_HD + 4;
+__host__ __device__ constexpr size_t attention_block_smem(uint32_t score_stride) {
+    return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_TILE) * AB_KSTRIDE * sizeof(float) + size_t(AB_PAIRS) * score_stride * sizeof(float);
+}
+__global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                                const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_query,
+                                                                uint32_t n_heads, uint32_t n_kv_heads, float scale, uint32_t score_stride) {
+    bhd_wait_for_prior_kernels();
+    extern __shared__ __align__(16) uint8_t ab_smem[];
+    double* qs = reinterpret_cast<double*>(ab_smem);                                  // [32 pairs][128] as f64
+    float* tile = reinterpret_cast<float*>(ab_smem + size_t(AB_PAIRS) * AB_HD * sizeof(double));   // [32 positions][132 or 128]
+    float* scores = tile + AB_TILE * AB_KSTRIDE;                                      // [32 pairs][score_stride]
+    const uint32_t G = n_heads / n_kv_heads, QB = AB_PAIRS / G, kv_head = blockIdx.y, q0 = blockIdx.x * QB;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n_here = min(QB, n_query - q0);            // queries of this block
+    const uint32_t max_vis = query_start + q0 + n_here;       // positions the block's last query sees
+    const uint64_t row_stride = uint64_t(n_kv_heads) * AB_HD;
+    // pair pi = (query q0 + pi / G, head kv_head * G + pi % G)
+    for (uint32_t i = threadIdx.x; i < AB_PAIRS * AB_HD; i += AB_THREADS) {
+        const uint32_t pi = i / AB_HD, d = i - pi * AB_HD, qi = pi / G;
+        qs[i] = qi < n_here ? double(q[(uint64_t(q0 + qi) * n_heads + kv_head * G + (pi - qi * G)) * AB_HD + d]) : 0.0;
+    }
+    uint32_t vis[4];   // visible positions of the warp's pairs (0: no such query)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t qi = (4 * warp + j) / G;
+        vis[j] = qi < n_here ? query_start + q0 + qi + 1 : 0u;
+    }
+    float4 stage[4];
+    auto fetch = [&](const float* cache, uint32_t p0) {   // rows p0 .. p0 + 31 of this kv head; rows from max_vis on are not read
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t idx = threadIdx.x + j * AB_THREADS, r = idx >> 5, c4 = idx & 31;
+            stage[j] = (p0 + r < max_vis) ? reinterpret_cast<const float4*>(cache + uint64_t(p0 + r) * row_stride + uint64_t(kv_head) * AB_HD)[c4]
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto put = [&](uint32_t stride) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t idx = threadIdx.x + j * AB_THREADS, r = idx >> 5, c4 = idx & 31;
+            *reinterpret_cast<float4*>(tile + r * stride + 4 * c4) = stage[j];
+        }
+    };
+    // ---- scores ----
+    fetch(k_cache, 0);
+    for (uint32_t p0 = 0; p0 < max_vis; p0 += AB_TILE) {
+        __syncthreads();                     // the tile's previous readers are done (first pass: qs is complete)
+        put(AB_KSTRIDE);
+        __syncthreads();
+        if (p0 + AB_TILE < max_vis) fetch(k_cache, p0 + AB_TILE);
+        const uint32_t kp = p0 + lane;
+        const float* krow = tile + lane * AB_KSTRIDE;
+        double dot[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll 4
+        for (uint32_t d4 = 0; d4 < AB_HD / 4; ++d4) {
+            const float4 kf = *reinterpret_cast<const float4*>(krow + 4 * d4);
+            const double k0 = double(kf.x), k1 = double(kf.y), k2 = double(kf.z), k3 = double(kf.w);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const double2* qq = reinterpret_cast<const double2*>(qs + (4 * warp + j) * AB_HD + 4 * d4);
+                const double2 a = qq[0], b = qq[1];
+                dot[j] = __fma_rn(a.x, k0, dot[j]);
+                dot[j] = __fma_rn(a.y, k1, dot[j]);
+                dot[j] = __fma_rn(b.x, k2, dot[j]);
+                dot[j] = __fma_rn(b.y, k3, dot[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (kp < vis[j]) scores[(4 * warp + j) * score_stride + kp] = float(__dmul_rn(dot[j], double(scale)));
+    }
+    __syncwarp();
+    // ---- softmax of the warp's four pairs (vecops::softmax: max, exp(v - max), sequential f32 sum, times 1 / sum) ----
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float* sc = scores + (4 * warp + j) * score_stride;
+        const uint32_t n = vis[j];
+        float m = -INFINITY;
+        for (uint32_t i = lane; i < n; i += 32) m = fmaxf(m, sc[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const bool all_masked = !isfinite(m);
+        for (uint32_t i = lane; i < n; i += 32) {
+            const float v = sc[i];
+            sc[i] = all_masked ? 0.0f : (isfinite(v) ? bhd_expf_exact(__fsub_rn(v, m)) : 0.0f);
+        }
+    }
+    __syncwarp();
+    float inv = 0.0f;
+    if (lane < 4) {   // lane j adds pair j's terms in position order
+        const float* sc = scores + (4 * warp + lane) * score_stride;
+        const uint32_t n = lane == 0 ? vis[0] : (lane == 1 ? vis[1] : (lane == 2 ? vis[2] : vis[3]));
+        float sum = 0.0f;
+        uint32_t i = 0;
+        for (; i + 8 <= n; i += 8) {
+            float e[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) e[t] = sc[i + t];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) sum = __fadd_rn(sum, e[t]);
+        }
+        for (; i < n; ++i) sum = __fadd_rn(sum, sc[i]);
+        inv = __fdiv_rn(1.0f, sum);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float* sc = scores + (4 * warp + j) * score_stride;
+        const float inv_j = __shfl_sync(0xffffffffu, inv, j);
+        // a row of -inf scores stays all zero, as in the single-query kernels (no multiplication by 1 / 0)
+        float m = -INFINITY;
+        for (uint32_t i = lane; i < vis[j]; i += 32) m = fmaxf(m, sc[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (m > 0.0f)
+            for (uint32_t i = lane; i < vis[j]; i += 32) sc[i] = __fmul_rn(sc[i], inv_j);
+    }
+    __syncwarp();
+    // ---- values ----
+    double acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = 0.0;
+    fetch(v_cache, 0);
+    for (uint32_t p0 = 0; p0 < max_vis; p0 += AB_TILE) {
+        __syncthreads();
+        put(AB_HD);
+        __syncthreads();
+        if (p0 + AB_TILE < max_vis) fetch(v_cache, p0 + AB_TILE);
+        const uint32_t n = min(uint32_t(AB_TILE), max_vis - p0);
+        for (uint32_t r = 0; r < n; ++r) {
+            const float* vrow = tile + r * AB_HD + lane;
+            const double v0 = double(vrow[0]), v1 = double(vrow[32]), v2 = double(vrow[64]), v3 = double(vrow[96]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (p0 + r < vis[j]) {   // uniform in the warp
+                    const double pj = double(scores[(4 * warp + j) * score_stride + p0 + r]);
+                    acc[j][0] = __fma_rn(pj, v0, acc[j][0]);
+                    acc[j][1] = __fma_rn(pj, v1, acc[j][1]);
+                    acc[j][2] = __fma_rn(pj, v2, acc[j][2]);
+                    acc[j][3] = __fma_rn(pj, v3, acc[j][3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t pi = 4 * warp + j, qi = pi / G;
+        if (qi < n_here) {
+            float* o = out + (uint64_t(q0 + qi) * n_heads + kv_head * G + (pi - qi * G)) * AB_HD;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) o[lane + 32 * c] = float(acc[j][c]);
+        }
+    }
+}
+
 // Launches the tiled kernel when the head shape allows, else the plain one. `score_slots` bounds the visible positions.
 static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const float* k, const float* v, uint32_t n_query, uint32_t query_start,
                                 uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, float scale, const int32_t* start_dev,
@@ -319,6 +486,21 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
         once.mark(ctx);
     }
     const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+    // several query positions of 128-wide heads: blocks of queries that share the keys and values of their kv head
+    const uint32_t group = n_heads / n_kv_heads, score_stride = uint32_t((score_slots + 3) / 4 * 4);
+    if (!start_dev && n_query >= 8 && head_dim == AB_HD && aligned && group <= 32 && (group & (group - 1)) == 0 &&
+        attention_block_smem(score_stride) <= 200 * 1024) {
+        static bhd_once_per_device once_block;
+        if (once_block.pending(ctx)) {
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_block, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+            once_block.mark(ctx);
+        }
+        const uint32_t qb = AB_PAIRS / group;
+        bhd_launch_dependent(ctx, k_attention_block, dim3((n_query + qb - 1) / qb, n_kv_heads), dim3(AB_THREADS), attention_block_smem(score_stride), s,
+                             out, q, k, v, query_start, n_query, n_heads, n_kv_heads, scale, score_stride);
+        BHD_LAUNCHED(ctx, "attention kernel");
+        return BHD_OK;
+    }
     const size_t tiled_smem = (size_t(ATT_TILE_FLOATS) + head_dim + score_slots) * sizeof(float);
     if (aligned && head_dim % 4 == 0 && head_dim >= 32 && head_dim <= 256 && ATT_TILE_FLOATS % head_dim == 0 && tiled_smem <= 200 * 1024) {
         bhd_launch_dependent(ctx, k_attention_tiled, dim3(n_query, n_heads), dim3(ATT_THREADS), tiled_smem, s, out, q, k, v, query_start, n_heads, n_kv_heads, head_dim, scale,

@@ -126,6 +126,17 @@ def test_attention_reference_vectors_and_seeded_cache_bit_exact(dev, oracle):
     out = torch.empty((3, n_heads, hd), device="cuda")
     dev.attention_resident(out, cuda(q[70:]), kd, vd, 70, 73, scale)
     assert np.array_equal(bits(out.cpu().numpy()), bits(want[70:]))
+    # a block-of-queries launch that starts inside the cache (33 queries at positions 40..72), and other group sizes
+    # (2 and 1 query heads per kv head: 16 and 32 positions per CTA)
+    out = torch.empty((33, n_heads, hd), device="cuda")
+    dev.attention_resident(out, cuda(q[40:]), kd, vd, 40, 73, scale)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want[40:]))
+    for heads2 in (8, 4):
+        q2 = synth.activations(37, (n_pos, heads2, hd))
+        want2 = oracle.causal_attention(q2, k, v, n_pos, heads2, n_kv, hd, scale).reshape(n_pos, heads2, hd)
+        out = torch.empty((n_pos, heads2, hd), device="cuda")
+        dev.attention_resident(out, cuda(q2), kd, vd, 0, n_pos, scale)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(want2))
     # a longer cache (several value tiles of the kernel), one decode query: the launch-parameter form and the form that
     # reads the position from device memory, both against the oracle to the bit
     n_pos = 203
