@@ -311,25 +311,41 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
 // Prefill form (head_dim 128, several query positions): the same sums in the same order, with the keys and values of a
 // kv head read once for a block of queries instead of once per (query, head). A CTA owns 32 (query, head) pairs: the G
 // query heads of one kv head for 32 / G consecutive positions; warp w owns pairs 4w .. 4w + 3. Keys and values pass through
-// shared memory in tiles of 32 positions (the next tile's loads in flight in registers).
+// shared memory in tiles of 32 positions (the next tile's loads in flight in registers), **as f64**: the f32 -> f64
+// conversion instruction runs at a few lanes per clock, and converting inside the chains (once per use) left the FP64
+// pipe 19 % busy; here every element is widened once per tile, with integer operations (f32_to_f64).
 //   scores  lane = key of the tile; four chains a lane (its key against the warp's four queries, which sit in shared memory as
 //           f64 and are read as broadcasts). One fused multiply-add per element: the product of two f32 values is exact in
 //           f64, so fma(q, k, dot) rounds once, to the same value as the reference's add of the product.
 //   softmax per pair by its warp: max, exact exp, the sequential f32 sum by one lane per pair, 1 / sum.
-//   values  lane = output dimensions lane, lane + 32, lane + 64, lane + 96: sixteen chains a lane over the positions in order.
-constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_HD = 128, AB_KSTRIDE = AB_HD + 4;
+//   values  lane = output dimensions lane, lane + 32, lane + 64, lane + 96: sixteen chains a lane over the positions in order;
+//           the tile's probabilities are widened once per warp into a small f64 table.
+// Blocks of late queries (the long ones) are scheduled first.
+constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_HD = 128, AB_KSTRIDE = AB_HD + 2;   // in doubles: rows 1040 bytes apart
 __host__ __device__ constexpr size_t attention_block_smem(uint32_t score_stride) {
-    return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_TILE) * AB_KSTRIDE * sizeof(float) + size_t(AB_PAIRS) * score_stride * sizeof(float);
+    return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_TILE) * AB_KSTRIDE * sizeof(double) + size_t(AB_PAIRS) * AB_TILE * sizeof(double) +
+           size_t(AB_PAIRS) * score_stride * sizeof(float);
+}
+// The f64 with the value of f, without the conversion unit: re-biased exponent and shifted mantissa for normal numbers and
+// zeros; subnormals, infinities and NaNs take the instruction.
+__device__ __forceinline__ double f32_to_f64(float f) {
+    const uint32_t b = __float_as_uint(f), e = b & 0x7f800000u;
+    if (e == 0u || e == 0x7f800000u) {
+        if ((b << 1) == 0u) return __hiloint2double(int(b), 0);
+        return double(f);
+    }
+    return __hiloint2double(int((b & 0x80000000u) | (((b & 0x7fffffffu) >> 3) + 0x38000000u)), int(b << 29));
 }
 __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
                                                                 const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_query,
                                                                 uint32_t n_heads, uint32_t n_kv_heads, float scale, uint32_t score_stride) {
     bhd_wait_for_prior_kernels();
     extern __shared__ __align__(16) uint8_t ab_smem[];
-    double* qs = reinterpret_cast<double*>(ab_smem);                                  // [32 pairs][128] as f64
-    float* tile = reinterpret_cast<float*>(ab_smem + size_t(AB_PAIRS) * AB_HD * sizeof(double));   // [32 positions][132 or 128]
-    float* scores = tile + AB_TILE * AB_KSTRIDE;                                      // [32 pairs][score_stride]
-    const uint32_t G = n_heads / n_kv_heads, QB = AB_PAIRS / G, kv_head = blockIdx.y, q0 = blockIdx.x * QB;
+    double* qs = reinterpret_cast<double*>(ab_smem);             // [32 pairs][128]
+    double* tile = qs + AB_PAIRS * AB_HD;                        // [32 positions][130 (keys) or 128 (values)]
+    double* pt = tile + AB_TILE * AB_KSTRIDE;                    // [32 pairs][32 positions]: the tile's probabilities
+    float* scores = reinterpret_cast<float*>(pt + AB_PAIRS * AB_TILE);   // [32 pairs][score_stride]
+    const uint32_t G = n_heads / n_kv_heads, QB = AB_PAIRS / G, kv_head = blockIdx.y, q0 = (gridDim.x - 1 - blockIdx.x) * QB;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_here = min(QB, n_query - q0);            // queries of this block
     const uint32_t max_vis = query_start + q0 + n_here;       // positions the block's last query sees
@@ -337,7 +353,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
     // pair pi = (query q0 + pi / G, head kv_head * G + pi % G)
     for (uint32_t i = threadIdx.x; i < AB_PAIRS * AB_HD; i += AB_THREADS) {
         const uint32_t pi = i / AB_HD, d = i - pi * AB_HD, qi = pi / G;
-        qs[i] = qi < n_here ? double(q[(uint64_t(q0 + qi) * n_heads + kv_head * G + (pi - qi * G)) * AB_HD + d]) : 0.0;
+        qs[i] = qi < n_here ? f32_to_f64(q[(uint64_t(q0 + qi) * n_heads + kv_head * G + (pi - qi * G)) * AB_HD + d]) : 0.0;
     }
     uint32_t vis[4];   // visible positions of the warp's pairs (0: no such query)
 #pragma unroll
@@ -354,11 +370,13 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
                                           : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
-    auto put = [&](uint32_t stride) {
+    auto put = [&](uint32_t stride) {   // widened
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t idx = threadIdx.x + j * AB_THREADS, r = idx >> 5, c4 = idx & 31;
-            *reinterpret_cast<float4*>(tile + r * stride + 4 * c4) = stage[j];
+            double2* dst = reinterpret_cast<double2*>(tile + r * stride + 4 * c4);
+            dst[0] = make_double2(f32_to_f64(stage[j].x), f32_to_f64(stage[j].y));
+            dst[1] = make_double2(f32_to_f64(stage[j].z), f32_to_f64(stage[j].w));
         }
     };
     // ---- scores ----
@@ -369,20 +387,19 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
         __syncthreads();
         if (p0 + AB_TILE < max_vis) fetch(k_cache, p0 + AB_TILE);
         const uint32_t kp = p0 + lane;
-        const float* krow = tile + lane * AB_KSTRIDE;
+        const double* krow = tile + lane * AB_KSTRIDE;
         double dot[4] = {0.0, 0.0, 0.0, 0.0};
 #pragma unroll 4
         for (uint32_t d4 = 0; d4 < AB_HD / 4; ++d4) {
-            const float4 kf = *reinterpret_cast<const float4*>(krow + 4 * d4);
-            const double k0 = double(kf.x), k1 = double(kf.y), k2 = double(kf.z), k3 = double(kf.w);
+            const double2 ka = *reinterpret_cast<const double2*>(krow + 4 * d4), kb = *reinterpret_cast<const double2*>(krow + 4 * d4 + 2);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const double2* qq = reinterpret_cast<const double2*>(qs + (4 * warp + j) * AB_HD + 4 * d4);
                 const double2 a = qq[0], b = qq[1];
-                dot[j] = __fma_rn(a.x, k0, dot[j]);
-                dot[j] = __fma_rn(a.y, k1, dot[j]);
-                dot[j] = __fma_rn(b.x, k2, dot[j]);
-                dot[j] = __fma_rn(b.y, k3, dot[j]);
+                dot[j] = __fma_rn(a.x, ka.x, dot[j]);
+                dot[j] = __fma_rn(a.y, ka.y, dot[j]);
+                dot[j] = __fma_rn(b.x, kb.x, dot[j]);
+                dot[j] = __fma_rn(b.y, kb.y, dot[j]);
             }
         }
 #pragma unroll
@@ -391,6 +408,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
     }
     __syncwarp();
     // ---- softmax of the warp's four pairs (vecops::softmax: max, exp(v - max), sequential f32 sum, times 1 / sum) ----
+    bool scaled[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         float* sc = scores + (4 * warp + j) * score_stride;
@@ -400,6 +418,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         const bool all_masked = !isfinite(m);
+        scaled[j] = !all_masked;             // a row without a finite maximum stays all zero (no multiplication by 1 / 0)
         for (uint32_t i = lane; i < n; i += 32) {
             const float v = sc[i];
             sc[i] = all_masked ? 0.0f : (isfinite(v) ? bhd_expf_exact(__fsub_rn(v, m)) : 0.0f);
@@ -427,12 +446,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
     for (int j = 0; j < 4; ++j) {
         float* sc = scores + (4 * warp + j) * score_stride;
         const float inv_j = __shfl_sync(0xffffffffu, inv, j);
-        // a row of -inf scores stays all zero, as in the single-query kernels (no multiplication by 1 / 0)
-        float m = -INFINITY;
-        for (uint32_t i = lane; i < vis[j]; i += 32) m = fmaxf(m, sc[i]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (m > 0.0f)
+        if (scaled[j])
             for (uint32_t i = lane; i < vis[j]; i += 32) sc[i] = __fmul_rn(sc[i], inv_j);
     }
     __syncwarp();
@@ -446,16 +460,20 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
     for (uint32_t p0 = 0; p0 < max_vis; p0 += AB_TILE) {
         __syncthreads();
         put(AB_HD);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)   // the warp's own rows of the probability table
+            pt[(4 * warp + j) * AB_TILE + lane] = (p0 + lane < vis[j]) ? f32_to_f64(scores[(4 * warp + j) * score_stride + p0 + lane]) : 0.0;
         __syncthreads();
         if (p0 + AB_TILE < max_vis) fetch(v_cache, p0 + AB_TILE);
         const uint32_t n = min(uint32_t(AB_TILE), max_vis - p0);
+#pragma unroll 2
         for (uint32_t r = 0; r < n; ++r) {
-            const float* vrow = tile + r * AB_HD + lane;
-            const double v0 = double(vrow[0]), v1 = double(vrow[32]), v2 = double(vrow[64]), v3 = double(vrow[96]);
+            const double* vrow = tile + r * AB_HD + lane;
+            const double v0 = vrow[0], v1 = vrow[32], v2 = vrow[64], v3 = vrow[96];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                if (p0 + r < vis[j]) {   // uniform in the warp
-                    const double pj = double(scores[(4 * warp + j) * score_stride + p0 + r]);
+                if (p0 + r < vis[j]) {   // uniform in the warp; a position a query does not see adds nothing, whatever its values
+                    const double pj = pt[(4 * warp + j) * AB_TILE + r];
                     acc[j][0] = __fma_rn(pj, v0, acc[j][0]);
                     acc[j][1] = __fma_rn(pj, v1, acc[j][1]);
                     acc[j][2] = __fma_rn(pj, v2, acc[j][2]);
