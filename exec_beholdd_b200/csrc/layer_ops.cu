@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
         const uint32_t kp = p0 + lane;
         const double* krow = tile + lane * AB_KSTRIDE;
         double dot[4] = {0.0, 0.0, 0.0, 0.0};
-#pragma unroll 4
+#pragma unroll 8
         for (uint32_t d4 = 0; d4 < AB_HD / 4; ++d4) {
             const double2 ka = *reinterpret_cast<const double2*>(krow + 4 * d4), kb = *reinterpret_cast<const double2*>(krow + 4 * d4 + 2);
 #pragma unroll
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
         __syncthreads();
         if (p0 + AB_TILE < max_vis) fetch(v_cache, p0 + AB_TILE);
         const uint32_t n = min(uint32_t(AB_TILE), max_vis - p0);
-#pragma unroll 2
+#pragma unroll 4
         for (uint32_t r = 0; r < n; ++r) {
             const double* vrow = tile + r * AB_HD + lane;
             const double v0 = vrow[0], v1 = vrow[32], v2 = vrow[64], v3 = vrow[96];
