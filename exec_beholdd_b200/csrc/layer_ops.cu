@@ -178,6 +178,18 @@ __global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, cons
     }
 }
 
+// The f64 with the value of f, without the conversion unit (which converts only a few lanes per clock: with one conversion per
+// operand inside the chains it, not the FP64 pipe, set the pace of the attention kernels): re-biased exponent and shifted
+// mantissa for normal numbers and zeros; subnormals, infinities and NaNs take the instruction.
+__device__ __forceinline__ double f32_to_f64(float f) {
+    const uint32_t b = __float_as_uint(f), e = b & 0x7f800000u;
+    if (e == 0u || e == 0x7f800000u) {
+        if ((b << 1) == 0u) return __hiloint2double(int(b), 0);
+        return double(f);
+    }
+    return __hiloint2double(int((b & 0x80000000u) | (((b & 0x7fffffffu) >> 3) + 0x38000000u)), int(b << 29));
+}
+
 // The same arithmetic in the same order, arranged so that memory latency stays off the dependent f64 chains (a decode
 // step has only one CTA per head, so nothing else hides it): 256 threads; a thread forms the dot products of its keys
 // from 16-byte loads, one 32-element batch ahead of the chain; the value rows are staged through shared memory in tiles
@@ -188,7 +200,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
                                                                  const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_heads,
                                                                  uint32_t n_kv_heads, uint32_t head_dim, float scale,
                                                                  const int32_t* __restrict__ start_dev, uint32_t max_positions,
-                                                                 uint32_t* __restrict__ status) {
+                                                                 uint32_t score_slots, uint32_t* __restrict__ status) {
     bhd_wait_for_prior_kernels();
     extern __shared__ __align__(16) float att_smem[];
     __shared__ float s_max, s_inv;
@@ -202,11 +214,12 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
         query_start = uint32_t(sd);
     }
     const uint32_t visible = query_start + qp + 1;
-    float* tile = att_smem;                          // ATT_TILE_FLOATS
-    float* qs = att_smem + ATT_TILE_FLOATS;          // head_dim
-    float* scores = qs + head_dim;                   // one per visible position (max_positions or the launch's bound)
+    float* tile = att_smem;                                              // ATT_TILE_FLOATS
+    double* qd = reinterpret_cast<double*>(att_smem + ATT_TILE_FLOATS);  // head_dim: the query, widened once
+    double* pd = qd + head_dim;                                          // one per visible position: the probabilities, widened once
+    float* scores = reinterpret_cast<float*>(pd + score_slots);          // one per visible position
     const float* query = q + (uint64_t(qp) * n_heads + head) * head_dim;
-    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = query[d];
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) qd[d] = f32_to_f64(query[d]);
     __syncthreads();
     const uint64_t row_stride = uint64_t(n_kv_heads) * head_dim;
     // scores: f64 dot product in element order, scaled in f64, rounded to f32
@@ -223,11 +236,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 if (b0 + j < n4) {
-                    const float* qq = qs + 4 * (b0 + j);
-                    dot = __dadd_rn(dot, __dmul_rn(double(qq[0]), double(cur[j].x)));
-                    dot = __dadd_rn(dot, __dmul_rn(double(qq[1]), double(cur[j].y)));
-                    dot = __dadd_rn(dot, __dmul_rn(double(qq[2]), double(cur[j].z)));
-                    dot = __dadd_rn(dot, __dmul_rn(double(qq[3]), double(cur[j].w)));
+                    const double2 qa = *reinterpret_cast<const double2*>(qd + 4 * (b0 + j)), qb = *reinterpret_cast<const double2*>(qd + 4 * (b0 + j) + 2);
+                    dot = __dadd_rn(dot, __dmul_rn(qa.x, double(cur[j].x)));
+                    dot = __dadd_rn(dot, __dmul_rn(qa.y, double(cur[j].y)));
+                    dot = __dadd_rn(dot, __dmul_rn(qb.x, double(cur[j].z)));
+                    dot = __dadd_rn(dot, __dmul_rn(qb.y, double(cur[j].w)));
                 }
             }
 #pragma unroll
@@ -266,9 +279,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
         s_inv = __fdiv_rn(1.0f, sum);
     }
     __syncthreads();
-    if (!all_masked) {
+    {
         const float inv = s_inv;
-        for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) scores[i] = __fmul_rn(scores[i], inv);
+        for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) pd[i] = f32_to_f64(all_masked ? scores[i] : __fmul_rn(scores[i], inv));
     }
     __syncthreads();
     // values: per output dimension an f64 sum over the visible positions, in position order
@@ -297,11 +310,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
             for (; pr + 8 <= n; pr += 8) {   // the eight products do not depend on the chain: formed ahead of it
                 double prod[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) prod[j] = __dmul_rn(double(scores[p0 + pr + j]), double(tile[(pr + j) * head_dim + threadIdx.x]));
+                for (int j = 0; j < 8; ++j) prod[j] = __dmul_rn(pd[p0 + pr + j], double(tile[(pr + j) * head_dim + threadIdx.x]));
 #pragma unroll
                 for (int j = 0; j < 8; ++j) sum = __dadd_rn(sum, prod[j]);
             }
-            for (; pr < n; ++pr) sum = __dadd_rn(sum, __dmul_rn(double(scores[p0 + pr]), double(tile[pr * head_dim + threadIdx.x])));
+            for (; pr < n; ++pr) sum = __dadd_rn(sum, __dmul_rn(pd[p0 + pr], double(tile[pr * head_dim + threadIdx.x])));
         }
         __syncthreads();
     }
@@ -325,16 +338,6 @@ constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_HD = 128, AB_KST
 __host__ __device__ constexpr size_t attention_block_smem(uint32_t score_stride) {
     return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_TILE) * AB_KSTRIDE * sizeof(double) + size_t(AB_PAIRS) * AB_TILE * sizeof(double) +
            size_t(AB_PAIRS) * score_stride * sizeof(float);
-}
-// The f64 with the value of f, without the conversion unit: re-biased exponent and shifted mantissa for normal numbers and
-// zeros; subnormals, infinities and NaNs take the instruction.
-__device__ __forceinline__ double f32_to_f64(float f) {
-    const uint32_t b = __float_as_uint(f), e = b & 0x7f800000u;
-    if (e == 0u || e == 0x7f800000u) {
-        if ((b << 1) == 0u) return __hiloint2double(int(b), 0);
-        return double(f);
-    }
-    return __hiloint2double(int((b & 0x80000000u) | (((b & 0x7fffffffu) >> 3) + 0x38000000u)), int(b << 29));
 }
 __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
                                                                 const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_query,
@@ -519,10 +522,10 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
         BHD_LAUNCHED(ctx, "attention kernel");
         return BHD_OK;
     }
-    const size_t tiled_smem = (size_t(ATT_TILE_FLOATS) + head_dim + score_slots) * sizeof(float);
+    const size_t tiled_smem = size_t(ATT_TILE_FLOATS) * sizeof(float) + (size_t(head_dim) + score_slots) * sizeof(double) + score_slots * sizeof(float);
     if (aligned && head_dim % 4 == 0 && head_dim >= 32 && head_dim <= 256 && ATT_TILE_FLOATS % head_dim == 0 && tiled_smem <= 200 * 1024) {
-        bhd_launch_dependent(ctx, k_attention_tiled, dim3(n_query, n_heads), dim3(ATT_THREADS), tiled_smem, s, out, q, k, v, query_start, n_heads, n_kv_heads, head_dim, scale,
-                                                                                   start_dev, max_positions, ctx->status_dev);
+        bhd_launch_dependent(ctx, k_attention_tiled, dim3(n_query, n_heads), dim3(ATT_THREADS), tiled_smem, s, out, q, k, v, query_start, n_heads, n_kv_heads,
+                             head_dim, scale, start_dev, max_positions, uint32_t(score_slots), ctx->status_dev);
     } else {
         bhd_launch_dependent(ctx, k_attention, dim3(n_query, n_heads), dim3(128), size_t(score_slots) * sizeof(float), s, out, q, k, v, query_start, n_heads, n_kv_heads, head_dim,
                                                                                               scale, start_dev, max_positions, ctx->status_dev);
