@@ -362,6 +362,24 @@ def bench_prefill(dev, torch, M, N, K, steps, warmup, peak_tflops, kind=8):
             "timed_ms": round(secs * 1e3, 1)}
 
 
+def bench_attention(dev, torch, n_query, start, steps, warmup):
+    """Causal attention at the full-forward head shapes (32 query heads, 4 kv heads, head_dim 128): `n_query` positions from
+    absolute position `start` against a cache of start + n_query positions. The sums are the reference's f64 chains."""
+    from exec_beholdd_b200 import synth
+
+    heads, kv, hd, n_pos = 32, 4, 128, start + n_query
+    q = torch.from_numpy(synth.activations(SEED + 41, (n_query, heads, hd))).cuda()
+    k = torch.from_numpy(synth.activations(SEED + 42, (n_pos, kv, hd))).cuda()
+    v = torch.from_numpy(synth.activations(SEED + 43, (n_pos, kv, hd))).cuda()
+    out = torch.empty((n_query, heads, hd), device="cuda")
+    scale = float(1.0 / np.sqrt(np.float32(hd)))
+    secs = time_region(torch, lambda: dev.attention_resident(out, q, k, v, start, n_pos, scale), steps, warmup)
+    dev.check_status()
+    pairs = sum(start + i + 1 for i in range(n_query)) * heads      # (query, head, visible position) triples
+    return {"us": round(secs / steps * 1e6, 1), "f64_fma_per_s": round(2.0 * pairs * hd * steps / secs / 1e9, 1), "unit": "G fused multiply-adds/s",
+            "timed_ms": round(secs * 1e3, 1)}
+
+
 def route_margin(torch, probs, top_k):
     """Smallest gap between the last selected and the first rejected probability over all positions:
     how far the selection is from a tie that a one-ulp difference in expf could flip."""
@@ -655,6 +673,10 @@ def run_gpu_arm(args):
                     psteps = max(dsteps, min(2000, int(0.2 / (2.0 * M * N * 4096 / (0.5 * tpeak * 1e12)))))
                     prefill_q4[f"M{M}_N{N}"] = leg(f"prefill_q4_k_M{M}_N{N}", lambda: bench_prefill(dev, torch, M, N, 4096, psteps, 3, tpeak, kind=12))
                     prefill_q6[f"M{M}_N{N}"] = leg(f"prefill_q6_k_M{M}_N{N}", lambda: bench_prefill(dev, torch, M, N, 4096, psteps, 3, tpeak, kind=14))
+        attention = {}
+        if not args.quick and "attention" in sections and world == 1:
+            attention["prefill_512"] = leg("attention_prefill", lambda: bench_attention(dev, torch, 512, 0, max(dsteps, 100), 3))
+            attention["decode_at_600"] = leg("attention_decode", lambda: bench_attention(dev, torch, 1, 599, max(dsteps, 400), 3))
         moe = {}
         tokens = () if (args.quick or "moe" not in sections) else tuple(int(v) for v in args.moe_tokens.split(",") if v)
         if world == 1:
@@ -705,7 +727,7 @@ def run_gpu_arm(args):
                          "traffic": HEAD_TRAFFIC_BYTES, "peak_source": peak_kind,
                          "kernel": "k_matvec_decode_i8 (the only kernel of the step)", "us_per_launch": launch_us},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["launches_timed"],
-            "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "prefill_q4_k_k4096": prefill_q4, "prefill_q6_k_k4096": prefill_q6, "moe_layer": moe,
+            "clocks": head_clocks, "matvec_detail": detail, "prefill_q8_0_k4096": prefill, "prefill_q4_k_k4096": prefill_q4, "prefill_q6_k_k4096": prefill_q6, "attention": attention, "moe_layer": moe,
             "row_split_projection": row_split, "full_forward": full,
         }
         if errors:
@@ -734,7 +756,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--moe-tokens", default="1,16,64,512", help="token counts of the routed-layer detail runs")
     ap.add_argument("--exchanges", default="peer,alltoall,gather", help="expert-parallel exchanges to run with several ranks")
-    ap.add_argument("--sections", default="detail,prefill,moe,rowsplit,forward", help="which detail runs follow the headline workload")
+    ap.add_argument("--sections", default="detail,prefill,attention,moe,rowsplit,forward", help="which detail runs follow the headline workload")
     ap.add_argument("--prefill-shapes", default="128x12288,128x4096,512x12288,512x4096,2048x12288,2048x4096",
                     help="MxN cases of the Q8_0 K=4096 prefill matmul detail run")
     args = ap.parse_args()

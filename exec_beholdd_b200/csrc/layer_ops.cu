@@ -321,6 +321,184 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
     if (threadIdx.x < head_dim) out[(uint64_t(qp) * n_heads + head) * head_dim + threadIdx.x] = float(sum);
 }
 
+// Decode form (one query position, head_dim 128): a cluster of four CTAs per head, because a decode step has only one CTA's
+// worth of work per head in the kernel above and leaves most SMs idle while its thread-per-key reads of the cache wait on
+// memory. Same sums, same order:
+//   scores  CTA r of the cluster takes the r-th quarter of the visible keys, in tiles of 128 keys copied asynchronously
+//           (16-byte cp.async, coalesced, double-buffered) into padded shared-memory rows; thread t runs the element-ordered
+//           chain of key t of the tile. Every score is stored into all four CTAs' score arrays through distributed shared
+//           memory; one cluster barrier.
+//   softmax by every CTA for itself (the same operations on the same values: the same bits).
+//   values  CTA r owns output dimensions 32r .. 32r + 31: warp 0 runs their position-ordered chains over tiles of 128
+//           positions x 32 dimensions, which all threads keep copying one tile ahead (the first two during the score phase).
+constexpr int AD_THREADS = 256, AD_CLUSTER = 4, AD_HD = 128, AD_KT = 128, AD_KROW = AD_HD + 4, AD_VT = 128, AD_VD = AD_HD / AD_CLUSTER;
+__host__ __device__ constexpr size_t attention_decode_smem(uint32_t score_slots) {
+    return 2 * size_t(AD_KT) * AD_KROW * sizeof(float) + 2 * size_t(AD_VT) * AD_VD * sizeof(float) + size_t(AD_HD) * sizeof(double) +
+           size_t(score_slots) * (sizeof(double) + sizeof(float)) + 16;
+}
+__device__ __forceinline__ uint32_t ad_smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ad_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ad_smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ad_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void ad_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__global__ void __launch_bounds__(AD_THREADS) k_attention_decode4(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                                  const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_heads,
+                                                                  uint32_t n_kv_heads, float scale, const int32_t* __restrict__ start_dev,
+                                                                  uint32_t max_positions, uint32_t score_slots, uint32_t* __restrict__ status) {
+    bhd_wait_for_prior_kernels();
+    extern __shared__ __align__(16) uint8_t ad_smem[];
+    __shared__ float s_max, s_inv;
+    float* kbuf = reinterpret_cast<float*>(ad_smem);                                   // [2][128 keys][132]
+    float* vbuf = kbuf + 2 * AD_KT * AD_KROW;                                          // [2][128 positions][32]
+    double* qd = reinterpret_cast<double*>(vbuf + 2 * AD_VT * AD_VD);                  // [128]
+    double* pd = qd + AD_HD;                                                           // [score_slots]
+    float* scores = reinterpret_cast<float*>(pd + score_slots);                        // [score_slots]
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const uint32_t head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
+    if (start_dev) {   // the same value in all four CTAs: they leave together, before any cluster barrier
+        const int32_t sd = *start_dev;
+        if (sd < 0 || uint32_t(sd) >= max_positions) {
+            if (threadIdx.x == 0 && rank == 0) atomicOr(status, BHD_DEV_BAD_EXPERT_ID);
+            return;
+        }
+        query_start = uint32_t(sd);
+    }
+    // every CTA of the cluster must be running before a peer stores into its shared memory: arrive now, wait before the stores
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    const uint32_t visible = query_start + 1;
+    const uint64_t row_stride = uint64_t(n_kv_heads) * AD_HD;
+    const float* kbase = k_cache + uint64_t(kv_head) * AD_HD;
+    const float* vbase = v_cache + uint64_t(kv_head) * AD_HD + rank * AD_VD;
+    const uint32_t kq = (visible + AD_CLUSTER - 1) / AD_CLUSTER, k0 = min(visible, rank * kq), k1 = min(visible, k0 + kq);   // this CTA's keys
+    const uint32_t k_tiles = (k1 - k0 + AD_KT - 1) / AD_KT, v_tiles = (visible + AD_VT - 1) / AD_VT;
+    auto copy_k = [&](uint32_t t) {   // keys k0 + 128 t .. of this CTA into buffer t & 1 (one commit group, possibly empty)
+        float* dst = kbuf + (t & 1) * AD_KT * AD_KROW;
+        const uint32_t base = k0 + t * AD_KT;
+#pragma unroll 4
+        for (uint32_t i = 0; i < AD_KT * (AD_HD / 4) / AD_THREADS; ++i) {
+            const uint32_t c = threadIdx.x + i * AD_THREADS, key = c >> 5, part = c & 31;
+            if (t < k_tiles && base + key < k1) ad_cp16(dst + key * AD_KROW + 4 * part, kbase + uint64_t(base + key) * row_stride + 4 * part);
+        }
+        ad_commit();
+    };
+    auto copy_v = [&](uint32_t t) {   // positions 128 t .. x this CTA's 32 dimensions into buffer t & 1
+        float* dst = vbuf + (t & 1) * AD_VT * AD_VD;
+#pragma unroll
+        for (uint32_t i = 0; i < AD_VT * (AD_VD / 4) / AD_THREADS; ++i) {
+            const uint32_t c = threadIdx.x + i * AD_THREADS, pos = c >> 3, part = c & 7;
+            if (t < v_tiles && t * AD_VT + pos < visible) ad_cp16(dst + pos * AD_VD + 4 * part, vbase + uint64_t(t * AD_VT + pos) * row_stride + 4 * part);
+        }
+        ad_commit();
+    };
+    // groups in flight, oldest first: K0, K1, V0, V1
+    copy_k(0);
+    copy_k(1);
+    copy_v(0);
+    copy_v(1);
+    const float* query = q + uint64_t(head) * AD_HD;
+    if (threadIdx.x < AD_HD) qd[threadIdx.x] = f32_to_f64(query[threadIdx.x]);
+    // ---- scores of this CTA's keys ----
+    uint32_t peer_scores[AD_CLUSTER];
+#pragma unroll
+    for (uint32_t r = 0; r < AD_CLUSTER; ++r)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_scores[r]) : "r"(ad_smem_u32(scores)), "r"(r));
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    for (uint32_t t = 0; t < k_tiles; ++t) {
+        // first tile: the three groups behind it (K1, V0, V1) may still be in flight; later tiles: only the newest group
+        // (the key tile after this one)
+        if (t == 0) ad_wait_group<3>(); else ad_wait_group<1>();
+        __syncthreads();
+        const uint32_t kp = k0 + t * AD_KT + threadIdx.x;
+        if (threadIdx.x < AD_KT && kp < k1) {
+            const float4* key = reinterpret_cast<const float4*>(kbuf + (t & 1) * AD_KT * AD_KROW + threadIdx.x * AD_KROW);
+            double dot = 0.0;
+#pragma unroll 2
+            for (uint32_t b0 = 0; b0 < AD_HD / 4; b0 += 8) {
+                double prod[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 kf = key[b0 + j];
+                    const double2 qa = *reinterpret_cast<const double2*>(qd + 4 * (b0 + j)), qb = *reinterpret_cast<const double2*>(qd + 4 * (b0 + j) + 2);
+                    prod[4 * j] = __dmul_rn(qa.x, double(kf.x));
+                    prod[4 * j + 1] = __dmul_rn(qa.y, double(kf.y));
+                    prod[4 * j + 2] = __dmul_rn(qb.x, double(kf.z));
+                    prod[4 * j + 3] = __dmul_rn(qb.y, double(kf.w));
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) dot = __dadd_rn(dot, prod[j]);
+            }
+            const float sc = float(__dmul_rn(dot, double(scale)));
+#pragma unroll
+            for (uint32_t r = 0; r < AD_CLUSTER; ++r)
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(peer_scores[r] + 4u * kp), "f"(sc) : "memory");
+        }
+        __syncthreads();                       // the buffer's readers are done
+        if (t + 2 < k_tiles) copy_k(t + 2); else ad_commit();   // keep the group count in step
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // ---- softmax (vecops::softmax: max, exp(v - max) (0 for -inf), sequential f32 sum, multiply by 1 / sum) ----
+    if (threadIdx.x < 32) {
+        float m = -INFINITY;
+        for (uint32_t i = threadIdx.x; i < visible; i += 32) m = fmaxf(m, scores[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x == 0) s_max = m;
+    }
+    __syncthreads();
+    const float m = s_max;
+    const bool all_masked = !isfinite(m);
+    for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) {
+        const float v = scores[i];
+        scores[i] = all_masked ? 0.0f : (isfinite(v) ? bhd_expf_exact(__fsub_rn(v, m)) : 0.0f);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.0f;
+        uint32_t i = 0;
+        for (; i + 8 <= visible; i += 8) {
+            float e[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) e[j] = scores[i + j];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum = __fadd_rn(sum, e[j]);
+        }
+        for (; i < visible; ++i) sum = __fadd_rn(sum, scores[i]);
+        s_inv = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    {
+        const float inv = s_inv;
+        for (uint32_t i = threadIdx.x; i < visible; i += blockDim.x) pd[i] = f32_to_f64(all_masked ? scores[i] : __fmul_rn(scores[i], inv));
+    }
+    // ---- values: warp 0, lane = output dimension 32 rank + lane ----
+    double sum = 0.0;
+    for (uint32_t t = 0; t < v_tiles; ++t) {
+        ad_wait_group<1>();                    // all but the newest group: tile t has landed
+        __syncthreads();                       // ... for every thread's copies (first pass: pd is complete)
+        if (threadIdx.x < 32) {
+            const float* vt = vbuf + (t & 1) * AD_VT * AD_VD + threadIdx.x;
+            const uint32_t p0 = t * AD_VT, n = min(uint32_t(AD_VT), visible - p0);
+            uint32_t pr = 0;
+            for (; pr + 8 <= n; pr += 8) {   // the eight products do not depend on the chain: formed ahead of it
+                double prod[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) prod[j] = __dmul_rn(pd[p0 + pr + j], double(vt[(pr + j) * AD_VD]));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum = __dadd_rn(sum, prod[j]);
+            }
+            for (; pr < n; ++pr) sum = __dadd_rn(sum, __dmul_rn(pd[p0 + pr], double(vt[pr * AD_VD])));
+        }
+        __syncthreads();
+        if (t + 2 < v_tiles) copy_v(t + 2); else ad_commit();
+    }
+    ad_wait_group<0>();
+    if (threadIdx.x < 32) out[uint64_t(head) * AD_HD + rank * AD_VD + threadIdx.x] = float(sum);
+    // no CTA may leave while a peer can still store scores into it: all stores precede the barrier above
+}
+
 // Prefill form (head_dim 128, several query positions): the same sums in the same order, with the keys and values of a
 // kv head read once for a block of queries instead of once per (query, head). A CTA owns 32 (query, head) pairs: the G
 // query heads of one kv head for 32 / G consecutive positions; warp w owns pairs 4w .. 4w + 3. Keys and values pass through
@@ -520,6 +698,33 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
         bhd_launch_dependent(ctx, k_attention_block, dim3((n_query + qb - 1) / qb, n_kv_heads), dim3(AB_THREADS), attention_block_smem(score_stride), s,
                              out, q, k, v, query_start, n_query, n_heads, n_kv_heads, scale, score_stride);
         BHD_LAUNCHED(ctx, "attention kernel");
+        return BHD_OK;
+    }
+    // one query position of 128-wide heads: a cluster of four CTAs per head
+    if (n_query == 1 && head_dim == AD_HD && aligned && attention_decode_smem(uint32_t(score_slots)) <= 200 * 1024) {
+        static bhd_once_per_device once_decode;
+        const size_t dyn = attention_decode_smem(uint32_t(score_slots));
+        if (once_decode.pending(ctx)) {
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_decode4, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+            once_decode.mark(ctx);
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(AD_CLUSTER, n_heads);
+        cfg.blockDim = dim3(AD_THREADS);
+        cfg.dynamicSmemBytes = dyn;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = AD_CLUSTER;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ctx->plain_launches ? 1 : 2;
+        BHD_CUDA(ctx, cudaLaunchKernelEx(&cfg, k_attention_decode4, out, q, k, v, query_start, n_heads, n_kv_heads, scale, start_dev, max_positions,
+                                         uint32_t(score_slots), ctx->status_dev), "launching the attention kernel");
+        ctx->launches += 1;
         return BHD_OK;
     }
     const size_t tiled_smem = size_t(ATT_TILE_FLOATS) * sizeof(float) + (size_t(head_dim) + score_slots) * sizeof(double) + score_slots * sizeof(float);

@@ -153,6 +153,15 @@ def test_attention_reference_vectors_and_seeded_cache_bit_exact(dev, oracle):
     dev.attention_at_resident(out, cuda(q1), kd, vd, pos, scale)
     assert np.array_equal(bits(out.cpu().numpy()), bits(want))
     dev.check_status()
+    # the four-CTA decode kernel at its edges: fewer keys than CTAs, one key tile, several key and value tiles
+    for n_vis in (1, 2, 5, 130, 1100):
+        qn = synth.activations(38 + n_vis, (1, n_heads, hd))
+        kn, vn = synth.activations(39, (n_vis, n_kv, hd)), synth.activations(40, (n_vis, n_kv, hd))
+        want_n = oracle.incremental_attention(qn, kn, vn, 1, n_vis - 1, n_vis, n_heads, n_kv, hd, scale).reshape(1, n_heads, hd)
+        out_n = torch.full((1, n_heads, hd), float("nan"), device="cuda")
+        dev.attention_resident(out_n, cuda(qn), cuda(kn), cuda(vn), n_vis - 1, n_vis, scale)
+        assert np.array_equal(bits(out_n.cpu().numpy()), bits(want_n)), n_vis
+    dev.check_status()
     pos.fill_(n_pos + 5)                       # a position outside the cache: reported, nothing written
     out.fill_(7.0)
     dev.attention_at_resident(out, cuda(q1), kd, vd, pos, scale)
