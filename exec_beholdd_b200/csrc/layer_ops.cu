@@ -178,9 +178,10 @@ __global__ void __launch_bounds__(128) k_attention(float* __restrict__ out, cons
     }
 }
 
-// The f64 with the value of f, without the conversion unit (which converts only a few lanes per clock: with one conversion per
-// operand inside the chains it, not the FP64 pipe, set the pace of the attention kernels): re-biased exponent and shifted
-// mantissa for normal numbers and zeros; subnormals, infinities and NaNs take the instruction.
+// The f64 with the value of f, without the conversion unit (16 lanes per clock and SM, a quarter of the FP64 pipe's rate: with
+// one conversion per operand in front of every multiply-add it was 54 % busy in the block kernel below and a third of that
+// kernel's instructions): re-biased exponent and shifted mantissa for normal numbers and zeros; subnormals, infinities and
+// NaNs take the instruction. For staging loops, not for use inside a dependent chain (its branch splits the schedule).
 __device__ __forceinline__ double f32_to_f64(float f) {
     const uint32_t b = __float_as_uint(f), e = b & 0x7f800000u;
     if (e == 0u || e == 0x7f800000u) {
@@ -502,9 +503,8 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode4(float* __restr
 // Prefill form (head_dim 128, several query positions): the same sums in the same order, with the keys and values of a
 // kv head read once for a block of queries instead of once per (query, head). A CTA owns 32 (query, head) pairs: the G
 // query heads of one kv head for 32 / G consecutive positions; warp w owns pairs 4w .. 4w + 3. Keys and values pass through
-// shared memory in tiles of 32 positions (the next tile's loads in flight in registers), **as f64**: the f32 -> f64
-// conversion instruction runs at a few lanes per clock, and converting inside the chains (once per use) left the FP64
-// pipe 19 % busy; here every element is widened once per tile, with integer operations (f32_to_f64).
+// shared memory in tiles of 32 positions (the next tile's loads in flight in registers), **as f64**: every element is
+// widened once per tile, with integer operations (f32_to_f64), instead of once per use inside the chains.
 //   scores  lane = key of the tile; four chains a lane (its key against the warp's four queries, which sit in shared memory as
 //           f64 and are read as broadcasts). One fused multiply-add per element: the product of two f32 values is exact in
 //           f64, so fma(q, k, dot) rounds once, to the same value as the reference's add of the product.
