@@ -511,23 +511,30 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode4(float* __restr
 //   softmax per pair by its warp: max, exact exp, the sequential f32 sum by one lane per pair, 1 / sum.
 //   values  lane = output dimensions lane, lane + 32, lane + 64, lane + 96: sixteen chains a lane over the positions in order;
 //           the tile's probabilities are widened once per warp into a small f64 table.
-// Blocks of late queries (the long ones) are scheduled first.
+// Blocks of late queries (the long ones) are scheduled first. The scores of the block's pairs sit in shared memory while they
+// fit (about 1000 positions); for longer caches (SCRATCH) the CTAs are persistent, take (query block, kv head) items
+// round-robin and keep their scores in a row per pair of a device-memory scratch area (each warp's own rows: they stay in L2).
 constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_HD = 128, AB_KSTRIDE = AB_HD + 2;   // in doubles: rows 1040 bytes apart
 __host__ __device__ constexpr size_t attention_block_smem(uint32_t score_stride) {
     return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_TILE) * AB_KSTRIDE * sizeof(double) + size_t(AB_PAIRS) * AB_TILE * sizeof(double) +
            size_t(AB_PAIRS) * score_stride * sizeof(float);
 }
+template <bool SCRATCH>
 __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k_cache,
                                                                 const float* __restrict__ v_cache, uint32_t query_start, uint32_t n_query,
-                                                                uint32_t n_heads, uint32_t n_kv_heads, float scale, uint32_t score_stride) {
+                                                                uint32_t n_heads, uint32_t n_kv_heads, float scale, uint32_t score_stride,
+                                                                float* __restrict__ scratch) {
     bhd_wait_for_prior_kernels();
     extern __shared__ __align__(16) uint8_t ab_smem[];
     double* qs = reinterpret_cast<double*>(ab_smem);             // [32 pairs][128]
     double* tile = qs + AB_PAIRS * AB_HD;                        // [32 positions][130 (keys) or 128 (values)]
     double* pt = tile + AB_TILE * AB_KSTRIDE;                    // [32 pairs][32 positions]: the tile's probabilities
-    float* scores = reinterpret_cast<float*>(pt + AB_PAIRS * AB_TILE);   // [32 pairs][score_stride]
-    const uint32_t G = n_heads / n_kv_heads, QB = AB_PAIRS / G, kv_head = blockIdx.y, q0 = (gridDim.x - 1 - blockIdx.x) * QB;
+    float* scores = SCRATCH ? scratch + uint64_t(blockIdx.x) * AB_PAIRS * score_stride   // [32 pairs][score_stride], this CTA's own
+                            : reinterpret_cast<float*>(pt + AB_PAIRS * AB_TILE);
+    const uint32_t G = n_heads / n_kv_heads, QB = AB_PAIRS / G, q_blocks = (n_query + QB - 1) / QB, n_items = q_blocks * n_kv_heads;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {   // one item per CTA unless SCRATCH
+    const uint32_t kv_head = item % n_kv_heads, q0 = (q_blocks - 1 - item / n_kv_heads) * QB;
     const uint32_t n_here = min(QB, n_query - q0);            // queries of this block
     const uint32_t max_vis = query_start + q0 + n_here;       // positions the block's last query sees
     const uint64_t row_stride = uint64_t(n_kv_heads) * AB_HD;
@@ -672,6 +679,7 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
             for (int c = 0; c < 4; ++c) o[lane + 32 * c] = float(acc[j][c]);
         }
     }
+    }   // items
 }
 
 // Launches the tiled kernel when the head shape allows, else the plain one. `score_slots` bounds the visible positions.
@@ -687,16 +695,28 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
     const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
     // several query positions of 128-wide heads: blocks of queries that share the keys and values of their kv head
     const uint32_t group = n_heads / n_kv_heads, score_stride = uint32_t((score_slots + 3) / 4 * 4);
-    if (!start_dev && n_query >= 8 && head_dim == AB_HD && aligned && group <= 32 && (group & (group - 1)) == 0 &&
-        attention_block_smem(score_stride) <= 200 * 1024) {
+    if (!start_dev && n_query >= 8 && head_dim == AB_HD && aligned && group <= 32 && (group & (group - 1)) == 0) {
         static bhd_once_per_device once_block;
+        static int per_sm[BHD_MAX_DEVICES] = {};
+        const size_t smem_scratch = attention_block_smem(0);
         if (once_block.pending(ctx)) {
-            BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_block, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_block<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+            BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_block<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_scratch)), "raising the shared memory limit");
+            BHD_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm[ctx->device], k_attention_block<true>, AB_THREADS, smem_scratch), "querying occupancy");
             once_block.mark(ctx);
         }
-        const uint32_t qb = AB_PAIRS / group;
-        bhd_launch_dependent(ctx, k_attention_block, dim3((n_query + qb - 1) / qb, n_kv_heads), dim3(AB_THREADS), attention_block_smem(score_stride), s,
-                             out, q, k, v, query_start, n_query, n_heads, n_kv_heads, scale, score_stride);
+        const uint32_t qb = AB_PAIRS / group, n_items = (n_query + qb - 1) / qb * n_kv_heads;
+        if (attention_block_smem(score_stride) <= 200 * 1024) {
+            bhd_launch_dependent(ctx, k_attention_block<false>, dim3(n_items), dim3(AB_THREADS), attention_block_smem(score_stride), s, out, q, k, v,
+                                 query_start, n_query, n_heads, n_kv_heads, scale, score_stride, static_cast<float*>(nullptr));
+        } else {
+            const uint32_t slots = uint32_t(ctx->sm_count) * uint32_t(per_sm[ctx->device] > 0 ? per_sm[ctx->device] : 1);
+            const uint32_t grid = n_items < slots ? n_items : slots;
+            const int32_t st = bhd_ensure_workspace(ctx, size_t(grid) * AB_PAIRS * score_stride * sizeof(float), s);
+            if (st != BHD_OK) return st;
+            bhd_launch_dependent(ctx, k_attention_block<true>, dim3(grid), dim3(AB_THREADS), smem_scratch, s, out, q, k, v, query_start, n_query, n_heads,
+                                 n_kv_heads, scale, score_stride, reinterpret_cast<float*>(ctx->workspace));
+        }
         BHD_LAUNCHED(ctx, "attention kernel");
         return BHD_OK;
     }

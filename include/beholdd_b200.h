@@ -222,7 +222,11 @@ int32_t bhd_rope(bhd_ctx* ctx, float* x_dev, const float* cos_dev, const float* 
 /* Device::incremental_causal_attention (lib.rs:228-253; cpu.rs:693-837): q [n_query][n_heads][head_dim] at absolute
  * positions query_start.., caches [n_kv_positions][n_kv_heads][head_dim] f32; position p attends to cache entries
  * 0..p. Device::causal_attention (cpu.rs:585-691) is query_start = 0 with the sequence itself as the cache. f64 dot
- * products and value sums, f32 softmax, as the CPU computes them. */
+ * products and value sums, f32 softmax, as the CPU computes them: every kernel form gives the CPU's bits. Forms: one
+ * query of 128-wide heads over up to about 2600 positions runs on a cluster of four CTAs per head; 8 or more queries of
+ * 128-wide heads run in blocks of 32 (query, head) pairs that share a kv head (the query heads per kv head a power of
+ * two, at most 32; over more than about 1000 positions the blocks keep their scores in the context workspace);
+ * everything else one CTA per (query, head). */
 int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev,
                                   const float* v_cache_dev, uint64_t n_query_positions, uint64_t query_start,
                                   uint64_t n_kv_positions, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,

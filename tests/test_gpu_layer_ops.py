@@ -153,6 +153,15 @@ def test_attention_reference_vectors_and_seeded_cache_bit_exact(dev, oracle):
     dev.attention_at_resident(out, cuda(q1), kd, vd, pos, scale)
     assert np.array_equal(bits(out.cpu().numpy()), bits(want))
     dev.check_status()
+    # a block-of-queries launch over a cache too long for the scores to sit in shared memory (persistent CTAs, scores in
+    # the context workspace): 40 queries at positions 1100..1139
+    n_long, n_q = 1140, 40
+    ql = synth.activations(44, (n_q, n_heads, hd))
+    kl, vl = synth.activations(45, (n_long, n_kv, hd)), synth.activations(46, (n_long, n_kv, hd))
+    want_l = oracle.incremental_attention(ql, kl, vl, n_q, n_long - n_q, n_long, n_heads, n_kv, hd, scale).reshape(n_q, n_heads, hd)
+    out_l = torch.full((n_q, n_heads, hd), float("nan"), device="cuda")
+    dev.attention_resident(out_l, cuda(ql), cuda(kl), cuda(vl), n_long - n_q, n_long, scale)
+    assert np.array_equal(bits(out_l.cpu().numpy()), bits(want_l))
     # the four-CTA decode kernel at its edges: fewer keys than CTAs, one key tile, several key and value tiles
     for n_vis in (1, 2, 5, 130, 1100):
         qn = synth.activations(38 + n_vis, (1, n_heads, hd))
