@@ -442,14 +442,22 @@ def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    # The prefill is ~1000 launches issued one by one from Python: a busy host stretches it. Three passes (each rewrites
+    # the same cache rows), the median reported and all three listed.
+    prefill_runs = []
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        logits = model.forward(ids, start=0)
+        e1.record()
+        torch.cuda.synchronize()
+        prefill_runs.append(e0.elapsed_time(e1) / 1e3)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record()
-    logits = model.forward(ids, start=0)
-    ev[1].record()
     out, logits = model.decode_greedy(logits, n_new)      # one graph launch per token
-    ev[2].record()
+    ev[1].record()
     torch.cuda.synchronize()
-    prefill_s, decode_s = ev[0].elapsed_time(ev[1]) / 1e3, ev[1].elapsed_time(ev[2]) / 1e3
+    prefill_s, decode_s = statistics.median(prefill_runs), ev[0].elapsed_time(ev[1]) / 1e3
     status_error = None
     try:
         dev.check_status()
@@ -460,6 +468,7 @@ def bench_full_forward(dev, torch, dist, rank, world, prompt_len=512, n_new=128)
         prefill_s, decode_s = max_over_ranks(torch, dist, prefill_s), max_over_ranks(torch, dist, decode_s)
     res = {"model": "Qwen3-30B-A3B architecture, random init, Q8_0 (separate Q8_0 LM head, f32 embeddings)", "layers": cfg.n_layers,
            "prefill_tokens_per_gpu": prompt_len, "decode_steps": n_new, "prefill_ms": prefill_s * 1e3,
+           "prefill_ms_runs": [round(v * 1e3, 2) for v in prefill_runs],
            "prefill_tokens_per_s": world * prompt_len / prefill_s, "decode_ms_per_token": decode_s / (n_new - 1) * 1e3,
            "decode_tokens_per_s": world * (n_new - 1) / decode_s, "weights_generated_in_s": build_s, "logits_finite": finite,
            "generated_ids_head": out[:8].cpu().tolist(),
