@@ -721,13 +721,31 @@ static int32_t launch_attention(bhd_ctx* ctx, float* out, const float* q, const 
         return BHD_OK;
     }
     // one query position of 128-wide heads: a cluster of four CTAs per head
-    if (n_query == 1 && head_dim == AD_HD && aligned && attention_decode_smem(uint32_t(score_slots)) <= 200 * 1024) {
-        static bhd_once_per_device once_decode;
-        const size_t dyn = attention_decode_smem(uint32_t(score_slots));
-        if (once_decode.pending(ctx)) {
-            BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_decode4, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
-            once_decode.mark(ctx);
+    static bool clusters_fit[BHD_MAX_DEVICES] = {};   // a cluster of four CTAs with the largest shared-memory size can be resident
+    static bhd_once_per_device once_decode;
+    if (n_query == 1 && head_dim == AD_HD && aligned && attention_decode_smem(uint32_t(score_slots)) <= 200 * 1024 && once_decode.pending(ctx)) {
+        BHD_CUDA(ctx, cudaFuncSetAttribute(k_attention_decode4, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "raising the shared memory limit");
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(AD_CLUSTER, 1);
+        probe.blockDim = dim3(AD_THREADS);
+        probe.dynamicSmemBytes = 200 * 1024;
+        cudaLaunchAttribute pa[1];
+        pa[0].id = cudaLaunchAttributeClusterDimension;
+        pa[0].val.clusterDim.x = AD_CLUSTER;
+        pa[0].val.clusterDim.y = 1;
+        pa[0].val.clusterDim.z = 1;
+        probe.attrs = pa;
+        probe.numAttrs = 1;
+        int n_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, k_attention_decode4, &probe) != cudaSuccess) {
+            cudaGetLastError();
+            n_clusters = 0;
         }
+        clusters_fit[ctx->device] = n_clusters > 0;
+        once_decode.mark(ctx);
+    }
+    if (n_query == 1 && head_dim == AD_HD && aligned && attention_decode_smem(uint32_t(score_slots)) <= 200 * 1024 && clusters_fit[ctx->device]) {
+        const size_t dyn = attention_decode_smem(uint32_t(score_slots));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(AD_CLUSTER, n_heads);
         cfg.blockDim = dim3(AD_THREADS);
