@@ -326,8 +326,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attention_tiled(float* __restri
 // worth of work per head in the kernel above and leaves most SMs idle while its thread-per-key reads of the cache wait on
 // memory. Same sums, same order:
 //   scores  CTA r of the cluster takes the r-th quarter of the visible keys, in tiles of 128 keys copied asynchronously
-//           (16-byte cp.async, coalesced, double-buffered) into padded shared-memory rows; thread t runs the element-ordered
-//           chain of key t of the tile. Every score is stored into all four CTAs' score arrays through distributed shared
+//           (16-byte cp.async, coalesced, two tiles in flight) into padded shared-memory rows; a thread runs the element-ordered
+//           chain of one key, the 256 threads covering two tiles a pass. Every score is stored into all four CTAs' score arrays through distributed shared
 //           memory; one cluster barrier.
 //   softmax by every CTA for itself (the same operations on the same values: the same bits).
 //   values  CTA r owns output dimensions 32r .. 32r + 31: warp 0 runs their position-ordered chains over tiles of 128
@@ -407,14 +407,14 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode4(float* __restr
     for (uint32_t r = 0; r < AD_CLUSTER; ++r)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_scores[r]) : "r"(ad_smem_u32(scores)), "r"(r));
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    for (uint32_t t = 0; t < k_tiles; ++t) {
-        // first tile: the three groups behind it (K1, V0, V1) may still be in flight; later tiles: only the newest group
-        // (the key tile after this one)
-        if (t == 0) ad_wait_group<3>(); else ad_wait_group<1>();
+    for (uint32_t tp = 0; tp < k_tiles; tp += 2) {   // two tiles a pass: threads 0..127 on the even tile, 128..255 on the odd one
+        // first pass: the two groups behind the pair (V0, V1) may still be in flight; later passes: the pair is the newest
+        if (tp == 0) ad_wait_group<2>(); else ad_wait_group<0>();
         __syncthreads();
-        const uint32_t kp = k0 + t * AD_KT + threadIdx.x;
-        if (threadIdx.x < AD_KT && kp < k1) {
-            const float4* key = reinterpret_cast<const float4*>(kbuf + (t & 1) * AD_KT * AD_KROW + threadIdx.x * AD_KROW);
+        const uint32_t t = tp + (threadIdx.x >> 7), krow_i = threadIdx.x & (AD_KT - 1);
+        const uint32_t kp = k0 + t * AD_KT + krow_i;
+        if (t < k_tiles && kp < k1) {
+            const float4* key = reinterpret_cast<const float4*>(kbuf + (t & 1) * AD_KT * AD_KROW + krow_i * AD_KROW);
             double dot = 0.0;
 #pragma unroll 2
             for (uint32_t b0 = 0; b0 < AD_HD / 4; b0 += 8) {
@@ -436,8 +436,9 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode4(float* __restr
             for (uint32_t r = 0; r < AD_CLUSTER; ++r)
                 asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(peer_scores[r] + 4u * kp), "f"(sc) : "memory");
         }
-        __syncthreads();                       // the buffer's readers are done
-        if (t + 2 < k_tiles) copy_k(t + 2); else ad_commit();   // keep the group count in step
+        __syncthreads();                       // the buffers' readers are done
+        copy_k(tp + 2);                        // one group each, empty beyond the last tile
+        copy_k(tp + 3);
     }
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     // ---- softmax (vecops::softmax: max, exp(v - max) (0 for -inf), sequential f32 sum, multiply by 1 / sum) ----
