@@ -506,18 +506,18 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode4(float* __restr
 // query heads of one kv head for 32 / G consecutive positions; warp w owns pairs 4w .. 4w + 3. Keys and values pass through
 // shared memory in tiles of 32 positions (the next tile's loads in flight in registers), **as f64**: every element is
 // widened once per tile, with integer operations (f32_to_f64), instead of once per use inside the chains.
-//   scores  lane = key of the tile; four chains a lane (its key against the warp's four queries, which sit in shared memory as
-//           f64 and are read as broadcasts). One fused multiply-add per element: the product of two f32 values is exact in
+//   scores  tiles of 64 keys, a lane takes keys lane and lane + 32: eight chains a lane (its keys against the warp's four
+//           queries, which sit in shared memory as f64 and are read as broadcasts). One fused multiply-add per element: the product of two f32 values is exact in
 //           f64, so fma(q, k, dot) rounds once, to the same value as the reference's add of the product.
 //   softmax per pair by its warp: max, exact exp, the sequential f32 sum by one lane per pair, 1 / sum.
 //   values  lane = output dimensions lane, lane + 32, lane + 64, lane + 96: sixteen chains a lane over the positions in order;
 //           the tile's probabilities are widened once per warp into a small f64 table.
 // Blocks of late queries (the long ones) are scheduled first. The scores of the block's pairs sit in shared memory while they
-// fit (about 1000 positions); for longer caches (SCRATCH) the CTAs are persistent, take (query block, kv head) items
+// fit (about 760 positions); for longer caches (SCRATCH) the CTAs are persistent, take (query block, kv head) items
 // round-robin and keep their scores in a row per pair of a device-memory scratch area (each warp's own rows: they stay in L2).
-constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_HD = 128, AB_KSTRIDE = AB_HD + 2;   // in doubles: rows 1040 bytes apart
+constexpr int AB_THREADS = 256, AB_PAIRS = 32, AB_TILE = 32, AB_KTILE = 64, AB_HD = 128, AB_KSTRIDE = AB_HD + 2;   // in doubles: rows 1040 bytes apart
 __host__ __device__ constexpr size_t attention_block_smem(uint32_t score_stride) {
-    return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_TILE) * AB_KSTRIDE * sizeof(double) + size_t(AB_PAIRS) * AB_TILE * sizeof(double) +
+    return size_t(AB_PAIRS) * AB_HD * sizeof(double) + size_t(AB_KTILE) * AB_KSTRIDE * sizeof(double) + size_t(AB_PAIRS) * AB_TILE * sizeof(double) +
            size_t(AB_PAIRS) * score_stride * sizeof(float);
 }
 template <bool SCRATCH>
@@ -528,8 +528,8 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
     bhd_wait_for_prior_kernels();
     extern __shared__ __align__(16) uint8_t ab_smem[];
     double* qs = reinterpret_cast<double*>(ab_smem);             // [32 pairs][128]
-    double* tile = qs + AB_PAIRS * AB_HD;                        // [32 positions][130 (keys) or 128 (values)]
-    double* pt = tile + AB_TILE * AB_KSTRIDE;                    // [32 pairs][32 positions]: the tile's probabilities
+    double* tile = qs + AB_PAIRS * AB_HD;                        // [64 keys][130] or [32 positions][128] (values)
+    double* pt = tile + AB_KTILE * AB_KSTRIDE;                   // [32 pairs][32 positions]: the tile's probabilities
     float* scores = SCRATCH ? scratch + uint64_t(blockIdx.x) * AB_PAIRS * score_stride   // [32 pairs][score_stride], this CTA's own
                             : reinterpret_cast<float*>(pt + AB_PAIRS * AB_TILE);
     const uint32_t G = n_heads / n_kv_heads, QB = AB_PAIRS / G, q_blocks = (n_query + QB - 1) / QB, n_items = q_blocks * n_kv_heads;
@@ -568,32 +568,60 @@ __global__ void __launch_bounds__(AB_THREADS) k_attention_block(float* __restric
             dst[1] = make_double2(f32_to_f64(stage[j].z), f32_to_f64(stage[j].w));
         }
     };
-    // ---- scores ----
-    fetch(k_cache, 0);
-    for (uint32_t p0 = 0; p0 < max_vis; p0 += AB_TILE) {
+    // ---- scores: tiles of 64 keys, a lane takes keys lane and lane + 32 of the tile (eight chains, and every broadcast
+    // query read serves two keys) ----
+    float4 kstage[8];
+    auto fetch_keys = [&](uint32_t p0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t idx = threadIdx.x + j * AB_THREADS, r = idx >> 5, c4 = idx & 31;
+            kstage[j] = (p0 + r < max_vis) ? reinterpret_cast<const float4*>(k_cache + uint64_t(p0 + r) * row_stride + uint64_t(kv_head) * AB_HD)[c4]
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto put_keys = [&]() {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t idx = threadIdx.x + j * AB_THREADS, r = idx >> 5, c4 = idx & 31;
+            double2* dst = reinterpret_cast<double2*>(tile + r * AB_KSTRIDE + 4 * c4);
+            dst[0] = make_double2(f32_to_f64(kstage[j].x), f32_to_f64(kstage[j].y));
+            dst[1] = make_double2(f32_to_f64(kstage[j].z), f32_to_f64(kstage[j].w));
+        }
+    };
+    fetch_keys(0);
+    for (uint32_t p0 = 0; p0 < max_vis; p0 += AB_KTILE) {
         __syncthreads();                     // the tile's previous readers are done (first pass: qs is complete)
-        put(AB_KSTRIDE);
+        put_keys();
         __syncthreads();
-        if (p0 + AB_TILE < max_vis) fetch(k_cache, p0 + AB_TILE);
-        const uint32_t kp = p0 + lane;
-        const double* krow = tile + lane * AB_KSTRIDE;
-        double dot[4] = {0.0, 0.0, 0.0, 0.0};
-#pragma unroll 8
+        if (p0 + AB_KTILE < max_vis) fetch_keys(p0 + AB_KTILE);
+        const double* krow0 = tile + lane * AB_KSTRIDE;
+        const double* krow1 = krow0 + 32 * AB_KSTRIDE;
+        double dot[2][4] = {{0.0, 0.0, 0.0, 0.0}, {0.0, 0.0, 0.0, 0.0}};
+#pragma unroll 4
         for (uint32_t d4 = 0; d4 < AB_HD / 4; ++d4) {
-            const double2 ka = *reinterpret_cast<const double2*>(krow + 4 * d4), kb = *reinterpret_cast<const double2*>(krow + 4 * d4 + 2);
+            const double2 ka0 = *reinterpret_cast<const double2*>(krow0 + 4 * d4), kb0 = *reinterpret_cast<const double2*>(krow0 + 4 * d4 + 2);
+            const double2 ka1 = *reinterpret_cast<const double2*>(krow1 + 4 * d4), kb1 = *reinterpret_cast<const double2*>(krow1 + 4 * d4 + 2);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const double2* qq = reinterpret_cast<const double2*>(qs + (4 * warp + j) * AB_HD + 4 * d4);
                 const double2 a = qq[0], b = qq[1];
-                dot[j] = __fma_rn(a.x, ka.x, dot[j]);
-                dot[j] = __fma_rn(a.y, ka.y, dot[j]);
-                dot[j] = __fma_rn(b.x, kb.x, dot[j]);
-                dot[j] = __fma_rn(b.y, kb.y, dot[j]);
+                dot[0][j] = __fma_rn(a.x, ka0.x, dot[0][j]);
+                dot[1][j] = __fma_rn(a.x, ka1.x, dot[1][j]);
+                dot[0][j] = __fma_rn(a.y, ka0.y, dot[0][j]);
+                dot[1][j] = __fma_rn(a.y, ka1.y, dot[1][j]);
+                dot[0][j] = __fma_rn(b.x, kb0.x, dot[0][j]);
+                dot[1][j] = __fma_rn(b.x, kb1.x, dot[1][j]);
+                dot[0][j] = __fma_rn(b.y, kb0.y, dot[0][j]);
+                dot[1][j] = __fma_rn(b.y, kb1.y, dot[1][j]);
             }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (kp < vis[j]) scores[(4 * warp + j) * score_stride + kp] = float(__dmul_rn(dot[j], double(scale)));
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t kp = p0 + 32 * h + lane;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (kp < vis[j]) scores[(4 * warp + j) * score_stride + kp] = float(__dmul_rn(dot[h][j], double(scale)));
+        }
     }
     __syncwarp();
     // ---- softmax of the warp's four pairs (vecops::softmax: max, exp(v - max), sequential f32 sum, times 1 / sum) ----

@@ -225,7 +225,7 @@ int32_t bhd_rope(bhd_ctx* ctx, float* x_dev, const float* cos_dev, const float* 
  * products and value sums, f32 softmax, as the CPU computes them: every kernel form gives the CPU's bits. Forms: one
  * query of 128-wide heads over up to about 2600 positions runs on a cluster of four CTAs per head; 8 or more queries of
  * 128-wide heads run in blocks of 32 (query, head) pairs that share a kv head (the query heads per kv head a power of
- * two, at most 32; over more than about 1000 positions the blocks keep their scores in the context workspace);
+ * two, at most 32; over more than about 760 positions the blocks keep their scores in the context workspace);
  * everything else one CTA per (query, head). */
 int32_t bhd_incremental_attention(bhd_ctx* ctx, float* out_dev, const float* q_dev, const float* k_cache_dev,
                                   const float* v_cache_dev, uint64_t n_query_positions, uint64_t query_start,
