@@ -60,3 +60,27 @@ def test_rope_tables_are_f64_angles_rounded_once():
     a = np.arange(5, dtype=np.float64)[:, None] * freqs[None, :]
     assert np.array_equal(cos, np.cos(a).astype(np.float32)) and np.array_equal(sin, np.sin(a).astype(np.float32))
     assert np.all(cos[0] == 1.0) and np.all(sin[0] == 0.0)
+
+
+def test_integer_widening_rule_of_the_attention_kernels_matches_the_conversion():
+    """The attention kernels widen f32 to f64 with integer operations for normal numbers and zeros (sign kept, exponent
+    re-biased by 896, mantissa shifted by 29 bits) and leave subnormals, infinities and NaNs to the conversion instruction.
+    The rule, restated on the host, gives the bits of the exact conversion on every normal number and zero."""
+    rng = np.random.default_rng(5)
+    bits32 = np.concatenate([rng.integers(0, 2**32, 200000, dtype=np.uint64).astype(np.uint32),
+                             np.array([0x00000000, 0x80000000, 0x00800000, 0x80800000, 0x7f7fffff, 0xff7fffff, 0x3f800000, 0x00000001,
+                                       0x007fffff, 0x7f800000, 0xff800000, 0x7fc00000], dtype=np.uint32)])
+    exp = bits32 & np.uint32(0x7f800000)
+    special = (exp == 0) | (exp == np.uint32(0x7f800000))
+    zero = (bits32 << np.uint32(1)) == 0
+    hi = (bits32 & np.uint32(0x80000000)) | (((bits32 & np.uint32(0x7fffffff)) >> np.uint32(3)) + np.uint32(0x38000000))
+    lo = bits32 << np.uint32(29)
+    widened = (hi.astype(np.uint64) << np.uint64(32)) | lo.astype(np.uint64)
+    widened[zero] = bits32[zero].astype(np.uint64) << np.uint64(32)
+    with np.errstate(invalid="ignore"):        # signalling NaN patterns among the random bits
+        exact = bits32.view(np.float32).astype(np.float64).view(np.uint64)
+    fast = ~special | zero
+    assert fast.sum() > 190000 and np.array_equal(widened[fast], exact[fast])
+    # the cases the kernels hand to the instruction are exactly the ones the rule would get wrong
+    slow = special & ~zero
+    assert slow.sum() >= 5 and not np.any(widened[slow] == exact[slow])
